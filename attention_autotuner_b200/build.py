@@ -1,0 +1,54 @@
+"""Builds libattn_b200.so (the C-ABI library of include/attn_b200.h) in-tree with nvcc for sm_100a.
+
+    python -m attention_autotuner_b200.build [--force]
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
+LIB_PATH = os.path.join(CSRC, "libattn_b200.so")
+NVCC = os.environ.get("NVCC", shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc")
+
+NVCC_FLAGS = [
+    "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+    "--shared", "-Xcompiler", "-fPIC", "--split-compile=0",
+]
+
+
+def _sources():
+    out = []
+    for name in sorted(os.listdir(CSRC)):
+        if name.endswith((".cu", ".cuh", ".h")):
+            out.append(os.path.join(CSRC, name))
+    out.append(os.path.join(CSRC, "..", "..", "include", "attn_b200.h"))
+    return out
+
+
+def is_stale() -> bool:
+    if not os.path.exists(LIB_PATH):
+        return True
+    t = os.path.getmtime(LIB_PATH)
+    return any(os.path.exists(s) and os.path.getmtime(s) > t for s in _sources())
+
+
+def build_library(force: bool = False, verbose: bool = False) -> str:
+    """Compiles csrc/attn_b200.cu into csrc/libattn_b200.so; returns the library path."""
+    if not force and not is_stale():
+        return LIB_PATH
+    cmd = [NVCC, *NVCC_FLAGS, "-o", LIB_PATH, os.path.join(CSRC, "attn_b200.cu")]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+    if verbose:
+        print(res.stderr)
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))

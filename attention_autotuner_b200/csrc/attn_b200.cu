@@ -1,0 +1,89 @@
+// libattn_b200.so: the ahead-of-time built C-ABI library (declarations in include/attn_b200.h).
+// Holds the default tile configuration of every kernel for the supported head dimensions; the
+// autotuner compiles further configurations into separate per-config libraries from the same
+// kernel headers.
+#include "../../include/attn_b200.h"
+
+#include "fa_fwd_launch.cuh"
+#include "selftest.cuh"
+
+using namespace ab200;
+
+namespace {
+
+// Default flash-attention tiles per (dqk, dv-chunk): two ping-ponging query tiles when tensor memory
+// and shared memory allow it, otherwise one.
+template <bool BF16>
+int fa_fwd_dispatch(const FaFwdArgs& a, int dqk, cudaStream_t st, bool profile, float* ms) {
+  auto run = [&](auto cfg_tag) -> int {
+    using Cfg = decltype(cfg_tag);
+    if (!profile) return fa_fwd_launch<Cfg>(a, st);
+    *ms = profile_loop([&] { return fa_fwd_launch<Cfg>(a, st); }, st);
+    return *ms < 0.f ? kErrCuda : kOk;
+  };
+  // chunk of the V head dim handled per CTA
+  const int dv = a.dv;
+  const int chunk = (dv % 256 == 0) ? 256 : (dv % 128 == 0) ? 128 : 64;
+  if (dv % 64 != 0 || dv > 512 || dv <= 0) return fail(kErrUnsupported, "fa_fwd: dv=%d (need multiple of 64, <= 512)", dv);
+  switch (dqk) {
+    case 64:
+      if (chunk == 64) return run(FaFwdConfig<64, 64, 2, 6, BF16>{});
+      if (chunk == 128) return run(FaFwdConfig<64, 128, 2, 4, BF16>{});
+      return run(FaFwdConfig<64, 256, 1, 3, BF16>{});
+    case 128:
+      if (chunk == 64) return run(FaFwdConfig<128, 64, 2, 4, BF16>{});
+      if (chunk == 128) return run(FaFwdConfig<128, 128, 2, 4, BF16>{});
+      return run(FaFwdConfig<128, 256, 1, 3, BF16>{});
+    case 256:
+      if (chunk == 64) return run(FaFwdConfig<256, 64, 1, 2, BF16>{});
+      if (chunk == 128) return run(FaFwdConfig<256, 128, 1, 2, BF16>{});
+      return run(FaFwdConfig<256, 256, 1, 2, BF16>{});
+    default:
+      return fail(kErrUnsupported, "fa_fwd: dqk=%d not built into libattn_b200 (64, 128, 256)", dqk);
+  }
+}
+
+int fa_fwd_common(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H, int Lq, int Lkv,
+                  int dqk, int dv, int dtype, float scale, int causal, void* stream, bool profile, float* ms) {
+  if (B <= 0 || H <= 0) return fail(kErrInvalidArgument, "fa_fwd: B and H must be positive");
+  if (dtype != ATTN_B200_F16 && dtype != ATTN_B200_BF16) return fail(kErrInvalidArgument, "fa_fwd: dtype %d", dtype);
+  FaFwdArgs a{q, k, v, o, lse, B * H, Lq, Lkv, dv, scale, causal};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return dtype == ATTN_B200_BF16 ? fa_fwd_dispatch<true>(a, dqk, st, profile, ms)
+                                 : fa_fwd_dispatch<false>(a, dqk, st, profile, ms);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* attn_b200_last_error(void) { return error_buffer(); }
+
+int attn_b200_device_status(int clear) {
+  int det = 0;
+  return read_device_status(clear, &det);
+}
+
+int attn_b200_abi_version(void) { return 1; }
+
+int attn_b200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H, int Lq,
+                     int Lkv, int dqk, int dv, int dtype, float scale, int causal, void* stream) {
+  return fa_fwd_common(q, k, v, o, lse, B, H, Lq, Lkv, dqk, dv, dtype, scale, causal, stream, false, nullptr);
+}
+
+float attn_b200_fa_fwd_profile(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H,
+                               int Lq, int Lkv, int dqk, int dv, int dtype, float scale, int causal,
+                               void* stream) {
+  float ms = -1.f;
+  int rc = fa_fwd_common(q, k, v, o, lse, B, H, Lq, Lkv, dqk, dv, dtype, scale, causal, stream, true, &ms);
+  return rc == kOk ? ms : -1.f;
+}
+
+int attn_b200_selftest_gemm_ss(const void* a, const void* b, float* d, int N, int K, int dtype, void* stream) {
+  return selftest_gemm_ss(a, b, d, N, K, dtype, reinterpret_cast<cudaStream_t>(stream));
+}
+int attn_b200_selftest_gemm_ts(const void* p, const void* v, float* d, int N, int dtype, void* stream) {
+  return selftest_gemm_ts(p, v, d, N, dtype, reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

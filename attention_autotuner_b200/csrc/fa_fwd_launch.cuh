@@ -1,0 +1,90 @@
+// Host launcher for fa_fwd_sm100_kernel: argument checks, tensor maps, grid, timing loop.
+// Plays the role of the reference's generated launch shims
+// (csrc/kernels/attention/regfuse/profile_code.py:28-76: profile() and kernel_entry()).
+#pragma once
+
+#include <math.h>
+
+#include "fa_fwd_sm100.cuh"
+#include "host_common.cuh"
+
+namespace ab200 {
+
+struct FaFwdArgs {
+  const void* q;  // [BH, Lq, dqk]
+  const void* k;  // [BH, Lkv, dqk]
+  const void* v;  // [BH, Lkv, dv]
+  void* o;        // [BH, Lq, dv]
+  float* lse;     // [BH, Lq] or nullptr
+  int BH, Lq, Lkv, dv;
+  float scale;
+  int causal;
+};
+
+template <class Cfg>
+int fa_fwd_launch(const FaFwdArgs& a, cudaStream_t stream) {
+  if (!a.q || !a.k || !a.v || !a.o) return fail(kErrInvalidArgument, "fa_fwd: null tensor pointer");
+  if (a.BH <= 0 || a.Lq <= 0 || a.Lkv <= 0) return fail(kErrInvalidArgument, "fa_fwd: sizes must be positive");
+  if (a.BH > 65535) return fail(kErrInvalidArgument, "fa_fwd: batch*heads %d exceeds 65535", a.BH);
+  if (a.dv % Cfg::DV != 0) return fail(kErrUnsupported, "fa_fwd: dv %d is not a multiple of the tile's %d", a.dv, Cfg::DV);
+  if (!(a.scale > 0.f) || !isfinite(a.scale)) return fail(kErrInvalidArgument, "fa_fwd: scale must be positive and finite");
+  if (!aligned16(a.q) || !aligned16(a.k) || !aligned16(a.v) || !aligned16(a.o))
+    return fail(kErrInvalidArgument, "fa_fwd: tensors must be 16-byte aligned");
+
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_tmap_3d(&tq, a.q, Cfg::BF16, Cfg::DQK, a.Lq, a.BH, 64, Cfg::BM))) return rc;
+  if ((rc = make_tmap_3d(&tk, a.k, Cfg::BF16, Cfg::DQK, a.Lkv, a.BH, 64, Cfg::BN))) return rc;
+  if ((rc = make_tmap_3d(&tv, a.v, Cfg::BF16, a.dv, a.Lkv, a.BH, 64, Cfg::BN))) return rc;
+
+  FaFwdParams p;
+  p.o = a.o;
+  p.lse = a.lse;
+  p.dv_total = a.dv;
+  p.Lq = a.Lq;
+  p.Lkv = a.Lkv;
+  p.causal = a.causal ? 1 : 0;
+  p.scale = a.scale;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+
+  auto kernel = &fa_fwd_sm100_kernel<Cfg>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+  if (e != cudaSuccess) return fail(kErrCuda, "fa_fwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  dim3 grid((a.Lq + Cfg::BM * Cfg::NQ - 1) / (Cfg::BM * Cfg::NQ), a.BH, a.dv / Cfg::DV);
+  kernel<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  return check_launch("fa_fwd launch");
+}
+
+// One warm-up launch, then enough launches to fill about 100 ms; returns ms per launch, -1 on error.
+template <class F>
+float profile_loop(F&& launch_once, cudaStream_t stream) {
+  cudaEvent_t e0, e1;
+  if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return -1.f;
+  float ms = -1.f;
+  do {
+    cudaEventRecord(e0, stream);
+    if (launch_once() != kOk) break;
+    if (cudaEventRecord(e1, stream) != cudaSuccess || cudaEventSynchronize(e1) != cudaSuccess) break;
+    float t = 0.f;
+    cudaEventElapsedTime(&t, e0, e1);
+    int repeats = t > 0.f ? static_cast<int>(ceilf(100.0f / t)) : 100;
+    if (repeats < 1) repeats = 1;
+    if (repeats > 2000) repeats = 2000;
+    cudaEventRecord(e0, stream);
+    bool bad = false;
+    for (int i = 0; i < repeats; ++i)
+      if (launch_once() != kOk) { bad = true; break; }
+    if (bad) break;
+    if (cudaEventRecord(e1, stream) != cudaSuccess || cudaEventSynchronize(e1) != cudaSuccess) break;
+    if (cudaGetLastError() != cudaSuccess) break;
+    cudaEventElapsedTime(&t, e0, e1);
+    int det = 0;
+    if (read_device_status(1, &det) != 0) break;
+    ms = t / repeats;
+  } while (0);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  return ms;
+}
+
+}  // namespace ab200
