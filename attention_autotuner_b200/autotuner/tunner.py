@@ -1,0 +1,72 @@
+"""Per-operation search spaces and feasibility checks (reference: python/autotuner/tunner.py).
+
+The knobs are Blackwell's: query tiles per CTA, depth of the TMA-fed K/V ring, V columns per CTA.
+Feasibility = shared memory per CTA <= arch.smem_cap and tensor-memory columns <= arch.tmem_columns,
+which replace the reference's shared-memory and accumulator-register checks (tunner.py:102-151)."""
+import ctypes
+
+from .base_tunner import BaseTunner, CompileResult  # noqa: F401
+from .configs import AttnConfig
+from .configs.base_config import dv_chunk_for, find_best_pair, find_factor_pairs  # noqa: F401
+
+
+def _flops_fwd(t, causal):
+    B, H, Lq, dqk = t[0].shape
+    Lkv, dv = t[2].shape[2], t[2].shape[3]
+    pairs = Lq * Lkv
+    if causal:
+        shift = Lkv - Lq
+        pairs = sum(max(0, min(Lkv, i + shift + 1)) for i in range(Lq))
+    return 2.0 * B * H * pairs * (dqk + dv)
+
+
+class AttnTunner(BaseTunner):
+    def __init__(self, arch, torch_array: list, *, scale=None, causal=False):
+        super().__init__(arch, torch_array, "attention", scale=scale, causal=causal)
+
+    def validate_kernel(self, config):
+        if config.Kd % 64 != 0 or config.D % 64 != 0 or config.D % config.dv_chunk != 0:
+            return False
+        if config.smem_bytes() > self.arch.smem_cap:
+            return False
+        if config.tmem_columns() > getattr(self.arch, "tmem_columns", 512):
+            return False
+        if config.dv_chunk > 256 or config.kv_stages < 2:
+            return False
+        return True
+
+    def generate_configs(self, Br: int, Bc: int, dim_qk: int, dim_v: int):
+        configs = []
+        q_tiles = Br // 128
+        chunks = [c for c in (256, 128, 64) if dim_v % c == 0]
+        for dv_chunk in chunks[:2]:
+            for kv_stages in (2, 3, 4, 5, 6):
+                configs.append(AttnConfig(Br, Bc, dim_qk, dim_v, q_tiles=q_tiles, kv_stages=kv_stages,
+                                          dv_chunk=dv_chunk, dtype=self.dtype))
+        return configs
+
+    def default_config(self):
+        dqk, dv = self.problem_key["dim_qk"], self.problem_key["dim_v"]
+        best = None
+        for q_tiles in (2, 1):
+            for kv_stages in (4, 6, 3, 2):
+                cfg = AttnConfig(128 * q_tiles, 128, dqk, dv, q_tiles=q_tiles, kv_stages=kv_stages,
+                                 dv_chunk=dv_chunk_for(dv), dtype=self.dtype)
+                if self.validate_kernel(cfg):
+                    best = cfg
+                    break
+            if best is not None:
+                break
+        if best is None:
+            raise ValueError(f"no feasible attention tile for dqk={dqk}, dv={dv}")
+        return best
+
+    def flops(self):
+        return _flops_fwd(self.torch_array, self.causal)
+
+    def _profile_args(self):
+        q, k, v, o = self.torch_array[:4]
+        ptrs = [ctypes.c_void_p(t.data_ptr()) for t in (q, k, v, o)] + [ctypes.c_void_p(0)]
+        scale = 0.125 if self.scale is None else self.scale
+        tail = [ctypes.c_float(scale), ctypes.c_int(1 if self.causal else 0), ctypes.c_void_p(0)]
+        return ptrs, tail

@@ -1,0 +1,204 @@
+"""Flash-attention forward on the GPU, through the C ABI and through the Python operator, against the
+CPU fp32 oracle and the golden vectors of the reference's formula.
+
+Tolerances (absolute, vs the fp32 oracle evaluated on the same 16-bit inputs): fp16 max-abs <= 2e-3 and
+mean-abs <= 2e-4; bf16 8x those (three fewer mantissa bits in P and O). LSE is fp32: 1e-3."""
+import ctypes
+
+import pytest
+import torch
+
+from attention_autotuner_b200 import _lib
+from attention_autotuner_b200.arch import B200
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+DT = {"fp16": (torch.float16, 0), "bf16": (torch.bfloat16, 1)}
+
+
+def P(t):
+    return ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+
+
+def run_capi(lib, q, k, v, scale, causal, want_lse=True):
+    B, H, Lq, dqk = q.shape
+    Lkv, dv = v.shape[2], v.shape[3]
+    code = 0 if q.dtype == torch.float16 else 1
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    o = torch.full((B, H, Lq, dv), float("nan"), device="cuda", dtype=q.dtype)
+    lse = torch.full((B, H, Lq), float("nan"), device="cuda") if want_lse else None
+    _lib.check(lib.attn_b200_fa_fwd(P(qd), P(kd), P(vd), P(o), P(lse), B, H, Lq, Lkv, dqk, dv, code, scale,
+                                    int(causal), None))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    return o.cpu(), (lse.cpu() if want_lse else None)
+
+
+def rand_qkv(seed, B, H, Lq, Lkv, dqk, dv, dt):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(B, H, Lq, dqk, generator=g).to(dt), torch.randn(B, H, Lkv, dqk, generator=g).to(dt),
+            torch.randn(B, H, Lkv, dv, generator=g).to(dt))
+
+
+def check(o, lse, q, k, v, scale, causal, dtype_name):
+    oref, lref = oracle.attention_fwd(q, k, v, scale, causal)
+    st = oracle.error_stats(o, oref)
+    assert oracle.within(st, dtype_name), st
+    if lse is not None:
+        assert (lse - lref).abs().max().item() < 1e-3
+
+
+@pytest.mark.parametrize("name", ["attn_d64", "attn_d128_ragged", "attn_d256_128_demo_scaling"])
+def test_golden_vectors_of_the_reference_formula(lib, golden, name):
+    g = golden(name)
+    q, k, v = (torch.from_numpy(g[x]) for x in ("q", "k", "v"))
+    o, _ = run_capi(lib, q, k, v, 0.125, False)
+    st = oracle.error_stats(o, torch.from_numpy(g["o"]))
+    # the demo-scaling case has |o| up to 12, where fp16's own spacing (2^-7) exceeds the absolute bound:
+    # the bound scales with max(1, peak |o|)
+    assert oracle.within(st, "fp16", scale_by_peak=True), st
+
+
+def test_config1_full(lib):
+    """BASELINE config 1: B=2 H=4 L=512 d=64 fp16 non-causal scale 1/8, every slice."""
+    c = oracle.CONFIGS["C1"]
+    qs, ks, vs = [], [], []
+    for b in range(c["B"]):
+        for h in range(c["H"]):
+            q, k, v = oracle.slice_inputs("C1", b, h, c["H"], c["Lq"], c["Lkv"], c["dqk"], c["dv"], torch.float16)
+            qs.append(q), ks.append(k), vs.append(v)
+    shape = lambda xs, L, d: torch.stack(xs).view(c["B"], c["H"], L, d)
+    q, k, v = shape(qs, 512, 64), shape(ks, 512, 64), shape(vs, 512, 64)
+    o, lse = run_capi(lib, q, k, v, 0.125, False)
+    check(o, lse, q, k, v, 0.125, False, "fp16")
+
+
+@pytest.mark.parametrize("dtype_name", ["fp16", "bf16"])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("dqk,dv", [(64, 64), (128, 128)])
+def test_square_medium(lib, dtype_name, causal, dqk, dv):
+    dt, _ = DT[dtype_name]
+    q, k, v = rand_qkv(3, 2, 3, 1024, 1024, dqk, dv, dt)
+    scale = dqk ** -0.5
+    o, lse = run_capi(lib, q, k, v, scale, causal)
+    check(o, lse, q, k, v, scale, causal, dtype_name)
+
+
+@pytest.mark.parametrize("Lq,Lkv,causal", [(1, 1, False), (1, 300, False), (127, 129, False), (129, 127, False),
+                                           (200, 333, True), (333, 200, True), (384, 640, True), (257, 256, True),
+                                           (128, 128, True), (256, 2048, False)])
+def test_ragged_and_rectangular(lib, Lq, Lkv, causal):
+    """Lengths that are not tile multiples, single rows, Lq != Lkv (causal is bottom-right aligned; rows
+    with no visible key give zeros and lse = -inf, as the oracle's softmax of an empty row would not)."""
+    q, k, v = rand_qkv(5, 1, 2, Lq, Lkv, 128, 128, torch.float16)
+    scale = 128 ** -0.5
+    o, lse = run_capi(lib, q, k, v, scale, causal)
+    oref, lref = oracle.attention_fwd(q, k, v, scale, causal)
+    if causal and Lkv < Lq:
+        empty = torch.arange(Lq) + (Lkv - Lq) < 0
+        assert (o[:, :, empty] == 0).all() and torch.isinf(lse[:, :, empty]).all()
+        o, oref, lse, lref = o[:, :, ~empty], oref[:, :, ~empty], lse[:, :, ~empty], lref[:, :, ~empty]
+    st = oracle.error_stats(o, oref)
+    assert oracle.within(st, "fp16"), st
+    assert (lse - lref).abs().max().item() < 1e-3
+
+
+@pytest.mark.parametrize("dqk,dv", [(256, 256), (256, 128), (128, 512), (64, 192), (128, 64), (256, 64), (64, 256)])
+def test_head_dim_matrix(lib, dqk, dv):
+    """The reference's head-dim range: dqk % 64 == 0 <= 256, dv % 64 == 0 <= 512
+    (python/ops/attention_interface.py:23-24), including its test shapes (256,256), (256,128), (128,128)."""
+    q, k, v = rand_qkv(7, 1, 2, 512, 512, dqk, dv, torch.float16)
+    o, lse = run_capi(lib, q, k, v, 0.125, False)
+    check(o, lse, q, k, v, 0.125, False, "fp16")
+
+
+def test_large_scores_trigger_rescale(lib):
+    """Keys whose scores grow along the sequence force the running maximum to move by far more than the
+    lazy-rescale threshold in every block."""
+    q, k, v = rand_qkv(9, 1, 1, 256, 1024, 64, 64, torch.float16)
+    ramp = torch.linspace(0.2, 4.0, 1024)[None, None, :, None]
+    k = (k.float() * ramp).half()
+    o, lse = run_capi(lib, q, k, v, 0.5, False)
+    check(o, lse, q, k, v, 0.5, False, "fp16")
+
+
+def test_reference_test_shape_and_scalings(lib):
+    """(B,H,L)=(4,8,2048) as python/tests/test_runtime.py:16 with one head kept, and the demo input scalings
+    key = 3*randn, value = 3*randn (python/tests/attntuner_demo.py:45-48), fixed 0.125 scale."""
+    q, k, v = rand_qkv(11, 1, 1, 2048, 2048, 128, 128, torch.float16)
+    k, v = (k.float() * 3).half(), (v.float() * 3).half()
+    o, _ = run_capi(lib, q, k, v, 0.125, False, want_lse=False)
+    oref, _ = oracle.attention_fwd(q, k, v, 0.125, False)
+    st = oracle.error_stats(o, oref)
+    # |v| is 3x larger here; scale the absolute bound with the output's peak
+    assert oracle.within(st, "fp16", scale_by_peak=True), st
+
+
+def test_deterministic_and_linear_in_v(lib):
+    """Size-independent properties: two runs are bit-identical; O is linear in V."""
+    q, k, v = rand_qkv(13, 1, 2, 1024, 1024, 128, 128, torch.float16)
+    o1, _ = run_capi(lib, q, k, v, 0.09, True)
+    o2, _ = run_capi(lib, q, k, v, 0.09, True)
+    assert torch.equal(o1, o2)
+    o3, _ = run_capi(lib, q, k, (v.float() * 2).half(), 0.09, True)
+    assert torch.allclose(o3.float(), 2 * o1.float(), atol=2e-3)
+
+
+def test_config2_full_size_properties(lib):
+    """BASELINE config 2 at full size (B=8 H=16 L=4096 d=128, fp16 and bf16, causal and not): two sampled
+    (batch, head) slices against the oracle, and softmax rows summing to one (V = ones gives O = 1)."""
+    c = oracle.CONFIGS["C2"]
+    B, H, L, d = c["B"], c["H"], c["Lq"], c["dqk"]
+    scale = d ** -0.5
+    for dtype_name in ("fp16", "bf16"):
+        dt, code = DT[dtype_name]
+        g = torch.Generator(device="cuda").manual_seed(17)
+        q = torch.randn(B, H, L, d, device="cuda", generator=g).to(dt)
+        k = torch.randn(B, H, L, d, device="cuda", generator=g).to(dt)
+        v = torch.randn(B, H, L, d, device="cuda", generator=g).to(dt)
+        ones = torch.ones_like(v)
+        o = torch.empty_like(q)
+        for causal in (False, True):
+            _lib.check(lib.attn_b200_fa_fwd(P(q), P(k), P(v), P(o), None, B, H, L, L, d, d, code, scale, int(causal), None))
+            torch.cuda.synchronize()
+            for (b, h) in ((0, 0), (B - 1, H - 1)):
+                oref, _ = oracle.attention_fwd(q[b, h].cpu(), k[b, h].cpu(), v[b, h].cpu(), scale, causal)
+                st = oracle.error_stats(o[b, h].cpu(), oref)
+                assert oracle.within(st, dtype_name), (dtype_name, causal, st)
+            _lib.check(lib.attn_b200_fa_fwd(P(q), P(k), P(ones), P(o), None, B, H, L, L, d, d, code, scale, int(causal), None))
+            torch.cuda.synchronize()
+            assert (o.float() - 1).abs().max().item() < (4e-3 if dtype_name == "fp16" else 2e-2)
+    assert _lib.device_status() == 0
+
+
+def test_python_operator_matches_capi(lib):
+    from attention_autotuner_b200.ops.attention_interface import flash_attn_func
+    q, k, v = rand_qkv(19, 2, 2, 512, 768, 128, 128, torch.float16)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    o = flash_attn_func(qd, kd, vd, B200())                      # reference defaults: scale 0.125, non-causal
+    oc, _ = run_capi(lib, q, k, v, 0.125, False)
+    assert torch.equal(o.cpu(), oc)
+    o2, lse = flash_attn_func(qd, kd, vd, B200(), True, 0.07, True)
+    check(o2.cpu(), lse.cpu(), q, k, v, 0.07, True, "fp16")
+    with pytest.raises(AssertionError):
+        flash_attn_func(qd[..., :96], kd[..., :96], vd, B200())   # key_dim % 64 != 0, as the reference asserts
+
+
+def test_legacy_kernel_entry_symbol():
+    """kernel_entry(q,k,v,o,B,H,Seq_k,Seq_q) and profile(q,k,v,o,B,H,Seq_q,Seq_k) of a per-config library keep
+    the reference's argument orders (csrc/kernels/attention/regfuse/profile_code.py:30,68)."""
+    from attention_autotuner_b200.autotuner.configs import AttnConfig
+    from attention_autotuner_b200.autotuner.runtime import Runtime
+    q, k, v = rand_qkv(23, 1, 2, 256, 640, 64, 64, torch.float16)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    o = torch.zeros(1, 2, 256, 64, device="cuda", dtype=torch.float16)
+    rt = Runtime(B200(), AttnConfig(256, 128, 64, 64, q_tiles=2, kv_stages=4))
+    rt.apply([qd, kd, vd, o])
+    torch.cuda.synchronize()
+    oref, _ = oracle.attention_fwd(q, k, v, 0.125, False)
+    assert oracle.within(oracle.error_stats(o.cpu(), oref), "fp16")
+    so = ctypes.CDLL(rt.lib_path)
+    so.profile.restype = ctypes.c_float
+    ms = so.profile(P(qd), P(kd), P(vd), P(o), 1, 2, 256, 640)
+    assert 0 < ms < 10

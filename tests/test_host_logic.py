@@ -1,0 +1,142 @@
+"""Host-side logic that needs no GPU: config records, search-space enumeration and feasibility, cache
+round trip, the reference's import names, and that the C-ABI library loads and exports every symbol its
+header declares."""
+import ctypes
+import json
+import os
+import re
+
+import pytest
+import torch
+
+from attention_autotuner_b200.arch import A100, B200, RTX4090, Arch
+from attention_autotuner_b200.autotuner.configs import AttnConfig, BaseConfig, supported_configs
+from attention_autotuner_b200.autotuner.runtime import KernelError, Runtime, nvcc_command
+from attention_autotuner_b200.autotuner.tunner import AttnTunner
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_arch_fields():
+    b = B200()
+    assert isinstance(b, Arch) and b.compute_capability == "100a"
+    assert b.smem_cap == 227 * 1024 and b.tmem_columns == 512 and b.compute_max_core == 148
+    for a in (A100(), RTX4090()):
+        for f in ("reg_cap", "smem_cap", "compute_max_core", "warp_size", "sm_partition", "transaction_size",
+                  "max_smem_usage", "bandwidth", "platform", "compute_capability", "register_per_thread"):
+            assert hasattr(a, f)
+
+
+def test_only_sm100_is_a_build_target():
+    with pytest.raises(KernelError):
+        nvcc_command(A100(), "x.cu", "x.so")
+    cmd = nvcc_command(B200(), "x.cu", "x.so")
+    assert "-gencode=arch=compute_100a,code=sm_100a" in cmd
+
+
+def test_attn_config_legacy_and_new_arguments():
+    # the reference's positional form (python/tests/test_runtime.py builds configs this way)
+    c = AttnConfig(64, 32, 256, 128, 256, 32, 1, 1, 128, 1, warps_mma1_n=1, warps_mma_n=2)
+    c.set_fuse_type("shared")
+    assert c.fuse_type == "tmem" and c.Br == 128 and c.Bc == 128 and c.q_tiles == 1
+    c2 = AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, dtype="bf16")
+    assert str(c2) == "attn_tmem_256_128_128_128_2_4_128_bf16"
+    assert c2.tmem_columns() == 512 and c2.smem_bytes() <= B200().smem_cap
+    d = json.loads(json.dumps(c2.__dict__))
+    c3 = supported_configs[d["operation"]].from_dict(d)
+    assert c3 == c2 and repr(c3) == repr(c2)
+    assert AttnConfig(128, 128, 128, 512).dv_chunk == 256 and AttnConfig(128, 128, 64, 192).dv_chunk == 64
+
+
+def _tensors(dqk, dv, dt=torch.float16):
+    q = torch.zeros(1, 1, 128, dqk, dtype=dt)
+    v = torch.zeros(1, 1, 128, dv, dtype=dt)
+    return [q, q, v, v]
+
+
+def test_attn_search_space_is_feasible():
+    arch = B200()
+    for dqk, dv in ((64, 64), (128, 128), (256, 256), (256, 512), (128, 64)):
+        t = AttnTunner(arch, _tensors(dqk, dv))
+        cfgs = t.get_tuned_configs()
+        assert cfgs, (dqk, dv)
+        for c in cfgs:
+            assert c.smem_bytes() <= arch.smem_cap and c.tmem_columns() <= 512
+            assert c.Kd == dqk and c.D == dv and dv % c.dv_chunk == 0
+        assert len({str(c) for c in cfgs}) == len(cfgs)
+        assert t.validate_kernel(t.default_config())
+    # two ping-ponging query tiles do not fit tensor memory at dv chunk 256
+    assert not AttnTunner(arch, _tensors(128, 256)).validate_kernel(AttnConfig(256, 128, 128, 256, q_tiles=2, kv_stages=2))
+
+
+def test_cache_round_trip(tmp_path, monkeypatch):
+    monkeypatch.setenv("ATTN_B200_CACHE_DIR", str(tmp_path))
+    t = AttnTunner(B200(), _tensors(128, 128, torch.bfloat16), causal=True)
+    assert t.check_cache() is None
+    cfg = AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=3, dtype="bf16")
+    with open(t._cache_file(), "w") as f:
+        json.dump(cfg.__dict__, f)
+    assert os.path.basename(t._cache_file()) == "best_config_attention_128_128_sm100a_bf16_causal.json"
+    got = t.check_cache()
+    assert got == cfg and got.kv_stages == 3
+    # tune() returns the cached config without touching a GPU
+    assert t.tune() == cfg
+    # a cache entry written for another dtype is not used
+    assert AttnTunner(B200(), _tensors(128, 128, torch.float16), causal=True).check_cache() is None
+
+
+def test_tune_without_search_returns_default(monkeypatch, tmp_path):
+    monkeypatch.setenv("ATTN_B200_CACHE_DIR", str(tmp_path))
+    t = AttnTunner(B200(), _tensors(64, 64))
+    assert t.tune(search=False) == t.default_config()
+
+
+def test_reference_import_names():
+    from attention_autotuner_b200 import compat
+    compat.install()
+    from arch import B200 as B  # noqa: F401
+    from autotuner.configs import AttnConfig as C  # noqa: F401
+    from autotuner.runtime import Runtime as R, compile_parallel  # noqa: F401
+    from autotuner.tunner import AttnTunner as T  # noqa: F401
+    from ops.attention_interface import flash_attn_func  # noqa: F401
+    from utils.misc import is_close_my  # noqa: F401
+    from utils.ref_op import attention_ref, retnet_ref  # noqa: F401
+    assert C is AttnConfig
+
+
+def test_library_exports_every_declared_symbol(lib):
+    header = open(os.path.join(ROOT, "include", "attn_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    names = re.findall(r"\b(attn_b200_\w+)\s*\(", header)
+    assert len(names) >= 6
+    for n in set(names):
+        assert hasattr(lib, n), n
+    assert lib.attn_b200_abi_version() >= 1
+    assert lib.attn_b200_last_error() is not None
+
+
+def test_argument_validation_without_gpu(lib):
+    # rejected before any CUDA call
+    rc = lib.attn_b200_fa_fwd(None, None, None, None, None, 1, 1, 128, 128, 128, 128, 0, 0.1, 0, None)
+    assert rc == 1 and b"null" in lib.attn_b200_last_error()
+    buf = ctypes.create_string_buffer(64)
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    assert lib.attn_b200_fa_fwd(p, p, p, p, None, 1, 1, 128, 128, 96, 128, 0, 0.1, 0, None) == 2   # dqk not built
+    assert lib.attn_b200_fa_fwd(p, p, p, p, None, 1, 1, 128, 128, 128, 128, 7, 0.1, 0, None) == 1  # dtype
+    assert lib.attn_b200_fa_fwd(p, p, p, p, None, 0, 1, 128, 128, 128, 128, 0, 0.1, 0, None) == 1  # B
+    assert lib.attn_b200_fa_fwd(p, p, p, p, None, 1, 1, 128, 128, 128, 128, 0, -1.0, 0, None) == 1  # scale
+
+
+def test_per_config_library_builds_and_exports_reference_symbols(tmp_path):
+    cfg = AttnConfig(128, 128, 64, 64, q_tiles=1, kv_stages=2)
+    rt = Runtime(B200(), cfg, tmp_dir=str(tmp_path))
+    assert rt.libname == str(cfg) + ".so"
+    so = ctypes.CDLL(rt.lib_path)
+    for n in ("kernel_entry", "profile", "kernel_entry_ex", "profile_ex", "last_error", "device_status"):
+        assert hasattr(so, n)
+    # second construction reuses the file
+    mtime = os.path.getmtime(rt.lib_path)
+    assert Runtime(B200(), cfg, tmp_dir=str(tmp_path)).libname == rt.libname
+    assert os.path.getmtime(rt.lib_path) == mtime
+    with pytest.raises(KernelError):
+        rt.apply([torch.zeros(1, 1, 128, 64, dtype=torch.float16)] * 4)  # CPU tensors: no CPU path
