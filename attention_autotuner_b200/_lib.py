@@ -33,6 +33,16 @@ def _declare(lib):
     lib.attn_b200_fa_fwd.argtypes = fa
     lib.attn_b200_fa_fwd_profile.restype = cf
     lib.attn_b200_fa_fwd_profile.argtypes = fa
+    rf = [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, vp, ci, vp]
+    lib.attn_b200_ret_fwd.restype = ci
+    lib.attn_b200_ret_fwd.argtypes = rf
+    lib.attn_b200_ret_fwd_profile.restype = cf
+    lib.attn_b200_ret_fwd_profile.argtypes = rf
+    rb = [vp] * 10 + [ci] * 7 + [cf, vp, ci, vp]
+    lib.attn_b200_ret_bwd.restype = ci
+    lib.attn_b200_ret_bwd.argtypes = rb
+    lib.attn_b200_ret_bwd_profile.restype = cf
+    lib.attn_b200_ret_bwd_profile.argtypes = rb
     lib.attn_b200_selftest_gemm_ss.restype = ci
     lib.attn_b200_selftest_gemm_ss.argtypes = [vp, vp, vp, ci, ci, ci, vp]
     lib.attn_b200_selftest_gemm_ts.restype = ci

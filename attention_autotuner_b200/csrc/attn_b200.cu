@@ -4,6 +4,7 @@
 // kernel headers.
 #include "../../include/attn_b200.h"
 
+#include "chain_launch.cuh"
 #include "fa_fwd_launch.cuh"
 #include "selftest.cuh"
 
@@ -53,6 +54,48 @@ int fa_fwd_common(const void* q, const void* k, const void* v, void* o, float* l
                                  : fa_fwd_dispatch<false>(a, dqk, st, profile, ms);
 }
 
+// RetNet head-dim pairs built into this library (others: per-config libraries from the tuner).
+constexpr int chunk_of(int d) { return d % 256 == 0 ? 256 : d % 128 == 0 ? 128 : 64; }
+
+template <bool BF16, bool BWD>
+int ret_dispatch(const RetArgs& a, cudaStream_t st) {
+#define AB200_RET_CASE(DQK, DV)                                                                        \
+  if (a.dqk == DQK && a.dv == DV) {                                                                    \
+    if constexpr (BWD) return ret_bwd_launch<DQK, DV, chunk_of(DV), chunk_of(DQK), BF16>(a, st);       \
+    else return ret_fwd_launch<DQK, chunk_of(DV), BF16>(a, st);                                        \
+  }
+  AB200_RET_CASE(64, 64)
+  AB200_RET_CASE(64, 128)
+  AB200_RET_CASE(128, 128)
+  AB200_RET_CASE(128, 256)
+  AB200_RET_CASE(256, 256)
+  AB200_RET_CASE(256, 512)
+#undef AB200_RET_CASE
+  return fail(kErrUnsupported, "retnet: (dqk, dv) = (%d, %d) not built into libattn_b200", a.dqk, a.dv);
+}
+
+int ret_common(bool bwd, const RetArgs& a, int dtype, void* stream, bool profile, float* ms) {
+  if (dtype != ATTN_B200_F16 && dtype != ATTN_B200_BF16) return fail(kErrInvalidArgument, "retnet: dtype %d", dtype);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  auto once = [&]() -> int {
+    if (dtype == ATTN_B200_BF16) return bwd ? ret_dispatch<true, true>(a, st) : ret_dispatch<true, false>(a, st);
+    return bwd ? ret_dispatch<false, true>(a, st) : ret_dispatch<false, false>(a, st);
+  };
+  if (!profile) return once();
+  *ms = profile_loop(once, st);
+  return *ms < 0.f ? kErrCuda : kOk;
+}
+
+RetArgs ret_args(const void* q, const void* k, const void* v, const void* mask, const float* decay, void* o, float* r,
+                 const void* dout, void* dq, void* dk, void* dv_out, int B, int H, int Lq, int Lkv, int dqk, int dv,
+                 float scale, int causal) {
+  RetArgs a{};
+  a.q = q; a.k = k; a.v = v; a.mask = mask; a.decay = decay; a.o = o; a.r = r;
+  a.dout = dout; a.dq = dq; a.dk = dk; a.dv_out = dv_out;
+  a.BH = B * H; a.H = H; a.Lq = Lq; a.Lkv = Lkv; a.dqk = dqk; a.dv = dv; a.scale = scale; a.causal = causal;
+  return a;
+}
+
 }  // namespace
 
 extern "C" {
@@ -76,6 +119,45 @@ float attn_b200_fa_fwd_profile(const void* q, const void* k, const void* v, void
                                void* stream) {
   float ms = -1.f;
   int rc = fa_fwd_common(q, k, v, o, lse, B, H, Lq, Lkv, dqk, dv, dtype, scale, causal, stream, true, &ms);
+  return rc == kOk ? ms : -1.f;
+}
+
+int attn_b200_ret_fwd(const void* q, const void* k, const void* v, const void* mask, void* o, float* r, int B, int H,
+                      int Lq, int Lkv, int dqk, int dv, int dtype, float scale, const float* decay, int causal,
+                      void* stream) {
+  if (B <= 0 || H <= 0) return fail(kErrInvalidArgument, "ret_fwd: B and H must be positive");
+  return ret_common(false, ret_args(q, k, v, mask, decay, o, r, nullptr, nullptr, nullptr, nullptr, B, H, Lq, Lkv, dqk,
+                                    dv, scale, causal), dtype, stream, false, nullptr);
+}
+
+float attn_b200_ret_fwd_profile(const void* q, const void* k, const void* v, const void* mask, void* o, float* r, int B,
+                                int H, int Lq, int Lkv, int dqk, int dv, int dtype, float scale, const float* decay,
+                                int causal, void* stream) {
+  float ms = -1.f;
+  if (B <= 0 || H <= 0) return -1.f;
+  int rc = ret_common(false, ret_args(q, k, v, mask, decay, o, r, nullptr, nullptr, nullptr, nullptr, B, H, Lq, Lkv,
+                                      dqk, dv, scale, causal), dtype, stream, true, &ms);
+  return rc == kOk ? ms : -1.f;
+}
+
+int attn_b200_ret_bwd(const void* q, const void* k, const void* v, const void* mask, const void* dout, const float* r,
+                      void* dq, void* dk, void* dv_out, float* dq_accum, int B, int H, int Lq, int Lkv, int dqk, int dv,
+                      int dtype, float scale, const float* decay, int causal, void* stream) {
+  (void)dq_accum;  // accepted for signature compatibility; the kernels need no scratch
+  if (B <= 0 || H <= 0) return fail(kErrInvalidArgument, "ret_bwd: B and H must be positive");
+  return ret_common(true, ret_args(q, k, v, mask, decay, nullptr, const_cast<float*>(r), dout, dq, dk, dv_out, B, H, Lq,
+                                   Lkv, dqk, dv, scale, causal), dtype, stream, false, nullptr);
+}
+
+float attn_b200_ret_bwd_profile(const void* q, const void* k, const void* v, const void* mask, const void* dout,
+                                const float* r, void* dq, void* dk, void* dv_out, float* dq_accum, int B, int H, int Lq,
+                                int Lkv, int dqk, int dv, int dtype, float scale, const float* decay, int causal,
+                                void* stream) {
+  (void)dq_accum;
+  float ms = -1.f;
+  if (B <= 0 || H <= 0) return -1.f;
+  int rc = ret_common(true, ret_args(q, k, v, mask, decay, nullptr, const_cast<float*>(r), dout, dq, dk, dv_out, B, H,
+                                     Lq, Lkv, dqk, dv, scale, causal), dtype, stream, true, &ms);
   return rc == kOk ? ms : -1.f;
 }
 

@@ -1,0 +1,126 @@
+// Host launchers of chain_sm100_kernel for the RetNet parallel forward and backward.
+// They play the role of the reference's generated launch shims
+// (csrc/kernels/retnet/regfuse/profile_code.py:30-80, csrc/kernels/retnet/bwd/profile_code.py:50-115).
+#pragma once
+
+#include <math.h>
+
+#include <type_traits>
+
+#include "chain_sm100.cuh"
+#include "fa_fwd_launch.cuh"  // profile_loop
+#include "host_common.cuh"
+
+namespace ab200 {
+
+struct RetArgs {
+  const void* q;     // [BH, Lq, dqk]
+  const void* k;     // [BH, Lkv, dqk]
+  const void* v;     // [BH, Lkv, dv]
+  const void* mask;  // [H, Lq, Lkv] 16-bit, or nullptr when decay is given
+  const float* decay;  // [H] gammas (device), or nullptr when mask is given
+  // forward
+  void* o;           // [BH, Lq, dv]
+  float* r;          // [BH, Lq]   written by forward, read by backward
+  // backward
+  const void* dout;  // [BH, Lq, dv]
+  void* dq;          // [BH, Lq, dqk]
+  void* dk;          // [BH, Lkv, dqk]
+  void* dv_out;      // [BH, Lkv, dv]
+  int BH, H, Lq, Lkv, dqk, dv;
+  float scale;
+  int causal;        // with a general mask: 1 = mask is lower triangular, skip the blocks above the diagonal
+};
+
+inline int ret_check_common(const RetArgs& a, const char* what) {
+  if (!a.q || !a.k || !a.v) return fail(kErrInvalidArgument, "%s: null tensor pointer", what);
+  if ((a.mask == nullptr) == (a.decay == nullptr))
+    return fail(kErrInvalidArgument, "%s: exactly one of mask / decay must be given", what);
+  if (a.BH <= 0 || a.H <= 0 || a.BH % a.H != 0 || a.Lq <= 0 || a.Lkv <= 0)
+    return fail(kErrInvalidArgument, "%s: sizes must be positive and BH a multiple of H", what);
+  if (a.BH > 65535) return fail(kErrInvalidArgument, "%s: batch*heads %d exceeds 65535", what, a.BH);
+  if (a.mask && a.Lkv % 8 != 0) return fail(kErrUnsupported, "%s: a mask tensor needs Lkv %% 8 == 0 (got %d)", what, a.Lkv);
+  if (!isfinite(a.scale) || a.scale == 0.f) return fail(kErrInvalidArgument, "%s: scale must be finite and non-zero", what);
+  if (!aligned16(a.q) || !aligned16(a.k) || !aligned16(a.v) || (a.mask && !aligned16(a.mask)))
+    return fail(kErrInvalidArgument, "%s: tensors must be 16-byte aligned", what);
+  return kOk;
+}
+
+// One launch of the chain kernel. r_len / c_len are the lengths of the row / column side; k1 and n2_total
+// the inner extents of the R/C and T tensors.
+template <class Cfg>
+int chain_launch(const void* R, int r_len, const void* C, int c_len, const void* T, int n2_total, ChainParams p, int BH,
+                 cudaStream_t stream, const char* what) {
+  CUtensorMap tr, tc, tt;
+  int rc;
+  if ((rc = make_tmap_3d(&tr, R, Cfg::BF16, Cfg::K1, r_len, BH, 64, 128))) return rc;
+  if ((rc = make_tmap_3d(&tc, C, Cfg::BF16, Cfg::K1, c_len, BH, 64, 128))) return rc;
+  if ((rc = make_tmap_3d(&tt, T, Cfg::BF16, n2_total, c_len, BH, 64, 128))) return rc;
+  auto kernel = &chain_sm100_kernel<Cfg>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+  if (e != cudaSuccess) return fail(kErrCuda, "%s: cudaFuncSetAttribute: %s", what, cudaGetErrorString(e));
+  dim3 grid((r_len + 127) / 128, BH, n2_total / Cfg::N2);
+  kernel<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tr, tc, tt, p);
+  return check_launch(what);
+}
+
+inline ChainParams ret_params(const RetArgs& a) {
+  ChainParams p{};
+  p.mask = reinterpret_cast<const uint16_t*>(a.mask);
+  p.decay = a.decay;
+  p.H = a.H;
+  p.Lq = a.Lq;
+  p.Lkv = a.Lkv;
+  p.scale = a.scale;
+  p.skip_upper = (a.decay != nullptr || a.causal) ? 1 : 0;
+  return p;
+}
+
+// Forward. DQK = head dim of q/k, DVC = columns of V per CTA (divides dv).
+template <int DQK, int DVC, bool BF16>
+int ret_fwd_launch(const RetArgs& a, cudaStream_t stream) {
+  int rc = ret_check_common(a, "ret_fwd");
+  if (rc) return rc;
+  if (!a.o || !a.r) return fail(kErrInvalidArgument, "ret_fwd: null output pointer");
+  if (a.dqk != DQK || a.dv % DVC != 0) return fail(kErrUnsupported, "ret_fwd: dqk=%d dv=%d do not match tile %d/%d", a.dqk, a.dv, DQK, DVC);
+  ChainParams p = ret_params(a);
+  p.out = a.o;
+  p.ld_out = a.dv;
+  p.r_out = a.r;
+  if (a.mask)
+    return chain_launch<ChainConfig<DQK, DVC, kChainFwd, true, BF16>>(a.q, a.Lq, a.k, a.Lkv, a.v, a.dv, p, a.BH, stream, "ret_fwd");
+  return chain_launch<ChainConfig<DQK, DVC, kChainFwd, false, BF16>>(a.q, a.Lq, a.k, a.Lkv, a.v, a.dv, p, a.BH, stream, "ret_fwd");
+}
+
+// Backward: dV, dK, dQ as three launches on the same stream. DV = full head dim of v (contraction length
+// of the dK and dQ kernels), DVC / DQC = output columns per CTA of the dV kernel / of the dK and dQ kernels.
+template <int DQK, int DV, int DVC, int DQC, bool BF16>
+int ret_bwd_launch(const RetArgs& a, cudaStream_t stream) {
+  int rc = ret_check_common(a, "ret_bwd");
+  if (rc) return rc;
+  if (!a.dout || !a.r || !a.dq || !a.dk || !a.dv_out) return fail(kErrInvalidArgument, "ret_bwd: null pointer");
+  if (a.dqk != DQK || a.dv != DV) return fail(kErrUnsupported, "ret_bwd: dqk=%d dv=%d do not match tile %d/%d", a.dqk, a.dv, DQK, DV);
+  static_assert(DV % DVC == 0 && DQK % DQC == 0, "chunking");
+  ChainParams p = ret_params(a);
+  p.r_in = a.r;
+  auto go = [&](auto general_tag) -> int {
+    constexpr bool G = decltype(general_tag)::value;
+    ChainParams pv = p;
+    pv.out = a.dv_out;
+    pv.ld_out = a.dv;
+    int r1 = chain_launch<ChainConfig<DQK, DVC, kChainRowK, G, BF16>>(a.k, a.Lkv, a.q, a.Lq, a.dout, a.dv, pv, a.BH, stream, "ret_bwd dV");
+    if (r1) return r1;
+    ChainParams pk = p;
+    pk.out = a.dk;
+    pk.ld_out = a.dqk;
+    r1 = chain_launch<ChainConfig<DV, DQC, kChainRowK, G, BF16>>(a.v, a.Lkv, a.dout, a.Lq, a.q, a.dqk, pk, a.BH, stream, "ret_bwd dK");
+    if (r1) return r1;
+    ChainParams pq = p;
+    pq.out = a.dq;
+    pq.ld_out = a.dqk;
+    return chain_launch<ChainConfig<DV, DQC, kChainRowQ, G, BF16>>(a.dout, a.Lq, a.v, a.Lkv, a.k, a.dqk, pq, a.BH, stream, "ret_bwd dQ");
+  };
+  return a.mask ? go(std::true_type{}) : go(std::false_type{});
+}
+
+}  // namespace ab200

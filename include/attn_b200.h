@@ -62,6 +62,44 @@ float attn_b200_fa_fwd_profile(const void* q, const void* k, const void* v, void
                                void* stream);
 
 /*
+ * RetNet parallel forward:  S~ = (Q K^T * scale) .* M,  r = max(sum_j |S~|, 1),  O = (S~ / r) V.
+ * Replaces python/ops/retnet_interface.py:11-33 -> Runtime.apply -> kernel_entry -> ret_fwd_regfuse /
+ * ret_fwd_smemfuse (csrc/kernels/retnet/regfuse/regfuse.h:47, csrc/kernels/retnet/smemfuse/smemfuse.h:62).
+ *   q [B,H,Lq,dqk]  k [B,H,Lkv,dqk]  v [B,H,Lkv,dv]  o [B,H,Lq,dv] (dtype)   r [B,H,Lq] fp32 (output)
+ *   The mask M is given in exactly one of two forms:
+ *     mask  != NULL, decay == NULL : the reference's general tensor [H,Lq,Lkv] (dtype), broadcast over batch;
+ *                                    needs Lkv % 8 == 0. causal != 0 declares it lower triangular
+ *                                    (M[i,j] = 0 for j > i) so that blocks above the diagonal are skipped.
+ *     mask  == NULL, decay != NULL : per-head decay, decay = device pointer to H floats gamma_h,
+ *                                    M[h,i,j] = gamma_h^(i-j) for i >= j and 0 otherwise; built in registers.
+ *   scale: the reference has none (= 1.0). (dqk, dv) in {(64,64),(64,128),(128,128),(128,256),(256,256),(256,512)}.
+ */
+int attn_b200_ret_fwd(const void* q, const void* k, const void* v, const void* mask, void* o, float* r, int B, int H,
+                      int Lq, int Lkv, int dqk, int dv, int dtype, float scale, const float* decay, int causal,
+                      void* stream);
+float attn_b200_ret_fwd_profile(const void* q, const void* k, const void* v, const void* mask, void* o, float* r, int B,
+                                int H, int Lq, int Lkv, int dqk, int dv, int dtype, float scale, const float* decay,
+                                int causal, void* stream);
+
+/*
+ * RetNet parallel backward (r is a constant, no gradient for the mask):
+ *   P = S~ / r,  dV = P^T dO,  G = ((dO V^T) / r) .* M * scale,  dK = G^T Q,  dQ = G K.
+ * Replaces python/ops/retnet_interface.py:36-55 -> kernel_entry -> ret_bwd_colblock + convert_dq
+ * (csrc/kernels/retnet/bwd/bwd_colblock.h:81, 742). Tensor order follows the reference's
+ * [q,k,v,mask,do,r,dq,dk,dv,dq_accum]; dq_accum (fp32 [B,H,Lq,dqk] in the reference) is accepted and
+ * ignored, may be NULL: every output tile is owned by one CTA, nothing is accumulated with atomics.
+ *   dout [B,H,Lq,dv]  r [B,H,Lq] (from the forward)  dq [B,H,Lq,dqk]  dk [B,H,Lkv,dqk]  dv_out [B,H,Lkv,dv]
+ * Outputs are fully overwritten.
+ */
+int attn_b200_ret_bwd(const void* q, const void* k, const void* v, const void* mask, const void* dout, const float* r,
+                      void* dq, void* dk, void* dv_out, float* dq_accum, int B, int H, int Lq, int Lkv, int dqk, int dv,
+                      int dtype, float scale, const float* decay, int causal, void* stream);
+float attn_b200_ret_bwd_profile(const void* q, const void* k, const void* v, const void* mask, const void* dout,
+                                const float* r, void* dq, void* dk, void* dv_out, float* dq_accum, int B, int H, int Lq,
+                                int Lkv, int dqk, int dv, int dtype, float scale, const float* decay, int causal,
+                                void* stream);
+
+/*
  * Building-block self tests (single CTA, used by the test-suite to pin the tcgen05 / TMA descriptors):
  *   ss: d[128,N] = a[128,K] * b[N,K]^T       K in {64,128,192,256}, N multiple of 32, N*K <= 32768
  *   ts: d[128,N] = p[128,128] * v[128,N]     N in {64,128,192,256}
