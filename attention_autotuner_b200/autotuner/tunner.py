@@ -6,7 +6,7 @@ which replace the reference's shared-memory and accumulator-register checks (tun
 import ctypes
 
 from .base_tunner import BaseTunner, CompileResult  # noqa: F401
-from .configs import AttnConfig
+from .configs import AttnConfig, RetBwdConfig, RetConfig  # noqa: F401
 from .configs.base_config import dv_chunk_for, find_best_pair, find_factor_pairs  # noqa: F401
 
 
@@ -70,3 +70,88 @@ class AttnTunner(BaseTunner):
         scale = 0.125 if self.scale is None else self.scale
         tail = [ctypes.c_float(scale), ctypes.c_int(1 if self.causal else 0), ctypes.c_void_p(0)]
         return ptrs, tail
+
+
+def _chunks(d):
+    return [c for c in (256, 128, 64) if d % c == 0]
+
+
+class _RetBase(BaseTunner):
+    def _tail(self):
+        scale = 1.0 if self.scale is None else self.scale
+        dec = ctypes.c_void_p(self.decay.data_ptr()) if self.decay is not None else ctypes.c_void_p(0)
+        return [ctypes.c_float(scale), dec, ctypes.c_int(1 if self.causal else 0), ctypes.c_void_p(0)]
+
+    def _ptrs(self, n):
+        return [ctypes.c_void_p(t.data_ptr() if t is not None else 0) for t in self.torch_array[:n]]
+
+    def _key_suffix(self) -> str:
+        return super()._key_suffix() + ("_decay" if self.decay is not None else "")
+
+    def _pairs_causal(self):
+        return self.causal or self.decay is not None
+
+
+class RetTunner(_RetBase):
+    """Forward search space: columns of V per CTA. torch_array = [q, k, v, mask, o, r] (mask may be None
+    when ``decay`` is given)."""
+
+    def __init__(self, arch, torch_array: list, *, scale=None, causal=False, decay=None):
+        super().__init__(arch, torch_array, "retnet", scale=scale, causal=causal, decay=decay)
+
+    def validate_kernel(self, config):
+        return (config.Kd % 64 == 0 and config.D % config.dv_chunk == 0 and config.dv_chunk <= 256
+                and config.smem_bytes() <= self.arch.smem_cap + 1024
+                and config.tmem_columns() <= getattr(self.arch, "tmem_columns", 512) and config.ring_slots() >= 4)
+
+    def generate_configs(self, Br: int, Bc: int, dim_qk: int, dim_v: int):
+        if Br != 128:
+            return []
+        from .configs import RetConfig
+        return [RetConfig(Br, Bc, dim_qk, dim_v, dv_chunk=c, dtype=self.dtype) for c in _chunks(dim_v)]
+
+    def default_config(self):
+        from .configs import RetConfig
+        return RetConfig(128, 128, self.problem_key["dim_qk"], self.problem_key["dim_v"], dtype=self.dtype)
+
+    def flops(self):
+        return _flops_fwd(self.torch_array, self._pairs_causal())
+
+    def _profile_args(self):
+        return self._ptrs(6), self._tail()
+
+
+class RetBwdTunner(_RetBase):
+    """Backward search space: output columns per CTA of the dV kernel and of the dK / dQ kernels.
+    torch_array = [q, k, v, mask, do, r, dq, dk, dv, dq_accum]."""
+
+    def __init__(self, arch, torch_array: list, *, scale=None, causal=False, decay=None):
+        super().__init__(arch, torch_array, "retnet_bwd", scale=scale, causal=causal, decay=decay)
+
+    def validate_kernel(self, config):
+        return (config.Kd % 64 == 0 and config.D % 64 == 0 and config.D <= 512 and config.D % config.dv_chunk == 0
+                and config.Kd % config.dq_chunk == 0 and config.smem_bytes() <= self.arch.smem_cap + 1024
+                and config.tmem_columns() <= getattr(self.arch, "tmem_columns", 512) and config.ring_slots() >= 4)
+
+    def generate_configs(self, Br: int, Bc: int, dim_qk: int, dim_v: int):
+        if Br != 128:
+            return []
+        from .configs import RetBwdConfig
+        return [RetBwdConfig(Br, Bc, dim_qk, dim_v, dv_chunk=cv, dq_chunk=cq, dtype=self.dtype)
+                for cv in _chunks(dim_v) for cq in _chunks(dim_qk)]
+
+    def default_config(self):
+        from .configs import RetBwdConfig
+        return RetBwdConfig(128, 128, self.problem_key["dim_qk"], self.problem_key["dim_v"], dtype=self.dtype)
+
+    def flops(self):
+        t = self.torch_array
+        B, H, Lq, dqk = t[0].shape
+        Lkv, dv = t[2].shape[2], t[2].shape[3]
+        pairs = Lq * Lkv
+        if self._pairs_causal():
+            pairs = sum(max(0, min(Lkv, i + 1)) for i in range(Lq))
+        return 2.0 * B * H * pairs * (3 * dqk + 2 * dv)
+
+    def _profile_args(self):
+        return self._ptrs(10), self._tail()

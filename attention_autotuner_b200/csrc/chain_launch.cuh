@@ -53,6 +53,7 @@ int chain_launch(const void* R, int r_len, const void* C, int c_len, const void*
                  cudaStream_t stream, const char* what) {
   CUtensorMap tr, tc, tt;
   int rc;
+  if ((rc = bind_device_of(R, what))) return rc;
   if ((rc = make_tmap_3d(&tr, R, Cfg::BF16, Cfg::K1, r_len, BH, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tc, C, Cfg::BF16, Cfg::K1, c_len, BH, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tt, T, Cfg::BF16, n2_total, c_len, BH, 64, 128))) return rc;

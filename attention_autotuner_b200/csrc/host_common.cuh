@@ -91,6 +91,27 @@ inline int read_device_status(int clear, int* detail) {
   return st;
 }
 
+// The tensor maps are encoded through the driver API, which needs a context current on the calling
+// thread; threads that have only ever been handed tensors (e.g. an autograd worker) may not have one yet.
+// Checks that `ptr` is device memory of the thread's current device and binds that device's primary context.
+inline int bind_device_of(const void* ptr, const char* what) {
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, ptr) != cudaSuccess) {
+    cudaError_t e = cudaGetLastError();
+    return fail(kErrCuda, "%s: cudaPointerGetAttributes: %s", what, cudaGetErrorString(e));
+  }
+  if (at.type != cudaMemoryTypeDevice && at.type != cudaMemoryTypeManaged)
+    return fail(kErrInvalidArgument, "%s: tensor pointer is not device memory", what);
+  int cur = -1;
+  cudaGetDevice(&cur);
+  if (at.type == cudaMemoryTypeDevice && cur != at.device)
+    return fail(kErrInvalidArgument, "%s: tensors live on device %d but the calling thread's current device is %d", what,
+                at.device, cur);
+  cudaError_t e = cudaFree(nullptr);  // binds the primary context to this thread if it is not yet
+  if (e != cudaSuccess) return fail(kErrCuda, "%s: context initialisation: %s", what, cudaGetErrorString(e));
+  return kOk;
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace ab200

@@ -160,6 +160,7 @@ inline int selftest_gemm_ss(const void* a, const void* b, float* d, int N, int K
     return fail(kErrInvalidArgument, "selftest_gemm_ss: unsupported N=%d K=%d", N, K);
   CUtensorMap ta, tb;
   int rc;
+  if ((rc = bind_device_of(a, "selftest_gemm_ss"))) return rc;
   if ((rc = make_tmap_3d(&ta, a, bf16 != 0, K, 128, 1, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tb, b, bf16 != 0, K, N, 1, 64, N))) return rc;
   cudaFuncSetAttribute(selftest_gemm_ss_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSelftestSmem);
@@ -173,6 +174,7 @@ inline int selftest_gemm_ts(const void* p, const void* v, float* d, int N, int b
   if (N % 64 != 0 || N < 64 || N > 256) return fail(kErrInvalidArgument, "selftest_gemm_ts: unsupported N=%d", N);
   CUtensorMap tv;
   int rc;
+  if ((rc = bind_device_of(v, "selftest_gemm_ts"))) return rc;
   if ((rc = make_tmap_3d(&tv, v, bf16 != 0, N, 128, 1, 64, 128))) return rc;
   cudaFuncSetAttribute(selftest_gemm_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSelftestSmem);
   selftest_gemm_ts_kernel<<<1, 128, kSelftestSmem, stream>>>(reinterpret_cast<const uint32_t*>(p), tv, d, N, bf16);

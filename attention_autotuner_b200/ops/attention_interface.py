@@ -45,4 +45,5 @@ class MultiHeadAttnFunc(torch.autograd.Function):
         raise NotImplementedError("attention backward is not part of this operator (nor of the reference)")
 
 
-flash_attn_func = MultiHeadAttnFunc.apply
+def flash_attn_func(q, k, v, device_type, causal=False, softmax_scale=None, return_lse=False):
+    return MultiHeadAttnFunc.apply(q, k, v, device_type, causal, softmax_scale, return_lse)

@@ -1,0 +1,72 @@
+"""``RetNetAttnFunc``: same entry point as the reference's python/ops/retnet_interface.py:57.
+
+    o = RetNetAttnFunc(q, k, v, mask, device_type, causal=False, scale=None, decay=None)
+    o.backward(do)            # dq, dk, dv; no gradient for mask, r is a constant (ref_op.py:11)
+
+q, k [B,H,L,dqk], v [B,H,Lkv,dv], mask [H,Lq,Lkv], all fp16 (bf16 also accepted). ``scale=None`` keeps the
+reference's unscaled scores. ``decay`` (tensor of H per-head gammas) replaces the mask tensor by
+M[h,i,j] = gamma_h^(i-j) (i >= j) built inside the kernel; ``mask`` may then be None. With a mask
+tensor, ``causal=True`` declares it lower triangular so the kernels skip the blocks above the diagonal
+(the reference accepts the argument and ignores it)."""
+import torch
+
+from ..arch import Arch
+from ..autotuner.runtime import Runtime
+from ..autotuner.tunner import RetBwdTunner, RetTunner
+
+
+class RetNetAttn(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, q, k, v, mask, device_type: Arch, *opts):
+        causal = bool(opts[0]) if len(opts) > 0 else False
+        scale = opts[1] if len(opts) > 1 else None
+        decay = opts[2] if len(opts) > 2 else None
+        assert q.dtype in (torch.float16, torch.bfloat16) and k.dtype == q.dtype and v.dtype == q.dtype
+        assert (mask is None) != (decay is None), "give either a mask tensor or per-head decay"
+        q, k, v = [x.contiguous() for x in [q, k, v]]
+        batch_size, nheads, seqlen_q, key_dim = q.shape
+        head_dim = v.shape[-1]
+        assert head_dim % 64 == 0 and head_dim <= 512
+        assert key_dim % 64 == 0 and key_dim <= 256
+        maskr = None
+        if mask is not None:
+            assert mask.dtype == q.dtype
+            maskr = mask.detach().contiguous()
+        decayr = None
+        if decay is not None:
+            decayr = decay.detach().to(device=q.device, dtype=torch.float32).contiguous()
+            assert decayr.numel() == nheads
+
+        o = torch.empty(batch_size, nheads, seqlen_q, head_dim, device=q.device, dtype=q.dtype)
+        r = torch.empty(batch_size, nheads, seqlen_q, device=q.device, dtype=torch.float32)
+        arr = [q, k, v, maskr, o, r]
+        cc = RetTunner(arch=device_type, torch_array=arr, scale=scale, causal=causal, decay=decayr).tune()
+        Runtime(device_type, cc).apply(arr, scale=1.0 if scale is None else scale, causal=causal, decay=decayr)
+        ctx.save_for_backward(q, k, v, maskr, r, decayr)
+        ctx.device_type = device_type
+        ctx.opts = (causal, scale)
+        ctx.n_extra = len(opts)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, mask, r, decay = ctx.saved_tensors
+        device_type = ctx.device_type
+        causal, scale = ctx.opts
+        do = do.contiguous()
+        dq = torch.empty_like(q)
+        dk = torch.empty_like(k)
+        dv = torch.empty_like(v)
+        arr = [q, k, v, mask, do, r, dq, dk, dv, None]  # no dq_accum scratch: each output tile has one owner
+        cc = RetBwdTunner(arch=device_type, torch_array=arr, scale=scale, causal=causal, decay=decay).tune()
+        Runtime(device_type, cc).apply(arr, scale=1.0 if scale is None else scale, causal=causal, decay=decay)
+        return (dq, dk, dv, None, None) + (None,) * ctx.n_extra
+
+
+def RetNetAttnFunc(q, k, v, mask, device_type, causal=False, scale=None, decay=None):
+    if scale is None and decay is None:
+        if causal is False:
+            return RetNetAttn.apply(q, k, v, mask, device_type)
+        return RetNetAttn.apply(q, k, v, mask, device_type, causal)
+    return RetNetAttn.apply(q, k, v, mask, device_type, causal, scale, decay)

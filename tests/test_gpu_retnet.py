@@ -1,0 +1,208 @@
+"""RetNet parallel forward + backward on the GPU, through the C ABI and the Python operator, against the
+CPU fp32 oracle (r detached in the backward, exactly as the reference's retnet_ref, python/utils/ref_op.py:11)
+and the golden vectors produced by the reference's own formula + torch.autograd.
+
+Tolerance: fp16 max-abs <= 2e-3, mean-abs <= 2e-4 against the fp32 oracle, scaled by max(1, peak |ref|) for
+tensors whose magnitude exceeds 1 (gradients sum hundreds of terms; fp16's spacing at 8 is already 7.8e-3)."""
+import ctypes
+
+import pytest
+import torch
+
+from attention_autotuner_b200 import _lib
+from attention_autotuner_b200.arch import B200
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def P(t):
+    return ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+
+
+def run_fwd_bwd(lib, q, k, v, do, mask=None, decay=None, scale=1.0, causal=0):
+    B, H, Lq, dqk = q.shape
+    Lkv, dv = v.shape[2], v.shape[3]
+    code = 0 if q.dtype == torch.float16 else 1
+    qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    md = mask.cuda() if mask is not None else None
+    dd = decay.float().cuda() if decay is not None else None
+    nan = float("nan")
+    o = torch.full((B, H, Lq, dv), nan, device="cuda", dtype=q.dtype)
+    r = torch.full((B, H, Lq), nan, device="cuda")
+    _lib.check(lib.attn_b200_ret_fwd(P(qd), P(kd), P(vd), P(md), P(o), P(r), B, H, Lq, Lkv, dqk, dv, code, scale,
+                                     P(dd), causal, None))
+    dq = torch.full((B, H, Lq, dqk), nan, device="cuda", dtype=q.dtype)
+    dk = torch.full((B, H, Lkv, dqk), nan, device="cuda", dtype=q.dtype)
+    dvo = torch.full((B, H, Lkv, dv), nan, device="cuda", dtype=q.dtype)
+    _lib.check(lib.attn_b200_ret_bwd(P(qd), P(kd), P(vd), P(md), P(dod), P(r), P(dq), P(dk), P(dvo), None, B, H, Lq,
+                                     Lkv, dqk, dv, code, scale, P(dd), causal, None))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    return o.cpu(), r.cpu(), dq.cpu(), dk.cpu(), dvo.cpu()
+
+
+def rand_case(seed, B, H, Lq, Lkv, dqk, dv, dt=torch.float16, mscale=0.5):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, H, Lq, dqk, generator=g).to(dt)
+    k = torch.randn(B, H, Lkv, dqk, generator=g).to(dt)
+    v = torch.randn(B, H, Lkv, dv, generator=g).to(dt)
+    do = torch.randn(B, H, Lq, dv, generator=g).to(dt)
+    mask = (mscale * torch.randn(H, Lq, Lkv, generator=g)).to(dt)
+    return q, k, v, do, mask
+
+
+def check_all(got, q, k, v, do, maskf, scale, dtype_name="fp16"):
+    o, r, dq, dk, dv = got
+    oref, rref = oracle.retnet_fwd(q, k, v, maskf, scale)
+    assert oracle.within(oracle.error_stats(o, oref), dtype_name, scale_by_peak=True)
+    assert ((r - rref).abs() / rref).max().item() < 1e-4
+    gq, gk, gv = oracle.retnet_bwd(q, k, v, maskf, do, scale)
+    for name, a, b in (("dq", dq, gq), ("dk", dk, gk), ("dv", dv, gv)):
+        st = oracle.error_stats(a, b)
+        assert oracle.within(st, dtype_name, scale_by_peak=True), (name, st)
+
+
+@pytest.mark.parametrize("name", ["ret_randmask", "ret_demo_scaling", "ret_decay"])
+def test_golden_vectors_of_the_reference_formula(lib, golden, name):
+    g = golden(name)
+    q, k, v, mask, do = (torch.from_numpy(g[x]) for x in ("q", "k", "v", "mask", "do"))
+    o, r, dq, dk, dv = run_fwd_bwd(lib, q, k, v, do, mask=mask)   # reference semantics: no scale, mask tensor
+    for key, got in (("o", o), ("dq", dq), ("dk", dk), ("dv", dv)):
+        st = oracle.error_stats(got, torch.from_numpy(g[key]))
+        assert oracle.within(st, "fp16", scale_by_peak=True), (key, st)
+
+
+@pytest.mark.parametrize("dqk,dv", [(64, 64), (64, 128), (128, 128), (128, 256), (256, 256), (256, 512)])
+def test_general_mask_head_dims(lib, dqk, dv):
+    q, k, v, do, mask = rand_case(dqk + dv, 1, 2, 384, 384, dqk, dv)
+    scale = 0.5 * dqk ** -0.5
+    check_all(run_fwd_bwd(lib, q, k, v, do, mask=mask, scale=scale), q, k, v, do, mask.float(), scale)
+
+
+@pytest.mark.parametrize("dqk,dv", [(64, 64), (128, 256), (256, 512)])
+def test_decay_head_dims(lib, dqk, dv):
+    H, L = 4, 640
+    q, k, v, do, _ = rand_case(7, 1, H, L, L, dqk, dv)
+    gam = oracle.decay_gammas(H)
+    scale = dqk ** -0.5
+    got = run_fwd_bwd(lib, q, k, v, do, decay=gam, scale=scale)
+    check_all(got, q, k, v, do, oracle.decay_mask(H, L, L, gam), scale)
+
+
+@pytest.mark.parametrize("Lq,Lkv", [(1, 8), (128, 128), (200, 328), (129, 136), (640, 256), (256, 640)])
+def test_ragged_lengths_general_mask(lib, Lq, Lkv):
+    q, k, v, do, mask = rand_case(Lq * 7 + Lkv, 2, 2, Lq, Lkv, 64, 128)
+    check_all(run_fwd_bwd(lib, q, k, v, do, mask=mask, scale=0.2), q, k, v, do, mask.float(), 0.2)
+
+
+@pytest.mark.parametrize("Lq,Lkv", [(1, 1), (100, 100), (333, 200), (200, 333), (512, 512)])
+def test_ragged_lengths_decay(lib, Lq, Lkv):
+    H = 3
+    q, k, v, do, _ = rand_case(Lq + Lkv, 1, H, Lq, Lkv, 64, 128)
+    gam = oracle.decay_gammas(H)
+    got = run_fwd_bwd(lib, q, k, v, do, decay=gam, scale=0.125)
+    check_all(got, q, k, v, do, oracle.decay_mask(H, Lq, Lkv, gam), 0.125)
+
+
+def test_lower_triangular_hint_equals_full_evaluation(lib):
+    """causal=1 with a mask tensor only skips blocks whose mask entries are zero: same bits as causal=0."""
+    q, k, v, do, mask = rand_case(5, 1, 2, 512, 512, 128, 128)
+    mask = torch.tril(mask)
+    a = run_fwd_bwd(lib, q, k, v, do, mask=mask, scale=0.1, causal=0)
+    b = run_fwd_bwd(lib, q, k, v, do, mask=mask, scale=0.1, causal=1)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+    check_all(b, q, k, v, do, mask.float(), 0.1)
+
+
+def test_decay_path_matches_materialised_mask_path(lib):
+    """gamma close to one: the fp16-rounded mask tensor and the in-register decay agree to fp16 accuracy."""
+    H, L = 2, 384
+    q, k, v, do, _ = rand_case(9, 1, H, L, L, 128, 128)
+    gam = torch.tensor([0.999, 0.9995], dtype=torch.float64)
+    m = oracle.decay_mask(H, L, L, gam)
+    a = run_fwd_bwd(lib, q, k, v, do, decay=gam, scale=0.09)
+    check_all(a, q, k, v, do, m, 0.09)
+    b = run_fwd_bwd(lib, q, k, v, do, mask=m.half(), scale=0.09)
+    check_all(b, q, k, v, do, m.half().float(), 0.09)
+
+
+def test_bf16(lib):
+    H, L = 2, 512
+    q, k, v, do, mask = rand_case(11, 1, H, L, L, 128, 128, dt=torch.bfloat16)
+    check_all(run_fwd_bwd(lib, q, k, v, do, mask=mask, scale=0.1), q, k, v, do, mask.float(), 0.1, "bf16")
+
+
+def test_unnormalised_scores_above_fp16_range_saturate_not_overflow(lib):
+    """Deferred normalisation keeps S~ unnormalised in fp16; huge scores must not turn into inf/NaN."""
+    q, k, v, do, mask = rand_case(13, 1, 1, 256, 256, 64, 64)
+    o, r, *_ = run_fwd_bwd(lib, (q.float() * 40).half(), (k.float() * 40).half(), v, do, mask=mask, scale=1.0)
+    assert torch.isfinite(o.float()).all() and torch.isfinite(r).all()
+
+
+def test_linearity_and_determinism_at_config3_size(lib):
+    """BASELINE config 3/4 at full size (B=8 H=8 L=2048 dqk=256 dv=512 fp16, scale 1/16, decay mask): two runs
+    bit-identical (no atomics anywhere), O linear in V, sampled slices against the oracle."""
+    c = oracle.CONFIGS["C4"]
+    B, H, L, dqk, dv = c["B"], c["H"], c["Lq"], c["dqk"], c["dv"]
+    gam = oracle.decay_gammas(H)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    mk = lambda *s: torch.randn(*s, device="cuda", generator=g).half()
+    q, k, v, do = mk(B, H, L, dqk), mk(B, H, L, dqk), mk(B, H, L, dv), mk(B, H, L, dv)
+    dd = gam.float().cuda()
+    outs = []
+    for rep in range(2):
+        o = torch.empty(B, H, L, dv, device="cuda", dtype=torch.float16)
+        r = torch.empty(B, H, L, device="cuda")
+        dq, dk, dvo = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        _lib.check(lib.attn_b200_ret_fwd(P(q), P(k), P(v), None, P(o), P(r), B, H, L, L, dqk, dv, 0, 1 / 16, P(dd), 0, None))
+        _lib.check(lib.attn_b200_ret_bwd(P(q), P(k), P(v), None, P(do), P(r), P(dq), P(dk), P(dvo), None, B, H, L, L,
+                                         dqk, dv, 0, 1 / 16, P(dd), 0, None))
+        torch.cuda.synchronize()
+        outs.append((o, r, dq, dk, dvo))
+    for x, y in zip(*outs):
+        assert torch.equal(x, y)
+    assert _lib.device_status() == 0
+    o, r, dq, dk, dvo = outs[0]
+    mfull = oracle.decay_mask(H, L, L, gam)
+    for (b, h) in ((0, 0), (B - 1, H - 1)):
+        sl = lambda t: t[b, h].cpu()
+        check_all((sl(o), sl(r), sl(dq), sl(dk), sl(dvo)), sl(q), sl(k), sl(v), sl(do), mfull[h], 1 / 16)
+
+
+def test_python_operator_forward_backward(lib):
+    from attention_autotuner_b200.ops.retnet_interface import RetNetAttnFunc
+    q, k, v, do, mask = rand_case(17, 2, 2, 256, 256, 64, 64)
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    o = RetNetAttnFunc(qd, kd, vd, mask.cuda(), B200())          # reference call form
+    o.backward(do.cuda())
+    got = (o.detach().cpu(), None, qd.grad.cpu(), kd.grad.cpu(), vd.grad.cpu())
+    oref, _ = oracle.retnet_fwd(q, k, v, mask.float())
+    assert oracle.within(oracle.error_stats(got[0], oref), "fp16", scale_by_peak=True)
+    for a, b in zip(got[2:], oracle.retnet_bwd_autograd(q, k, v, mask.float(), do)):
+        assert oracle.within(oracle.error_stats(a, b), "fp16", scale_by_peak=True)
+    # decay form, scaled, through the same operator
+    H = 2
+    gam = oracle.decay_gammas(H)
+    qd2, kd2, vd2 = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    o2 = RetNetAttnFunc(qd2, kd2, vd2, None, B200(), True, scale=0.125, decay=gam)
+    o2.backward(do.cuda())
+    m = oracle.decay_mask(H, 256, 256, gam)
+    oref2, _ = oracle.retnet_fwd(q, k, v, m, 0.125)
+    assert oracle.within(oracle.error_stats(o2.detach().cpu(), oref2), "fp16", scale_by_peak=True)
+    for a, b in zip((qd2.grad, kd2.grad, vd2.grad), oracle.retnet_bwd(q, k, v, m, do, 0.125)):
+        assert oracle.within(oracle.error_stats(a.cpu(), b), "fp16", scale_by_peak=True)
+
+
+def test_argument_errors(lib):
+    x = torch.zeros(1, 1, 128, 64, device="cuda", dtype=torch.float16)
+    r = torch.zeros(1, 1, 128, device="cuda")
+    m = torch.zeros(1, 128, 128, device="cuda", dtype=torch.float16)
+    d = torch.ones(1, device="cuda")
+    args = lambda mask, dec, dqk=64: (P(x), P(x), P(x), P(mask), P(x), P(r), 1, 1, 128, 128, dqk, 64, 0, 1.0, P(dec), 0, None)
+    assert lib.attn_b200_ret_fwd(*args(None, None)) == 1        # neither mask nor decay
+    assert lib.attn_b200_ret_fwd(*args(m, d)) == 1              # both
+    assert lib.attn_b200_ret_fwd(*args(m, None, 96)) == 2       # head dim not built
+    assert lib.attn_b200_ret_fwd(*args(m, None)) == 0
+    torch.cuda.synchronize()
