@@ -59,6 +59,19 @@ struct FaFwdConfig {
   static_assert(SMEM_BYTES <= 232448, "shared memory overflow");
 };
 
+// Optional event trace (compile with -DAB200_TRACE): CTA (0,0,0) records clock64() at the hand-off points of
+// softmax warp 0 of each tile and of the MMA thread, for the first kTraceIters KV blocks.
+#ifdef AB200_TRACE
+constexpr int kTraceIters = 16;
+__device__ long long g_trace[5][kTraceIters][8];
+#define AB200_TR(who, j, ev)                                                                       \
+  do {                                                                                             \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < kTraceIters) g_trace[who][j][ev] = clock64(); \
+  } while (0)
+#else
+#define AB200_TR(who, j, ev) do {} while (0)
+#endif
+
 // Barrier tags reported with a timeout status.
 enum FaTag : int { kTagQ = 1, kTagKvFull = 2, kTagKvEmpty = 3, kTagSFull = 4, kTagPFull = 5, kTagODone = 6 };
 
@@ -84,7 +97,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(o_done + NQ);
   CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 1);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // provably warp-uniform
   const int lane = threadIdx.x & 31;
   constexpr int kMmaWarp = 4 * NQ;
   constexpr int kTmaWarp = 4 * NQ + 1;
@@ -143,7 +156,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   // With three warpgroups the launch-time register split (168/thread) starves the softmax threads, which
   // hold a full 128-column score row; each role branch moves registers accordingly (setmaxnreg).
   if (warp >= 4 * NQ) {
-    if constexpr (NQ == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
+    if constexpr (NQ == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -162,8 +175,10 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int t = 0; t < nitems && ok; ++t) {
         const int slot = t % NSTAGE;
         const int use = t / NSTAGE;
+        AB200_TR(3, t >> 1, (t & 1) * 4 + 0);
         if (use > 0) ok = mbar_wait(&kv_empty[slot], (use - 1) & 1, ab, kTagKvEmpty);
         if (!ok) break;
+        AB200_TR(3, t >> 1, (t & 1) * 4 + 1);
         uint8_t* dst = sKV + slot * Cfg::KV_SLOT_BYTES;
         const int j = t >> 1;
         if ((t & 1) == 0) {
@@ -192,7 +207,9 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs this role converged (waits included); one elected lane issues each batch of
+    // tcgen05.mma + commits, so that addresses and descriptors stay warp-uniform.
+    {
       constexpr uint32_t idesc_qk = umma_idesc(BM, BN, BF16, false, false);
       constexpr uint32_t idesc_pv = umma_idesc(BM, DV, BF16, false, true);
       bool ok = true;
@@ -202,49 +219,60 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         while (ok && static_cast<int>(full_waited) <= t) {
           const int slot = full_waited % NSTAGE;
           const int use = full_waited / NSTAGE;
-          ok = mbar_wait(&kv_full[slot], use & 1, ab, kTagKvFull);
+          if (lane == 0) AB200_TR(4, full_waited >> 1, (full_waited & 1) * 4 + 0);
+          ok = mbar_wait_warp(&kv_full[slot], use & 1, ab, kTagKvFull);
+          if (lane == 0) AB200_TR(4, full_waited >> 1, (full_waited & 1) * 4 + 1);
           ++full_waited;
         }
         return ok;
       };
-      auto issue_s = [&](int s, int j) {
-        // S_s = Q_s K_j^T
+      const uint32_t q_addr = smem_u32(sQ);
+      const uint32_t kv_addr = smem_u32(sKV);
+      // S_s = Q_s K_j^T, then optionally release the K slot
+      auto issue_s = [&](int s, int j, bool release) {
         const int slot = (2 * j) % NSTAGE;
-        const uint32_t qa = smem_u32(sQ + s * Cfg::Q_TILE_BYTES);
-        const uint32_t ka = smem_u32(sKV + slot * Cfg::KV_SLOT_BYTES);
+        const uint32_t qa = q_addr + s * Cfg::Q_TILE_BYTES;
+        const uint32_t ka = kv_addr + slot * Cfg::KV_SLOT_BYTES;
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < DQK / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * (BM * 128) + (ks & 3) * 32;
-          umma_ss(tmem_base + s * 128, umma_smem_desc(qa + off, 16, 1024), umma_smem_desc(ka + off, 16, 1024),
-                  idesc_qk, ks > 0 ? 1u : 0u);
+          for (int ks = 0; ks < DQK / 16; ++ks) {
+            const uint32_t off = (ks >> 2) * (BM * 128) + (ks & 3) * 32;
+            umma_ss(tmem_base + s * 128, umma_smem_desc(qa + off, 16, 1024), umma_smem_desc(ka + off, 16, 1024),
+                    idesc_qk, ks > 0 ? 1u : 0u);
+          }
+          tc_commit(&s_full[s]);
+          if (release) tc_commit(&kv_empty[slot]);
         }
-        tc_commit(&s_full[s]);
+        __syncwarp();
       };
-      auto issue_pv = [&](int s, int j) {
-        // O_s += P_s V_j
+      // O_s += P_s V_j, then optionally release the V slot
+      auto issue_pv = [&](int s, int j, bool release) {
         const int slot = (2 * j + 1) % NSTAGE;
-        const uint32_t va = smem_u32(sKV + slot * Cfg::KV_SLOT_BYTES);
+        const uint32_t va = kv_addr + slot * Cfg::KV_SLOT_BYTES;
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < BN / 16; ++ks) {
-          umma_ts(tmem_base + NQ * 128 + s * DV, tmem_base + s * 128 + ks * 8,
-                  umma_smem_desc(va + ks * 2048, BN * 128, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < BN / 16; ++ks) {
+            umma_ts(tmem_base + NQ * 128 + s * DV, tmem_base + s * 128 + ks * 8,
+                    umma_smem_desc(va + ks * 2048, BN * 128, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          }
+          tc_commit(&o_done[s]);
+          if (release) tc_commit(&kv_empty[slot]);
         }
-        tc_commit(&o_done[s]);
+        __syncwarp();
       };
-      int first_user = -1, last_user = -1;
+      int last_user = -1;
       // prologue: S_s(0)
 #pragma unroll
       for (int s = 0; s < NQ; ++s)
-        if (nblk[s] > 0) { if (first_user < 0) first_user = s; last_user = s; }
+        if (nblk[s] > 0) last_user = s;
       if (nmax > 0) {
 #pragma unroll
         for (int s = 0; s < NQ; ++s) {
           if (nblk[s] > 0 && ok) {
-            ok = mbar_wait(&q_full[s], 0, ab, kTagQ);
+            ok = mbar_wait_warp(&q_full[s], 0, ab, kTagQ);
             if (ok && wait_item(0)) {
               tc_fence_after();
-              issue_s(s, 0);
-              if (s == last_user) tc_commit(&kv_empty[0 % NSTAGE]);
+              issue_s(s, 0, s == last_user);
             }
           }
         }
@@ -261,17 +289,19 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int s = 0; s < NQ; ++s) {
           if (nblk[s] > j && ok) {
             if (!wait_item(2 * j + 1)) break;
-            ok = mbar_wait(&p_full[s], j & 1, ab, kTagPFull);
+            if (lane == 0) AB200_TR(2, j, s * 4 + 0);
+            ok = mbar_wait_warp(&p_full[s], j & 1, ab, kTagPFull);
             if (!ok) break;
+            if (lane == 0) AB200_TR(2, j, s * 4 + 1);
             tc_fence_after();
-            issue_pv(s, j);
-            if (s == last_v) tc_commit(&kv_empty[(2 * j + 1) % NSTAGE]);
+            issue_pv(s, j, s == last_v);
+            if (lane == 0) AB200_TR(2, j, s * 4 + 2);
           }
           if (nblk[s] > j + 1 && ok) {
             if (!wait_item(2 * j + 2)) break;
             tc_fence_after();
-            issue_s(s, j + 1);
-            if (s == last_k) tc_commit(&kv_empty[(2 * j + 2) % NSTAGE]);
+            issue_s(s, j + 1, s == last_k);
+            if (lane == 0) AB200_TR(2, j, s * 4 + 3);
           }
         }
       }
@@ -279,7 +309,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
-    if constexpr (NQ == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    if constexpr (NQ == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     const int s = warp >> 2;                    // query tile of this warpgroup
     const int row_in_tile = threadIdx.x & 127;  // TMEM lane
     const int row = m_base + s * BM + row_in_tile;
@@ -294,8 +324,10 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     bool ok = true;
 
     for (int j = 0; j < n_my; ++j) {
+      if (threadIdx.x % 128 == 0) AB200_TR(s, j, 0);
       ok = mbar_wait_warp(&s_full[s], j & 1, ab, kTagSFull);
       if (!ok) break;
+      if (threadIdx.x % 128 == 0) AB200_TR(s, j, 1);
       tc_fence_after();
       float sv[BN];
       {
@@ -306,6 +338,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld32(tS + 96, r + 96);
         tc_wait_ld();
       }
+      if (threadIdx.x % 128 == 0) AB200_TR(s, j, 2);
       const int n0 = j * BN;
       // masking: keys past Lkv (ragged tail) and, under causal, keys j > i + shift
       const bool tail_blk = (n0 + BN > p.Lkv);
@@ -320,9 +353,19 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int c = 0; c < BN; ++c)
           if (c >= limit) sv[c] = -INFINITY;
       }
-      float m_blk = sv[0];
+      // row maximum: four independent chains of three-input maxima
+      float mA = sv[0], mB = sv[1], mC = sv[2], mD = sv[3];
 #pragma unroll
-      for (int c = 1; c < BN; ++c) m_blk = fmaxf(m_blk, sv[c]);
+      for (int c = 4; c < BN - 4; c += 8) {
+        mA = fmax3(mA, sv[c], sv[c + 1]);
+        mB = fmax3(mB, sv[c + 2], sv[c + 3]);
+        mC = fmax3(mC, sv[c + 4], sv[c + 5]);
+        mD = fmax3(mD, sv[c + 6], sv[c + 7]);
+      }
+      mA = fmax3(mA, sv[BN - 4], sv[BN - 3]);
+      mB = fmax3(mB, sv[BN - 2], sv[BN - 1]);
+      const float m_blk = fmaxf(fmaxf(mA, mB), fmaxf(mC, mD));
+      if (threadIdx.x % 128 == 0) AB200_TR(s, j, 3);
 
       // Lazy rescale: keep the old reference unless the maximum grew by more than 2^8 in the exp2 domain.
       bool need = (j == 0) || ((m_blk - m_ref) * p.scale_log2 > 8.0f);
@@ -351,23 +394,35 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
       const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref * p.scale_log2;
-      float psum = 0.f;
+      // P = exp2(S * scale_log2 - m * scale_log2): packed FMA, MUFU ex2, four packed partial sums
+      const uint64_t sl2 = f2_pack(p.scale_log2, p.scale_log2);
+      const uint64_t nm2 = f2_pack(neg_m, neg_m);
+      uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t pk[BN / 4];
 #pragma unroll
         for (int c = 0; c < BN / 2; c += 2) {
-          const float e0 = ex2_approx(fmaf(sv[h * (BN / 2) + c], p.scale_log2, neg_m));
-          const float e1 = ex2_approx(fmaf(sv[h * (BN / 2) + c + 1], p.scale_log2, neg_m));
-          psum += e0 + e1;
+          const int cc = h * (BN / 2) + c;
+          float x0, x1;
+          f2_unpack(ffma2(f2_pack(sv[cc], sv[cc + 1]), sl2, nm2), x0, x1);
+          const float e0 = ex2_approx(x0);
+          const float e1 = ex2_approx(x1);
+          acc[(c >> 1) & 3] = fadd2(acc[(c >> 1) & 3], f2_pack(e0, e1));
           pk[c >> 1] = pack2<BF16>(e0, e1);
         }
         tmem_st32(tS + h * (BN / 4), pk);
       }
-      l_sum += psum;
+      {
+        float a0, a1;
+        f2_unpack(fadd2(fadd2(acc[0], acc[1]), fadd2(acc[2], acc[3])), a0, a1);
+        l_sum += a0 + a1;
+      }
+      if (threadIdx.x % 128 == 0) AB200_TR(s, j, 4);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full[s]);
+      if (threadIdx.x % 128 == 0) AB200_TR(s, j, 5);
     }
 
     // epilogue: O / l  ->  global, lse

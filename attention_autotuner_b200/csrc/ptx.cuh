@@ -70,6 +70,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// One lane of a converged warp (elect.sync). Keeping the surrounding control flow warp-uniform and
+// electing only around the instruction lets the compiler hold descriptors in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t"
+      ".reg .b32 rx;\n\t"
+      ".reg .pred px;\n\t"
+      "elect.sync rx|px, %1;\n\t"
+      "@px mov.s32 %0, 1;\n\t"
+      "}\n"
+      : "+r"(pred)
+      : "r"(0xFFFFFFFFu));
+  return pred != 0;
+}
+
 // Per-CTA abort word in shared memory: once any role gives up, every other bounded wait of the CTA
 // returns false quickly so that all roles fall through to the common tail (TMEM free, exit).
 struct CtaAbort {
@@ -83,6 +99,9 @@ __device__ __noinline__ void report_timeout(CtaAbort* ab, int tag) {
   }
 }
 
+// Once any CTA of any launch has reported a failure the status word stays non-zero until the host clears
+// it; every later wait gives up at once, so a broken pipeline costs about one wait limit in total rather
+// than one per CTA.
 // Bounded wait for one thread (the single-thread producer / MMA roles). Returns false on expiry or
 // when another role of the CTA already aborted.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, CtaAbort* ab, int tag) {
@@ -91,7 +110,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, CtaAbo
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 0u) {
-      if (ab->flag) return false;
+      if (ab->flag || *reinterpret_cast<volatile int*>(&g_device_status) != 0) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
       if (now - t0 > AB200_WAIT_LIMIT_NS) {
@@ -121,7 +140,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, C
     if ((it & 63u) == 63u) {
       int give_up = 0;
       if ((threadIdx.x & 31) == 0) {
-        if (ab->flag) {
+        if (ab->flag || *reinterpret_cast<volatile int*>(&g_device_status) != 0) {
           give_up = 1;
         } else {
           uint64_t now = globaltimer_ns();
@@ -310,6 +329,37 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Three-input maximum and packed two-wide fp32 arithmetic (sm_100): halve the instruction count of the
+// element-wise phases.
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 // Packs two fp32 into one 32-bit register of two 16-bit floats: low half = lo, high half = hi.
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
