@@ -6,11 +6,11 @@ CSRC_DIR = os.path.normpath(os.path.join(os.path.dirname(__file__), "..", "..", 
 
 
 def _chain_smem(k1: int) -> int:
-    """Shared memory of one chain-kernel CTA: the resident 128 x k1 tile plus the largest ring of 16 KB
-    boxes that fits (capped at 12), as ChainConfig in csrc/chain_sm100.cuh computes it."""
+    """Shared memory of one chain-kernel CTA: the resident 128 x k1 tile plus the largest ring of 32 KB
+    items that fits (capped at 6), as ChainConfig in csrc/chain_sm100.cuh computes it."""
     r_bytes = 128 * k1 * 2
-    nslot = min(12, (232448 - 1024 - 2048 - r_bytes) // 16384)
-    return 1024 + r_bytes + nslot * 16384 + 2048, nslot
+    nslot = min(6, (232448 - 1024 - 2048 - r_bytes) // 32768)
+    return 1024 + r_bytes + nslot * 32768 + 2048, nslot
 
 
 class RetConfig(BaseConfig):

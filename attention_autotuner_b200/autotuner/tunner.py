@@ -102,7 +102,7 @@ class RetTunner(_RetBase):
     def validate_kernel(self, config):
         return (config.Kd % 64 == 0 and config.D % config.dv_chunk == 0 and config.dv_chunk <= 256
                 and config.smem_bytes() <= self.arch.smem_cap + 1024
-                and config.tmem_columns() <= getattr(self.arch, "tmem_columns", 512) and config.ring_slots() >= 4)
+                and config.tmem_columns() <= getattr(self.arch, "tmem_columns", 512) and config.ring_slots() >= 3)
 
     def generate_configs(self, Br: int, Bc: int, dim_qk: int, dim_v: int):
         if Br != 128:
@@ -131,7 +131,7 @@ class RetBwdTunner(_RetBase):
     def validate_kernel(self, config):
         return (config.Kd % 64 == 0 and config.D % 64 == 0 and config.D <= 512 and config.D % config.dv_chunk == 0
                 and config.Kd % config.dq_chunk == 0 and config.smem_bytes() <= self.arch.smem_cap + 1024
-                and config.tmem_columns() <= getattr(self.arch, "tmem_columns", 512) and config.ring_slots() >= 4)
+                and config.tmem_columns() <= getattr(self.arch, "tmem_columns", 512) and config.ring_slots() >= 3)
 
     def generate_configs(self, Br: int, Bc: int, dim_qk: int, dim_v: int):
         if Br != 128:

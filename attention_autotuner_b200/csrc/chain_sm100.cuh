@@ -26,10 +26,10 @@
 //     the thread that owns the row / column) or a per-head decay gamma, M[i,j] = gamma^(i-j) for i>=j,
 //     computed in registers, with the all-zero blocks above the diagonal skipped.
 //
-// Roles: warps 0-3 element-wise warpgroup (thread t owns TMEM lane t), warp 4 lane 0 issues every
-// tcgen05.mma, warp 5 lane 0 is the TMA producer. Z is double buffered in tensor memory so that GEMM1
-// of block t+1 runs while the warpgroup works on block t. All streamed operands travel through one ring
-// of 16 KB boxes (128 rows x 64 columns, 128-byte swizzle).
+// Roles: warps 0-3 element-wise warpgroup (thread t owns TMEM lane t), warp 4 issues every tcgen05.mma
+// (converged warp, one elected lane), warp 5 lane 0 is the TMA producer. Z is double buffered in tensor
+// memory so that GEMM1 of block t+1 runs while the warpgroup works on block t. All streamed operands
+// travel through one ring of 32 KB items (two boxes of 128 rows x 64 columns, 128-byte swizzle).
 #pragma once
 
 #include "ptx.cuh"
@@ -60,18 +60,35 @@ struct ChainConfig {
   static constexpr int K1B = K1 / 64;  // boxes per C tile
   static constexpr int N2B = N2 / 64;  // boxes per T tile
   static constexpr int BOX_BYTES = 128 * 128;
+  // A ring item is up to two boxes (32 KB): 128 columns of K for GEMM1, 128 columns of N for GEMM2, so that
+  // every MMA is 128x128x16 (64 tensor-pipe cycles against ~49 cycles of issue cost per instruction).
+  static constexpr int ITEM_BYTES = 2 * BOX_BYTES;
+  static constexpr int CI = (K1B + 1) / 2;  // items per C tile
+  static constexpr int TI = (N2B + 1) / 2;  // items per T tile
   static constexpr int R_BYTES = 128 * K1 * 2;
   static constexpr int AUX_BYTES = 2048;  // column-factor tables (2 x 128 floats), barriers, flags
-  static constexpr int NSLOT_FIT = (232448 - 1024 - AUX_BYTES - R_BYTES) / BOX_BYTES;
-  static constexpr int NSLOT = NSLOT_FIT > 12 ? 12 : NSLOT_FIT;
-  static constexpr int SMEM_BYTES = 1024 + R_BYTES + NSLOT * BOX_BYTES + AUX_BYTES;
-  static constexpr int NTHREADS = 192;
+  static constexpr int NSLOT_FIT = (232448 - 1024 - AUX_BYTES - R_BYTES) / ITEM_BYTES;
+  static constexpr int NSLOT = NSLOT_FIT > 6 ? 6 : NSLOT_FIT;
+  static constexpr int SMEM_BYTES = 1024 + R_BYTES + NSLOT * ITEM_BYTES + AUX_BYTES;
+  static constexpr int NTHREADS = 192;  // element-wise warpgroup + MMA issuer warp + TMA producer warp
   static constexpr int TMEM_COLS = 512;  // 2 x 128 (Z) + N2
   static_assert(K1 % 64 == 0 && K1 >= 64 && K1 <= 512, "K1");
   static_assert(N2 % 64 == 0 && N2 >= 64 && N2 <= 256, "N2");
-  static_assert(NSLOT >= 4, "ring too small");
-  static_assert(2 * NSLOT + 6 <= 64, "barrier area");
+  static_assert(NSLOT >= 3, "ring too small");
+  static_assert(2 * NSLOT + 8 <= 64, "barrier area");
 };
+
+// Optional event trace (compile with -DAB200_TRACE), see fa_fwd_sm100.cuh: CTA (0,0,0) only.
+#ifdef AB200_TRACE
+constexpr int kChainTraceIters = 16;
+__device__ long long g_chain_trace[2][kChainTraceIters][8];
+#define AB200_CTR(who, j, ev)                                                                            \
+  do {                                                                                                   \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < kChainTraceIters) g_chain_trace[who][j][ev] = clock64(); \
+  } while (0)
+#else
+#define AB200_CTR(who, j, ev) do {} while (0)
+#endif
 
 enum ChainTag : int { kCtR = 11, kCtSlotFull = 12, kCtSlotEmpty = 13, kCtZFull = 14, kCtWFull = 15, kCtAccDone = 16 };
 
@@ -80,6 +97,7 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
 chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constant__ CUtensorMap tmC,
                    const __grid_constant__ CUtensorMap tmT, const ChainParams p) {
   constexpr int K1B = Cfg::K1B, N2B = Cfg::N2B, N2 = Cfg::N2, NSLOT = Cfg::NSLOT, MODE = Cfg::MODE;
+  constexpr int CI = Cfg::CI, TI = Cfg::TI, ITEM = Cfg::ITEM_BYTES;
   constexpr bool GENERAL = Cfg::GENERAL, BF16 = Cfg::BF16;
   constexpr int BOX = Cfg::BOX_BYTES;
 
@@ -87,7 +105,7 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sR = smem;
   uint8_t* sRing = smem + Cfg::R_BYTES;
-  float* cf = reinterpret_cast<float*>(sRing + NSLOT * BOX);  // [2][128] column factors
+  float* cf = reinterpret_cast<float*>(sRing + NSLOT * ITEM);  // [2][128] column factors
   uint64_t* bars = reinterpret_cast<uint64_t*>(cf + 256);
   uint64_t* r_full = bars;                    // [1]
   uint64_t* slot_full = bars + 1;             // [NSLOT]
@@ -98,7 +116,7 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 1);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // provably warp-uniform
   const int lane = threadIdx.x & 31;
   const int bh = blockIdx.y;
   const int n_off = blockIdx.z * N2;
@@ -160,23 +178,27 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
       mbar_expect_tx(r_full, Cfg::R_BYTES);
 #pragma unroll
       for (int c = 0; c < K1B; ++c) tma_load_3d(sR + c * BOX, &tmR, r_full, c * 64, row0, bh);
-      int bi = 0;  // boxes issued
-      auto put = [&](const CUtensorMap* map, int x, int y) {
+      int bi = 0;  // items issued
+      // one item = boxes [2i, 2i+2) of the tile (the last item of an odd tile holds one box)
+      auto put = [&](const CUtensorMap* map, int x0, int nboxes, int y) {
         const int slot = bi % NSLOT;
         const int use = bi / NSLOT;
         if (use > 0) ok = mbar_wait(&slot_empty[slot], (use - 1) & 1, ab, kCtSlotEmpty);
         if (!ok) return;
-        mbar_expect_tx(&slot_full[slot], BOX);
-        tma_load_3d(sRing + slot * BOX, map, &slot_full[slot], x, y, bh);
+        mbar_expect_tx(&slot_full[slot], nboxes * BOX);
+        for (int b = 0; b < nboxes; ++b)
+          tma_load_3d(sRing + slot * ITEM + b * BOX, map, &slot_full[slot], x0 + b * 64, y, bh);
         ++bi;
       };
       // consumption order: C_0, then for t >= 1: C_t, T_{t-1}; finally T_{n-1}
       for (int t = 0; t <= n_iter && ok; ++t) {
         if (t < n_iter) {
-          for (int c = 0; c < K1B && ok; ++c) put(&tmC, c * 64, (t_start + t) * 128);
+          for (int i = 0; i < CI && ok; ++i)
+            put(&tmC, i * 128, (K1B - 2 * i) >= 2 ? 2 : 1, (t_start + t) * 128);
         }
         if (t >= 1) {
-          for (int c = 0; c < N2B && ok; ++c) put(&tmT, n_off + c * 64, (t_start + t - 1) * 128);
+          for (int i = 0; i < TI && ok; ++i)
+            put(&tmT, n_off + i * 128, (N2B - 2 * i) >= 2 ? 2 : 1, (t_start + t - 1) * 128);
         }
       }
       if (!ok) {
@@ -187,60 +209,83 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
     }
   } else if (warp == 4) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && n_iter > 0) {
+    // The whole warp runs converged (waits included) and one elected lane issues, so that addresses and
+    // descriptors stay warp-uniform. (Splitting GEMM1 and GEMM2 over two issuing warps was measured and
+    // does not pay: the kernel is bound by the L2->SM operand stream, not by issue slots.)
+    if (n_iter > 0) {
       constexpr uint32_t idesc_z = umma_idesc(128, 128, BF16, false, false);
-      constexpr uint32_t idesc_acc = umma_idesc(128, 64, BF16, false, true);
+      constexpr uint32_t idesc_acc2 = umma_idesc(128, 128, BF16, false, true);  // two boxes: N = 128
+      constexpr uint32_t idesc_acc1 = umma_idesc(128, 64, BF16, false, true);   // one box:   N = 64
       bool ok = true;
-      int bi = 0;  // boxes consumed
+      int bi = 0;  // items consumed
       auto take = [&](int& slot) -> uint32_t {
         slot = bi % NSLOT;
-        ok = mbar_wait(&slot_full[slot], (bi / NSLOT) & 1, ab, kCtSlotFull);
+        ok = mbar_wait_warp(&slot_full[slot], (bi / NSLOT) & 1, ab, kCtSlotFull);
         ++bi;
-        return smem_u32(sRing + slot * BOX);
+        return smem_u32(sRing) + slot * ITEM;
       };
       const uint32_t r_addr = smem_u32(sR);
       auto issue_z = [&](int t) {
         const uint32_t tz = tZ0 + (t & 1) * 128;
-        for (int c = 0; c < K1B && ok; ++c) {
+#pragma unroll
+        for (int i = 0; i < CI; ++i) {
           int slot;
           const uint32_t a = take(slot);
           if (!ok) return;
+          const int nb = (K1B - 2 * i) >= 2 ? 2 : 1;
+          if (elect_one()) {
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_ss(tz, umma_smem_desc(r_addr + c * BOX + ks * 32, 16, 1024), umma_smem_desc(a + ks * 32, 16, 1024),
-                    idesc_z, (c > 0 || ks > 0) ? 1u : 0u);
-          tc_commit(&slot_empty[slot]);
+            for (int b = 0; b < 2; ++b) {
+              if (b < nb) {
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+                  umma_ss(tz, umma_smem_desc(r_addr + (2 * i + b) * BOX + ks * 32, 16, 1024),
+                          umma_smem_desc(a + b * BOX + ks * 32, 16, 1024), idesc_z, (i > 0 || b > 0 || ks > 0) ? 1u : 0u);
+              }
+            }
+            tc_commit(&slot_empty[slot]);
+            if (i == CI - 1) tc_commit(&z_full[t & 1]);
+          }
+          __syncwarp();
         }
-        tc_commit(&z_full[t & 1]);
       };
       auto issue_acc = [&](int t) {
-        ok = mbar_wait(&w_full[t & 1], (t >> 1) & 1, ab, kCtWFull);
+        ok = mbar_wait_warp(&w_full[t & 1], (t >> 1) & 1, ab, kCtWFull);
         if (!ok) return;
+        if (lane == 0) AB200_CTR(1, t, 2);
         tc_fence_after();
         const uint32_t tw = tZ0 + (t & 1) * 128;
-        for (int c = 0; c < N2B && ok; ++c) {
+#pragma unroll
+        for (int i = 0; i < TI; ++i) {
           int slot;
           const uint32_t a = take(slot);
           if (!ok) return;
+          const bool two = (N2B - 2 * i) >= 2;
+          if (elect_one()) {
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            umma_ts(tACC + c * 64, tw + ks * 8, umma_smem_desc(a + ks * 2048, BOX, 1024), idesc_acc,
-                    (t > 0 || ks > 0) ? 1u : 0u);
-          tc_commit(&slot_empty[slot]);
+            for (int ks = 0; ks < 8; ++ks)
+              umma_ts(tACC + i * 128, tw + ks * 8, umma_smem_desc(a + ks * 2048, BOX, 1024), two ? idesc_acc2 : idesc_acc1,
+                      (t > 0 || ks > 0) ? 1u : 0u);
+            tc_commit(&slot_empty[slot]);
+            if (i == TI - 1 && t == n_iter - 1) tc_commit(acc_done);
+          }
+          __syncwarp();
         }
       };
-      ok = mbar_wait(r_full, 0, ab, kCtR);
+      ok = mbar_wait_warp(r_full, 0, ab, kCtR);
       if (ok) {
         tc_fence_after();
         issue_z(0);
         for (int t = 0; t < n_iter && ok; ++t) {
+          if (lane == 0) AB200_CTR(1, t, 0);
           if (t + 1 < n_iter) issue_z(t + 1);
+          if (lane == 0) AB200_CTR(1, t, 1);
           if (ok) issue_acc(t);
+          if (lane == 0) AB200_CTR(1, t, 3);
         }
-        if (ok) tc_commit(acc_done);
       }
     }
-  } else {
+  } else if (warp < 4) {
     // ------------------------------------------------------------------ element-wise warpgroup
     const int tid = threadIdx.x;  // 0..127 = TMEM lane = row of the resident tile
     const int grow = row0 + tid;  // global row index on the row side
@@ -279,8 +324,10 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
       const bool straddle = decay_mode && (MODE == kChainRowK ? (col0 < row0 + 127) : (col0 + 127 > row0));
       const int dlim = grow - col0;
 
+      if (tid == 0) AB200_CTR(0, t, 0);
       ok = mbar_wait_warp(&z_full[t & 1], (t >> 1) & 1, ab, kCtZFull);
       if (!ok) break;
+      if (tid == 0) AB200_CTR(0, t, 1);
       tc_fence_after();
       const uint32_t tz = tmem_addr(tZ0 + (t & 1) * 128, lane_base, 0);
 #pragma unroll
@@ -353,9 +400,11 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
         }
         tmem_st16(tz + qd * 16, pk);
       }
+      if (tid == 0) AB200_CTR(0, t, 2);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&w_full[t & 1]);
+      if (tid == 0) AB200_CTR(0, t, 3);
     }
 
     // ---- epilogue

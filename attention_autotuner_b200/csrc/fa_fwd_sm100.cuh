@@ -35,8 +35,12 @@ struct FaFwdParams {
   float scale_log2;    // scale * log2(e)
 };
 
-template <int DQK_, int DV_, int NQ_, int NSTAGE_, bool BF16_>
+template <int DQK_, int DV_, int NQ_, int NSTAGE_, bool BF16_, int EXP_EMU_ = 0>
 struct FaFwdConfig {
+  // of every 8 pairs of scores, how many take the FMA-pipe exponential instead of MUFU ex2 (0..8). Measured
+  // on B200 at d = 128: every non-zero setting is slower (the softmax warps are issue/latency bound, not
+  // MUFU bound), so the default is 0; kept as a tuning knob.
+  static constexpr int EXP_EMU = EXP_EMU_;
   static constexpr int DQK = DQK_;        // head dim of Q/K, multiple of 64
   static constexpr int DV = DV_;          // head dim of V/O, multiple of 64
   static constexpr int NQ = NQ_;          // query tiles per CTA
@@ -404,10 +408,16 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
         for (int c = 0; c < BN / 2; c += 2) {
           const int cc = h * (BN / 2) + c;
-          float x0, x1;
-          f2_unpack(ffma2(f2_pack(sv[cc], sv[cc + 1]), sl2, nm2), x0, x1);
-          const float e0 = ex2_approx(x0);
-          const float e1 = ex2_approx(x1);
+          const uint64_t x2 = ffma2(f2_pack(sv[cc], sv[cc + 1]), sl2, nm2);
+          float e0, e1;
+          if (((c >> 1) & 7) < Cfg::EXP_EMU) {
+            exp2_poly2(x2, e0, e1);  // FMA-pipe exponential for EXP_EMU of every 8 pairs
+          } else {
+            float x0, x1;
+            f2_unpack(x2, x0, x1);
+            e0 = ex2_approx(x0);
+            e1 = ex2_approx(x1);
+          }
           acc[(c >> 1) & 3] = fadd2(acc[(c >> 1) & 3], f2_pack(e0, e1));
           pk[c >> 1] = pack2<BF16>(e0, e1);
         }

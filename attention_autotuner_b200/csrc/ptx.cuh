@@ -360,6 +360,34 @@ __device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
   return r;
 }
 
+__device__ __forceinline__ uint64_t fsub2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// 2^x for a packed pair on the FMA pipes (no MUFU): floor(x) by a round-down magic-number add, a cubic
+// for 2^frac on [0,1) (max relative error 8.7e-5, below the rounding step of a 16-bit result), and the
+// integer part added to the exponent field. x is clamped at -126 (results below 2^-126 are not needed).
+__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& e0, float& e1) {
+  float x0, x1;
+  f2_unpack(x2, x0, x1);
+  x0 = fmaxf(x0, -126.0f);
+  x1 = fmaxf(x1, -126.0f);
+  const uint64_t xc = f2_pack(x0, x1);
+  const uint64_t magic = f2_pack(12582912.0f, 12582912.0f);  // 1.5 * 2^23
+  uint64_t t;
+  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(t) : "l"(xc), "l"(magic));
+  const uint64_t fr = fsub2(xc, fsub2(t, magic));
+  uint64_t pl = ffma2(fr, f2_pack(0.07705805f, 0.07705805f), f2_pack(0.22764558f, 0.22764558f));
+  pl = ffma2(pl, fr, f2_pack(0.69512289f, 0.69512289f));
+  pl = ffma2(pl, fr, f2_pack(1.0f, 1.0f));
+  float p0, p1, t0, t1;
+  f2_unpack(pl, p0, p1);
+  f2_unpack(t, t0, t1);
+  e0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
+  e1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
+}
+
 // Packs two fp32 into one 32-bit register of two 16-bit floats: low half = lo, high half = hi.
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
