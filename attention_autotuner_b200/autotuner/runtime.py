@@ -26,6 +26,25 @@ PKG_DIR = os.path.normpath(os.path.join(os.path.dirname(__file__), ".."))
 CSRC_DIR = os.path.join(PKG_DIR, "csrc")
 DEFAULT_JIT_DIR = os.environ.get("ATTN_B200_JIT_DIR", os.path.join(PKG_DIR, "_jit"))
 
+_source_tag_cache = None
+
+
+def source_tag() -> str:
+    """Short hash of the kernel sources; part of every per-config library name, so that libraries built
+    from older sources are never picked up."""
+    global _source_tag_cache
+    if _source_tag_cache is None:
+        import hashlib
+        h = hashlib.sha1()
+        for root, _dirs, files in sorted(os.walk(CSRC_DIR)):
+            for name in sorted(files):
+                if name.endswith((".cuh", ".cu", ".h", ".py")):
+                    with open(os.path.join(root, name), "rb") as f:
+                        h.update(name.encode() + b"\0" + f.read())
+        _source_tag_cache = h.hexdigest()[:10]
+    return _source_tag_cache
+
+
 _handles: dict = {}
 _handles_lock = threading.Lock()
 
@@ -85,8 +104,8 @@ class Runtime:
         """Writes <str(config)>.cu and builds <str(config)>.so in tmp_dir (skipped if it exists).
         Returns the library file name, or None if nvcc failed or timed out."""
         config = self.config
-        filename = str(config) + ".cu"
-        lib_name = str(config) + ".so"
+        filename = str(config) + "_" + source_tag() + ".cu"
+        lib_name = str(config) + "_" + source_tag() + ".so"
         lib_path = os.path.join(self.tmp_dir, lib_name)
         if os.path.exists(lib_path):
             return lib_name

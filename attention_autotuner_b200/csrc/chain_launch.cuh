@@ -60,7 +60,7 @@ int chain_launch(const void* R, int r_len, const void* C, int c_len, const void*
   auto kernel = &chain_sm100_kernel<Cfg>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
   if (e != cudaSuccess) return fail(kErrCuda, "%s: cudaFuncSetAttribute: %s", what, cudaGetErrorString(e));
-  dim3 grid((r_len + 127) / 128, BH, n2_total / Cfg::N2);
+  dim3 grid((r_len + 127) / 128, n2_total / Cfg::N2, BH);
   kernel<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tr, tc, tt, p);
   return check_launch(what);
 }

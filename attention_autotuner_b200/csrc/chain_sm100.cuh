@@ -118,8 +118,10 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // provably warp-uniform
   const int lane = threadIdx.x & 31;
-  const int bh = blockIdx.y;
-  const int n_off = blockIdx.z * N2;
+  // grid: x = row block, y = column chunk, z = (batch, head): the chunks of one slice run side by side and
+  // share their streamed operands in L2
+  const int bh = blockIdx.z;
+  const int n_off = blockIdx.y * N2;
 
   // row side = the resident tile; column side = the streamed blocks
   const int rows_len = (MODE == kChainRowK) ? p.Lkv : p.Lq;

@@ -51,7 +51,7 @@ int fa_fwd_launch(const FaFwdArgs& a, cudaStream_t stream) {
   auto kernel = &fa_fwd_sm100_kernel<Cfg>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
   if (e != cudaSuccess) return fail(kErrCuda, "fa_fwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  dim3 grid((a.Lq + Cfg::BM * Cfg::NQ - 1) / (Cfg::BM * Cfg::NQ), a.BH, a.dv / Cfg::DV);
+  dim3 grid((a.Lq + Cfg::BM * Cfg::NQ - 1) / (Cfg::BM * Cfg::NQ), a.dv / Cfg::DV, a.BH);
   kernel<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
   return check_launch("fa_fwd launch");
 }

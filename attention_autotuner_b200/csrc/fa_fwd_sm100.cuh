@@ -108,8 +108,9 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   // Heaviest (latest) query blocks first under a causal mask.
   const int qblk = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
-  const int bh = blockIdx.y;
-  const int dv_off = blockIdx.z * DV;
+  // grid: x = query block, y = V-column chunk, z = (batch, head)
+  const int bh = blockIdx.z;
+  const int dv_off = blockIdx.y * DV;
   const int m_base = qblk * (BM * NQ);
 
   // KV blocks needed per query tile.
