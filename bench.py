@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Headline benchmark: flash-attention forward TFLOPS on B200 (and the CPU reference beside it).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload C2|C2causal|C2bf16|C1|C5sq|C5dec]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload C2|C2causal|C2bf16|C1|C3|C4|C5sq|C5dec]
     python bench.py --impl reference ...          # the reference's CPU formula on the host cores
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
@@ -32,6 +32,9 @@ os.environ.setdefault("ATTN_B200_AUTOTUNE", "0")  # never search for tile config
 
 WORKLOADS = {
     # name: (B, H, Lq, Lkv, dqk, dv, dtype, causal)
+    # C3 / C4: RetNet parallel forward / forward+backward with the per-head decay mask (FLOPs count the i >= j pairs)
+    "C3": (8, 8, 2048, 2048, 256, 512, "fp16", True),
+    "C4": (8, 8, 2048, 2048, 256, 512, "fp16", True),
     "C1": (2, 4, 512, 512, 64, 64, "fp16", False),
     "C2": (8, 16, 4096, 4096, 128, 128, "fp16", False),
     "C2causal": (8, 16, 4096, 4096, 128, 128, "fp16", True),
@@ -43,6 +46,21 @@ WORKLOADS = {
 }
 METRIC = "attn fwd TFLOPS at B=8,H=16,L=4096,d=128 fp16"
 UNIT = "TFLOP/s"
+RETNET = {"C3": "fwd", "C4": "fwd+bwd"}
+
+
+def metric_name(workload):
+    if workload in RETNET:
+        return "RetNet %s TFLOPS at B=8,H=8,L=2048,dqk=256,dv=512 fp16 (decay mask, unmasked pairs counted)" % RETNET[workload]
+    return METRIC
+
+
+def flops_of(workload):
+    B, H, Lq, Lkv, dqk, dv, dtype, causal = WORKLOADS[workload]
+    f = flops_fwd(B, H, Lq, Lkv, dqk, dv, causal)
+    if workload == "C4":
+        f += f / (dqk + dv) * (3 * dqk + 2 * dv)
+    return f
 
 
 def flops_fwd(B, H, Lq, Lkv, dqk, dv, causal):
@@ -59,8 +77,8 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as f:
             d = json.load(f)
-        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
-    return 1590.0, 6650.0, "fallback"
+        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured", float(d.get("bf16_tflops_sustained", 0.0))
+    return 1590.0, 6650.0, "fallback", 1400.0
 
 
 class ClockSampler:
@@ -76,7 +94,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -121,17 +139,29 @@ def cpu_reference_run(workload, steps, warmup, budget_s=20.0):
     torch.set_num_threads(os.cpu_count() or 1)
     dt = oracle.torch_dtype(dtype)
     scale = dqk ** -0.5
-    q, k, v = oracle.slice_inputs(workload, 0, 0, H, Lq, Lkv, dqk, dv, dt)
+    ret = RETNET.get(workload)
+    masks = oracle.decay_mask(H, Lq, Lkv) if ret else None
+
+    def run_slice(i, sl):
+        if not ret:
+            oracle.attention_fwd(sl[0], sl[1], sl[2], scale, causal)
+        elif ret == "fwd":
+            oracle.retnet_fwd(sl[0], sl[1], sl[2], masks[i % H], scale)
+        else:  # the reference's own way: autograd through the formula with r detached (ref_op.py:8-13)
+            oracle.retnet_bwd_autograd(sl[0], sl[1], sl[2], masks[i % H], sl[3], scale)
+
+    first = oracle.slice_inputs(workload, 0, 0, H, Lq, Lkv, dqk, dv, dt, with_do=bool(ret))
     t0 = time.perf_counter()
-    oracle.attention_fwd(q, k, v, scale, causal)
+    run_slice(0, first)
     per_slice = time.perf_counter() - t0
     n_slices = max(1, min(B * H, int(budget_s / max(per_slice, 1e-6) / max(1, steps + warmup))))
-    slices = [oracle.slice_inputs(workload, (i // H) % B, i % H, H, Lq, Lkv, dqk, dv, dt) for i in range(n_slices)]
-    fl = flops_fwd(1, n_slices, Lq, Lkv, dqk, dv, causal)
+    slices = [oracle.slice_inputs(workload, (i // H) % B, i % H, H, Lq, Lkv, dqk, dv, dt, with_do=bool(ret))
+              for i in range(n_slices)]
+    fl = flops_of(workload) * n_slices / (B * H)
 
     def one_step():
-        for (a, b, c) in slices:
-            oracle.attention_fwd(a, b, c, scale, causal)
+        for i, sl in enumerate(slices):
+            run_slice(i, sl)
     for _ in range(warmup):
         one_step()
     t0 = time.perf_counter()
@@ -146,7 +176,7 @@ def cpu_reference_run(workload, steps, warmup, budget_s=20.0):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="C2", choices=sorted(WORKLOADS))
@@ -159,7 +189,8 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     B, H, Lq, Lkv, dqk, dv, dtype, causal = WORKLOADS[args.workload]
-    config = {"workload": f"{args.workload}: flash-attention forward B={B} H={H} Lq={Lq} Lkv={Lkv} dqk={dqk} dv={dv} "
+    opname = "RetNet parallel " + RETNET[args.workload] + " (decay mask)" if args.workload in RETNET else "flash-attention forward"
+    config = {"workload": f"{args.workload}: {opname} B={B} H={H} Lq={Lq} Lkv={Lkv} dqk={dqk} dv={dv} "
                           f"{dtype} causal={causal} scale=1/sqrt(dqk), per GPU",
               "slices_per_gpu": B * H, "sharding": "(batch, head) slices, no collective",
               "l2": "inputs (4 tensors, %d MB) exceed the 126 MB L2" % (2 * B * H * (Lq * (dqk + dv) + Lkv * (dqk + dv)) // 2**20)}
@@ -168,7 +199,7 @@ def main():
         if rank != 0:
             return
         r = cpu_reference_run(args.workload, max(1, args.steps), args.warmup)
-        line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
+        line = {"impl": "reference", "metric": metric_name(args.workload), "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
                 "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
@@ -200,11 +231,28 @@ def main():
     v = torch.randn(B, H, Lkv, dv, device=dev, generator=g).to(tdt)
     o = torch.empty(B, H, Lq, dv, device=dev, dtype=tdt)
     stream = torch.cuda.current_stream(dev)
-    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    P = lambda t: ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+    ret = RETNET.get(args.workload)
+    launches_per_step = 1
+    if ret:
+        from attention_autotuner_b200.ops.retnet_interface import RetNetAttnFunc
+        gam = (1.0 - torch.pow(2.0, -5.0 - torch.arange(H, dtype=torch.float64))).float().to(dev)
+        r = torch.empty(B, H, Lq, device=dev, dtype=torch.float32)
+        do = torch.randn(B, H, Lq, dv, device=dev, generator=g).to(tdt)
+        dq, dk, dvo = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        launches_per_step = 1 if ret == "fwd" else 4
+        sp = ctypes.c_void_p(stream.cuda_stream)
 
-    def step():
-        _lib.check(lib.attn_b200_fa_fwd(P(q), P(k), P(v), P(o), None, B, H, Lq, Lkv, dqk, dv, code, scale,
-                                        int(causal), ctypes.c_void_p(stream.cuda_stream)))
+        def step():
+            _lib.check(lib.attn_b200_ret_fwd(P(q), P(k), P(v), None, P(o), P(r), B, H, Lq, Lkv, dqk, dv, code, scale,
+                                             P(gam), 1, sp))
+            if ret != "fwd":
+                _lib.check(lib.attn_b200_ret_bwd(P(q), P(k), P(v), None, P(do), P(r), P(dq), P(dk), P(dvo), None, B, H,
+                                                 Lq, Lkv, dqk, dv, code, scale, P(gam), 1, sp))
+    else:
+        def step():
+            _lib.check(lib.attn_b200_fa_fwd(P(q), P(k), P(v), P(o), None, B, H, Lq, Lkv, dqk, dv, code, scale,
+                                            int(causal), ctypes.c_void_p(stream.cuda_stream)))
 
     def barrier():
         if world > 1:
@@ -239,12 +287,25 @@ def main():
         oh = torch.empty(o.shape, dtype=tdt).pin_memory()
         e2e_steps = max(3, min(args.steps, 10))
 
+        if ret == "fwd+bwd":
+            doh = do.cpu().pin_memory()
+            gh = [torch.empty(t.shape, dtype=tdt).pin_memory() for t in (q, k, v)]
+
         def e2e_step():
             qd = qh.to(dev, non_blocking=True)
             kd = kh.to(dev, non_blocking=True)
             vd = vh.to(dev, non_blocking=True)
-            od = flash_attn_func(qd, kd, vd, arch, causal, scale)
-            oh.copy_(od, non_blocking=True)
+            if not ret:
+                od = flash_attn_func(qd, kd, vd, arch, causal, scale)
+            else:
+                if ret == "fwd+bwd":
+                    qd.requires_grad_(True), kd.requires_grad_(True), vd.requires_grad_(True)
+                od = RetNetAttnFunc(qd, kd, vd, None, arch, True, scale=scale, decay=gam)
+                if ret == "fwd+bwd":
+                    od.backward(doh.to(dev, non_blocking=True))
+                    for dst, src in zip(gh, (qd.grad, kd.grad, vd.grad)):
+                        dst.copy_(src, non_blocking=True)
+            oh.copy_(od.detach(), non_blocking=True)
         for _ in range(2):
             e2e_step()
         torch.cuda.synchronize()
@@ -266,26 +327,31 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_step, e2e_ms = t[0].item(), (t[1].item() if e2e_ms is not None else None)
 
-    fl_gpu = flops_fwd(B, H, Lq, Lkv, dqk, dv, causal)
+    fl_gpu = flops_of(args.workload)
     if rank == 0:
-        peak_tf, peak_hbm, peak_src = measured_peaks()
+        peak_tf, peak_hbm, peak_src, peak_sus = measured_peaks()
         achieved = fl_gpu / (ms_step * 1e-3) / 1e12
         line = {
-            "metric": METRIC, "value": world * achieved, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "metric": metric_name(args.workload), "value": world * achieved, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": dtype, "data": "synthetic", "config": config,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
                          "frac": achieved / peak_tf, "traffic": None,
-                         "peak_source": f"{peak_src} (cuBLAS bf16 burst)",
-                         "flops_per_launch": fl_gpu, "kernel": "fa_fwd_sm100_kernel"},
-            "clocks": clocks, "gpu_launches": args.steps + (2 + e2e_steps if e2e_ms is not None else 0),
+                         "peak_source": f"{peak_src} (cuBLAS bf16 burst; the timed region is a burst of a few tens of ms)",
+                         "peak_sustained": peak_sus, "frac_of_sustained": (achieved / peak_sus if peak_sus else None),
+                         "flops_per_step": fl_gpu, "launches_per_step": launches_per_step,
+                         "kernel": "chain_sm100_kernel" if ret else "fa_fwd_sm100_kernel"},
+            "clocks": clocks,
+            "gpu_launches": launches_per_step * (args.steps + (2 + e2e_steps if e2e_ms is not None else 0)),
         }
         if e2e_ms is not None:
             es = q.element_size()
+            h2d = (q.numel() + k.numel() + v.numel()) * es + (o.numel() * es if ret == "fwd+bwd" else 0)
+            d2h = o.numel() * es + ((q.numel() + k.numel() + v.numel()) * es if ret == "fwd+bwd" else 0)
             line["e2e"] = {"value": world * fl_gpu / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
-                           "h2d_bytes_per_step": (q.numel() + k.numel() + v.numel()) * es,
-                           "d2h_bytes_per_step": o.numel() * es, "ms_per_step": e2e_ms,
-                           "api": "attention_autotuner_b200.ops.attention_interface.flash_attn_func"}
+                           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                           "api": "attention_autotuner_b200.ops." + ("retnet_interface.RetNetAttnFunc" if ret
+                                                                      else "attention_interface.flash_attn_func")}
         if not args.no_cpu_baseline and world == 1:
             r = cpu_reference_run(args.workload, 2, 1, budget_s=15.0)
             line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
