@@ -46,6 +46,23 @@ inline int ret_check_common(const RetArgs& a, const char* what) {
   return kOk;
 }
 
+// CTAs of the persistent grid: one per SM (a CTA uses all of shared and tensor memory), reduced to the largest
+// count coprime to `period` (row blocks x column chunks of one slice), so that the round-robin assignment hands
+// every CTA the same mix of light and heavy row blocks.
+inline int persistent_grid(int total_items, int period) {
+  static int sms = [] {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      n = 148;
+    return n > 0 ? n : 148;
+  }();
+  if (total_items <= sms) return total_items;
+  auto gcd = [](int a, int b) { while (b) { int t = a % b; a = b; b = t; } return a; };
+  for (int g = sms; g > sms / 2; --g)
+    if (gcd(g, period) == 1) return g;
+  return sms;
+}
+
 // One launch of the chain kernel. r_len / c_len are the lengths of the row / column side; k1 and n2_total
 // the inner extents of the R/C and T tensors.
 template <class Cfg>
@@ -60,8 +77,12 @@ int chain_launch(const void* R, int r_len, const void* C, int c_len, const void*
   auto kernel = &chain_sm100_kernel<Cfg>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
   if (e != cudaSuccess) return fail(kErrCuda, "%s: cudaFuncSetAttribute: %s", what, cudaGetErrorString(e));
-  dim3 grid((r_len + 127) / 128, n2_total / Cfg::N2, BH);
-  kernel<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tr, tc, tt, p);
+  p.nrb = (r_len + 127) / 128;
+  p.ny = n2_total / Cfg::N2;
+  const long long total = static_cast<long long>(p.nrb) * p.ny * BH;
+  if (total > 0x7fffffffLL) return fail(kErrInvalidArgument, "%s: too many tiles", what);
+  p.total_items = static_cast<int>(total);
+  kernel<<<persistent_grid(p.total_items, p.nrb * p.ny), Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tr, tc, tt, p);
   return check_launch(what);
 }
 

@@ -48,6 +48,15 @@ struct ChainParams {
   int H, Lq, Lkv;
   float scale;
   int skip_upper;        // 1: blocks strictly above the diagonal are all zero and are skipped
+  // work list of the persistent grid: item w = (bh * ny + chunk) * nrb + row-block index
+  int nrb;               // 128-row blocks on the row side
+  int ny;                // column chunks of the output (n2_total / N2)
+  int total_items;       // nrb * ny * BH
+};
+
+// One unit of work of the persistent chain kernel: a 128-row tile x one output-column chunk of one slice.
+struct ChainItem {
+  int bh, n_off, row0, t_start, n_iter;
 };
 
 template <int K1_, int N2_, int MODE_, bool GENERAL_, bool BF16_>
@@ -75,12 +84,12 @@ struct ChainConfig {
   static_assert(K1 % 64 == 0 && K1 >= 64 && K1 <= 512, "K1");
   static_assert(N2 % 64 == 0 && N2 >= 64 && N2 <= 256, "N2");
   static_assert(NSLOT >= 3, "ring too small");
-  static_assert(2 * NSLOT + 8 <= 64, "barrier area");
+  static_assert(2 * NSLOT + 10 <= 64, "barrier area");
 };
 
 // Optional event trace (compile with -DAB200_TRACE), see fa_fwd_sm100.cuh: CTA (0,0,0) only.
 #ifdef AB200_TRACE
-constexpr int kChainTraceIters = 16;
+constexpr int kChainTraceIters = 48;
 __device__ long long g_chain_trace[2][kChainTraceIters][8];
 #define AB200_CTR(who, j, ev)                                                                            \
   do {                                                                                                   \
@@ -90,7 +99,9 @@ __device__ long long g_chain_trace[2][kChainTraceIters][8];
 #define AB200_CTR(who, j, ev) do {} while (0)
 #endif
 
-enum ChainTag : int { kCtR = 11, kCtSlotFull = 12, kCtSlotEmpty = 13, kCtZFull = 14, kCtWFull = 15, kCtAccDone = 16 };
+enum ChainTag : int {
+  kCtR = 11, kCtSlotFull = 12, kCtSlotEmpty = 13, kCtZFull = 14, kCtWFull = 15, kCtAccDone = 16, kCtAccFree = 17, kCtRFree = 18
+};
 
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
@@ -112,36 +123,46 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
   uint64_t* slot_empty = slot_full + NSLOT;   // [NSLOT]
   uint64_t* z_full = slot_empty + NSLOT;      // [2]
   uint64_t* w_full = z_full + 2;              // [2]
-  uint64_t* acc_done = w_full + 2;            // [1]
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+  uint64_t* acc_done = w_full + 2;            // [1] GEMM2 of an item complete        (MMA -> element-wise)
+  uint64_t* acc_free = acc_done + 1;          // [1] accumulator drained by the epilogue (element-wise -> MMA)
+  uint64_t* r_free = acc_free + 1;            // [1] GEMM1 of an item complete: R may be overwritten (MMA -> TMA)
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(r_free + 1);
   CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 1);
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // provably warp-uniform
   const int lane = threadIdx.x & 31;
-  // grid: x = row block, y = column chunk, z = (batch, head): the chunks of one slice run side by side and
-  // share their streamed operands in L2
-  const int bh = blockIdx.z;
-  const int n_off = blockIdx.y * N2;
-
-  // row side = the resident tile; column side = the streamed blocks
+  // Persistent grid: CTA c works on items c, c + gridDim.x, ... of the list
+  //   w = (bh * ny + chunk) * nrb + k,   row block = k-th heaviest,
+  // so that the CTAs running at any moment cover a few neighbouring slices (operands shared in L2) and every
+  // CTA gets the same mix of light and heavy row blocks (gridDim.x is chosen coprime to nrb * ny).
+  // Loads, MMAs and element-wise work of consecutive items overlap: the producer prefetches the next item's
+  // resident tile as soon as GEMM1 of the current one has finished (r_free), the epilogue of an item runs
+  // while GEMM1 of the next one is already in flight, and only the first GEMM2 waits for it (acc_free).
   const int rows_len = (MODE == kChainRowK) ? p.Lkv : p.Lq;
   const int cols_len = (MODE == kChainRowK) ? p.Lq : p.Lkv;
-  const int nrb = (rows_len + 127) / 128;
-  // heaviest row blocks first when blocks are skipped (Fwd/RowQ: late queries; RowK: early keys)
-  const int rb = (p.skip_upper && MODE != kChainRowK) ? (nrb - 1 - blockIdx.x) : blockIdx.x;
-  const int row0 = rb * 128;
   const int ncb = (cols_len + 127) / 128;
-  int t_start = 0, n_iter = ncb;
-  if (p.skip_upper) {
-    if (MODE == kChainRowK) {
-      t_start = row0 / 128;  // query blocks that end before this key block see none of its keys
-      n_iter = ncb - t_start;
-    } else {
-      const int last = row0 / 128 + 1;  // key blocks up to the one containing the last query row
-      n_iter = last < ncb ? last : ncb;
+  auto decode = [&](int w) -> ChainItem {
+    ChainItem it;
+    const int k = w % p.nrb;
+    const int rest = w / p.nrb;
+    it.n_off = (rest % p.ny) * N2;
+    it.bh = rest / p.ny;
+    // heaviest row blocks first when blocks are skipped (Fwd/RowQ: late queries; RowK: early keys)
+    const int rb = (p.skip_upper && MODE != kChainRowK) ? (p.nrb - 1 - k) : k;
+    it.row0 = rb * 128;
+    it.t_start = 0;
+    it.n_iter = ncb;
+    if (p.skip_upper) {
+      if (MODE == kChainRowK) {
+        it.t_start = rb;  // query blocks that end before this key block see none of its keys
+        it.n_iter = ncb - rb;
+      } else {
+        it.n_iter = (rb + 1 < ncb) ? rb + 1 : ncb;  // key blocks up to the one holding the last query row
+      }
+      if (it.n_iter < 0) it.n_iter = 0;
     }
-    if (n_iter < 0) n_iter = 0;
-  }
+    return it;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(r_full, 1);
@@ -154,6 +175,8 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
       mbar_init(&w_full[i], 128);
     }
     mbar_init(acc_done, 1);
+    mbar_init(acc_free, 128);
+    mbar_init(r_free, 1);
     ab->flag = 0;
     fence_mbar_init();
   }
@@ -175,14 +198,12 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
 
   if (warp == 5) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && n_iter > 0) {
+    if (lane == 0) {
       bool ok = true;
-      mbar_expect_tx(r_full, Cfg::R_BYTES);
-#pragma unroll
-      for (int c = 0; c < K1B; ++c) tma_load_3d(sR + c * BOX, &tmR, r_full, c * 64, row0, bh);
-      int bi = 0;  // items issued
-      // one item = boxes [2i, 2i+2) of the tile (the last item of an odd tile holds one box)
-      auto put = [&](const CUtensorMap* map, int x0, int nboxes, int y) {
+      int bi = 0;    // ring items issued so far (all work items)
+      int kacc = 0;  // non-empty work items started so far
+      // one ring item = boxes [2i, 2i+2) of a tile (the last item of an odd tile holds one box)
+      auto put = [&](const CUtensorMap* map, int x0, int nboxes, int y, int bh) {
         const int slot = bi % NSLOT;
         const int use = bi / NSLOT;
         if (use > 0) ok = mbar_wait(&slot_empty[slot], (use - 1) & 1, ab, kCtSlotEmpty);
@@ -192,19 +213,31 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
           tma_load_3d(sRing + slot * ITEM + b * BOX, map, &slot_full[slot], x0 + b * 64, y, bh);
         ++bi;
       };
-      // consumption order: C_0, then for t >= 1: C_t, T_{t-1}; finally T_{n-1}
-      for (int t = 0; t <= n_iter && ok; ++t) {
-        if (t < n_iter) {
-          for (int i = 0; i < CI && ok; ++i)
-            put(&tmC, i * 128, (K1B - 2 * i) >= 2 ? 2 : 1, (t_start + t) * 128);
-        }
-        if (t >= 1) {
-          for (int i = 0; i < TI && ok; ++i)
-            put(&tmT, n_off + i * 128, (N2B - 2 * i) >= 2 ? 2 : 1, (t_start + t - 1) * 128);
+      for (int w = blockIdx.x; w < p.total_items && ok; w += gridDim.x) {
+        const ChainItem it = decode(w);
+        if (it.n_iter == 0) continue;
+        // the resident tile may be overwritten once GEMM1 of the previous item has completed
+        if (kacc > 0) ok = mbar_wait(r_free, (kacc - 1) & 1, ab, kCtRFree);
+        if (!ok) break;
+        mbar_expect_tx(r_full, Cfg::R_BYTES);
+#pragma unroll
+        for (int c = 0; c < K1B; ++c) tma_load_3d(sR + c * BOX, &tmR, r_full, c * 64, it.row0, it.bh);
+        ++kacc;
+        // consumption order: C_0, then for t >= 1: C_t, T_{t-1}; finally T_{n-1}
+        for (int t = 0; t <= it.n_iter && ok; ++t) {
+          if (t < it.n_iter) {
+            for (int i = 0; i < CI && ok; ++i)
+              put(&tmC, i * 128, (K1B - 2 * i) >= 2 ? 2 : 1, (it.t_start + t) * 128, it.bh);
+          }
+          if (t >= 1) {
+            for (int i = 0; i < TI && ok; ++i)
+              put(&tmT, it.n_off + i * 128, (N2B - 2 * i) >= 2 ? 2 : 1, (it.t_start + t - 1) * 128, it.bh);
+          }
         }
       }
       if (!ok) {
-        mbar_wait_drain(r_full, 0, 2000000ull);
+        // abort path: let the copies already issued land before this CTA's shared memory is released
+        if (kacc > 0) mbar_wait_drain(r_full, (kacc - 1) & 1, 2000000ull);
         for (int slot = 0; slot < NSLOT; ++slot)
           if (bi > slot) mbar_wait_drain(&slot_full[slot], ((bi - 1 - slot) / NSLOT) & 1, 2000000ull);
       }
@@ -213,13 +246,15 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
     // ------------------------------------------------------------------ MMA issuer
     // The whole warp runs converged (waits included) and one elected lane issues, so that addresses and
     // descriptors stay warp-uniform. (Splitting GEMM1 and GEMM2 over two issuing warps was measured and
-    // does not pay: the kernel is bound by the L2->SM operand stream, not by issue slots.)
-    if (n_iter > 0) {
+    // does not pay.)
+    {
       constexpr uint32_t idesc_z = umma_idesc(128, 128, BF16, false, false);
       constexpr uint32_t idesc_acc2 = umma_idesc(128, 128, BF16, false, true);  // two boxes: N = 128
       constexpr uint32_t idesc_acc1 = umma_idesc(128, 64, BF16, false, true);   // one box:   N = 64
       bool ok = true;
-      int bi = 0;  // items consumed
+      int bi = 0;    // ring items consumed so far
+      int g0 = 0;    // 128-wide blocks processed before the current work item (selects the Z buffer)
+      int kacc = 0;  // non-empty work items finished so far
       auto take = [&](int& slot) -> uint32_t {
         slot = bi % NSLOT;
         ok = mbar_wait_warp(&slot_full[slot], (bi / NSLOT) & 1, ab, kCtSlotFull);
@@ -227,8 +262,9 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
         return smem_u32(sRing) + slot * ITEM;
       };
       const uint32_t r_addr = smem_u32(sR);
-      auto issue_z = [&](int t) {
-        const uint32_t tz = tZ0 + (t & 1) * 128;
+      // Z(block g) = R C^T; last_of_item: GEMM1 of this work item is complete after it
+      auto issue_z = [&](int g, bool last_of_item) {
+        const uint32_t tz = tZ0 + (g & 1) * 128;
 #pragma unroll
         for (int i = 0; i < CI; ++i) {
           int slot;
@@ -246,17 +282,21 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
               }
             }
             tc_commit(&slot_empty[slot]);
-            if (i == CI - 1) tc_commit(&z_full[t & 1]);
+            if (i == CI - 1) {
+              tc_commit(&z_full[g & 1]);
+              if (last_of_item) tc_commit(r_free);
+            }
           }
           __syncwarp();
         }
       };
-      auto issue_acc = [&](int t) {
-        ok = mbar_wait_warp(&w_full[t & 1], (t >> 1) & 1, ab, kCtWFull);
+      // ACC (+)= W(block g) T; first / last of the work item
+      auto issue_acc = [&](int g, bool first, bool last) {
+        ok = mbar_wait_warp(&w_full[g & 1], (g >> 1) & 1, ab, kCtWFull);
         if (!ok) return;
-        if (lane == 0) AB200_CTR(1, t, 2);
+        if (lane == 0) AB200_CTR(1, g, 2);
         tc_fence_after();
-        const uint32_t tw = tZ0 + (t & 1) * 128;
+        const uint32_t tw = tZ0 + (g & 1) * 128;
 #pragma unroll
         for (int i = 0; i < TI; ++i) {
           int slot;
@@ -267,57 +307,90 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)
               umma_ts(tACC + i * 128, tw + ks * 8, umma_smem_desc(a + ks * 2048, BOX, 1024), two ? idesc_acc2 : idesc_acc1,
-                      (t > 0 || ks > 0) ? 1u : 0u);
+                      (!first || ks > 0) ? 1u : 0u);
             tc_commit(&slot_empty[slot]);
-            if (i == TI - 1 && t == n_iter - 1) tc_commit(acc_done);
+            if (i == TI - 1 && last) tc_commit(acc_done);
           }
           __syncwarp();
         }
       };
-      ok = mbar_wait_warp(r_full, 0, ab, kCtR);
-      if (ok) {
+      for (int w = blockIdx.x; w < p.total_items && ok; w += gridDim.x) {
+        const ChainItem it = decode(w);
+        const int n = it.n_iter;
+        if (n == 0) continue;
+        ok = mbar_wait_warp(r_full, kacc & 1, ab, kCtR);
+        if (!ok) break;
         tc_fence_after();
-        issue_z(0);
-        for (int t = 0; t < n_iter && ok; ++t) {
-          if (lane == 0) AB200_CTR(1, t, 0);
-          if (t + 1 < n_iter) issue_z(t + 1);
-          if (lane == 0) AB200_CTR(1, t, 1);
-          if (ok) issue_acc(t);
-          if (lane == 0) AB200_CTR(1, t, 3);
+        issue_z(g0, n == 1);
+        for (int t = 0; t < n && ok; ++t) {
+          if (lane == 0) AB200_CTR(1, g0 + t, 0);
+          if (t + 1 < n) issue_z(g0 + t + 1, t + 2 == n);
+          if (lane == 0) AB200_CTR(1, g0 + t, 1);
+          if (!ok) break;
+          if (t == 0 && kacc > 0) {
+            // the first GEMM2 overwrites the accumulator: the previous item's epilogue must have read it
+            ok = mbar_wait_warp(acc_free, (kacc - 1) & 1, ab, kCtAccFree);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          issue_acc(g0 + t, t == 0, t + 1 == n);
+          if (lane == 0) AB200_CTR(1, g0 + t, 3);
         }
+        g0 += n;
+        ++kacc;
       }
     }
   } else if (warp < 4) {
     // ------------------------------------------------------------------ element-wise warpgroup
     const int tid = threadIdx.x;  // 0..127 = TMEM lane = row of the resident tile
-    const int grow = row0 + tid;  // global row index on the row side
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32);
-    const int h = bh % p.H;
     const bool decay_mode = !GENERAL;
-    float lg = 0.f;  // log2(gamma)
-    if (decay_mode) lg = log2f(p.decay[h]);
-    // per-row factor that does not depend on the block
-    float rowf_base = p.scale;
-    if (decay_mode) rowf_base *= exp2f((MODE == kChainRowK ? -tid : tid) * lg);
-    if (MODE == kChainRowQ) rowf_base *= (grow < p.Lq) ? 1.0f / p.r_in[static_cast<size_t>(bh) * p.Lq + grow] : 0.f;
-    if (MODE != kChainRowK && decay_mode) {
-      cf[tid] = exp2f(-tid * lg);  // gamma^(-c)
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-    }
-    float rsum = 0.f;
     bool ok = true;
+    int g0 = 0;     // blocks processed before the current work item
+    int kacc = 0;   // non-empty work items finished so far
+    int kitem = 0;  // work items seen so far (selects the per-item column-factor table)
+
+    for (int w = blockIdx.x; w < p.total_items && ok; w += gridDim.x, ++kitem) {
+      const ChainItem it = decode(w);
+      const int bh = it.bh, row0 = it.row0, n_off = it.n_off, t_start = it.t_start, n_iter = it.n_iter;
+      const int grow = row0 + tid;  // global row index on the row side
+      const int h = bh % p.H;
+      float lg = 0.f;  // log2(gamma)
+      if (decay_mode) lg = log2f(p.decay[h]);
+      // per-row factor that does not depend on the block
+      float rowf_base = p.scale;
+      if (decay_mode) rowf_base *= exp2f((MODE == kChainRowK ? -tid : tid) * lg);
+      if (MODE == kChainRowQ) rowf_base *= (grow < p.Lq) ? 1.0f / p.r_in[static_cast<size_t>(bh) * p.Lq + grow] : 0.f;
+      const float* cf_item = cf + (kitem & 1) * 128;
+      if (MODE != kChainRowK && decay_mode) {
+        // gamma^(-c); two tables alternate between work items so that a thread still finishing the previous
+        // item is not overtaken (one named barrier per item keeps the threads within one item of each other)
+        cf[(kitem & 1) * 128 + tid] = exp2f(-tid * lg);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      float rsum = 0.f;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + (static_cast<size_t>(bh) * rows_len + grow) * p.ld_out + n_off;
+      if (n_iter == 0) {
+        // no block contributes to this tile: zeros (and r = 1 in the forward)
+        if (grow < rows_len) {
+          for (int c = 0; c < N2; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
+          if (MODE == kChainFwd && n_off == 0) p.r_out[static_cast<size_t>(bh) * p.Lq + grow] = 1.0f;
+        }
+        continue;
+      }
 
     for (int t = 0; t < n_iter; ++t) {
+      const int g = g0 + t;  // running block index: Z buffer g & 1
       const int col0 = (t_start + t) * 128;
-      const float* cft = cf;
+      const float* cft = cf_item;
       if (MODE == kChainRowK) {
         // column factor: 1/r of the block's queries (times gamma^c under decay)
         const int qi = col0 + tid;
         float f = (qi < p.Lq) ? 1.0f / p.r_in[static_cast<size_t>(bh) * p.Lq + qi] : 0.f;
         if (decay_mode) f *= exp2f(tid * lg);
-        cf[(t & 1) * 128 + tid] = f;
+        cf[(g & 1) * 128 + tid] = f;
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        cft = cf + (t & 1) * 128;
+        cft = cf + (g & 1) * 128;
       }
       float rowf = rowf_base;
       if (decay_mode) rowf *= exp2f((MODE == kChainRowK ? (col0 - row0) : (row0 - col0)) * lg);
@@ -326,12 +399,12 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
       const bool straddle = decay_mode && (MODE == kChainRowK ? (col0 < row0 + 127) : (col0 + 127 > row0));
       const int dlim = grow - col0;
 
-      if (tid == 0) AB200_CTR(0, t, 0);
-      ok = mbar_wait_warp(&z_full[t & 1], (t >> 1) & 1, ab, kCtZFull);
+      if (tid == 0) AB200_CTR(0, g, 0);
+      ok = mbar_wait_warp(&z_full[g & 1], (g >> 1) & 1, ab, kCtZFull);
       if (!ok) break;
-      if (tid == 0) AB200_CTR(0, t, 1);
+      if (tid == 0) AB200_CTR(0, g, 1);
       tc_fence_after();
-      const uint32_t tz = tmem_addr(tZ0 + (t & 1) * 128, lane_base, 0);
+      const uint32_t tz = tmem_addr(tZ0 + (g & 1) * 128, lane_base, 0);
 #pragma unroll
       for (int qd = 0; qd < 4; ++qd) {
         uint32_t zr[32];
@@ -402,48 +475,49 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
         }
         tmem_st16(tz + qd * 16, pk);
       }
-      if (tid == 0) AB200_CTR(0, t, 2);
+      if (tid == 0) AB200_CTR(0, g, 2);
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(&w_full[t & 1]);
-      if (tid == 0) AB200_CTR(0, t, 3);
+      mbar_arrive(&w_full[g & 1]);
+      if (tid == 0) AB200_CTR(0, g, 3);
     }
+      if (!ok) break;
 
-    // ---- epilogue
-    uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + (static_cast<size_t>(bh) * rows_len + grow) * p.ld_out + n_off;
-    if (ok && n_iter > 0) {
-      ok = mbar_wait_warp(acc_done, 0, ab, kCtAccDone);
-      if (ok) {
-        tc_fence_after();
-        float osc = 1.0f;
-        if (MODE == kChainFwd) {
-          const float r = fmaxf(rsum, 1.0f);
-          osc = 1.0f / r;
-          if (n_off == 0 && grow < rows_len) p.r_out[static_cast<size_t>(bh) * p.Lq + grow] = r;
+      // ---- epilogue of the work item: ACC -> scale -> 16-bit -> global; then hand the accumulator back
+      ok = mbar_wait_warp(acc_done, kacc & 1, ab, kCtAccDone);
+      if (!ok) break;
+      tc_fence_after();
+      float osc = 1.0f;
+      if (MODE == kChainFwd) {
+        const float r = fmaxf(rsum, 1.0f);
+        osc = 1.0f / r;
+        if (n_off == 0 && grow < rows_len) p.r_out[static_cast<size_t>(bh) * p.Lq + grow] = r;
+      }
+      const uint32_t ta = tmem_addr(tACC, lane_base, 0);
+#pragma unroll
+      for (int c0 = 0; c0 < N2; c0 += 32) {
+        uint32_t rr[32];
+        tmem_ld32(ta + c0, rr);
+        tc_wait_ld();
+        if (c0 + 32 >= N2) {
+          // every column of the accumulator is in registers now: GEMM2 of the next item may overwrite it
+          tc_fence_before();
+          mbar_arrive(acc_free);
         }
-        const uint32_t ta = tmem_addr(tACC, lane_base, 0);
+        if (grow < rows_len) {
 #pragma unroll
-        for (int c0 = 0; c0 < N2; c0 += 32) {
-          uint32_t rr[32];
-          tmem_ld32(ta + c0, rr);
-          tc_wait_ld();
-          if (grow < rows_len) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 v;
-              v.x = pack2<BF16>(__uint_as_float(rr[i + 0]) * osc, __uint_as_float(rr[i + 1]) * osc);
-              v.y = pack2<BF16>(__uint_as_float(rr[i + 2]) * osc, __uint_as_float(rr[i + 3]) * osc);
-              v.z = pack2<BF16>(__uint_as_float(rr[i + 4]) * osc, __uint_as_float(rr[i + 5]) * osc);
-              v.w = pack2<BF16>(__uint_as_float(rr[i + 6]) * osc, __uint_as_float(rr[i + 7]) * osc);
-              *reinterpret_cast<uint4*>(orow + c0 + i) = v;
-            }
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = pack2<BF16>(__uint_as_float(rr[i + 0]) * osc, __uint_as_float(rr[i + 1]) * osc);
+            v.y = pack2<BF16>(__uint_as_float(rr[i + 2]) * osc, __uint_as_float(rr[i + 3]) * osc);
+            v.z = pack2<BF16>(__uint_as_float(rr[i + 4]) * osc, __uint_as_float(rr[i + 5]) * osc);
+            v.w = pack2<BF16>(__uint_as_float(rr[i + 6]) * osc, __uint_as_float(rr[i + 7]) * osc);
+            *reinterpret_cast<uint4*>(orow + c0 + i) = v;
           }
         }
       }
-    } else if (ok && grow < rows_len) {
-      // no block contributes to this tile: zeros (and r = 1 in the forward)
-      for (int c = 0; c < N2; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
-      if (MODE == kChainFwd && n_off == 0) p.r_out[static_cast<size_t>(bh) * p.Lq + grow] = 1.0f;
+      g0 += n_iter;
+      ++kacc;
     }
   }
 
