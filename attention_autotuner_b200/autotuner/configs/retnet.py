@@ -34,7 +34,7 @@ class RetConfig(BaseConfig):
         self.dv_chunk = dv_chunk if dv_chunk is not None else dv_chunk_for(D)
         self.Br = 128
         self.Bc = 128
-        self.Nthreads = 192
+        self.Nthreads = 384
         self.operation = "ret"
         self.template_dir = os.path.join(CSRC_DIR, "kernels", "retnet")
 

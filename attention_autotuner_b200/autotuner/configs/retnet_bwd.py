@@ -28,7 +28,7 @@ class RetBwdConfig(BaseConfig):
         self.dq_chunk = dq_chunk if dq_chunk is not None else dv_chunk_for(Kd)
         self.Br = 128
         self.Bc = 128
-        self.Nthreads = 192
+        self.Nthreads = 384
         self.operation = "ret_bwd"
         self.template_dir = os.path.join(CSRC_DIR, "kernels", "retnet", "bwd")
 

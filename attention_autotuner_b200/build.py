@@ -10,12 +10,12 @@ import subprocess
 import sys
 
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
-LIB_PATH = os.path.join(CSRC, "libattn_b200.so")
+LIB_PATH = os.environ.get("ATTN_B200_LIB", os.path.join(CSRC, "libattn_b200.so"))  # override: a library built elsewhere
 NVCC = os.environ.get("NVCC", shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc")
 
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
-    "--shared", "-Xcompiler", "-fPIC", "--split-compile=0",
+    "--shared", "-Xcompiler", "-fPIC",
 ]
 
 

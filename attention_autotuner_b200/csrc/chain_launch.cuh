@@ -70,6 +70,7 @@ int chain_launch(const void* R, int r_len, const void* C, int c_len, const void*
                  cudaStream_t stream, const char* what) {
   CUtensorMap tr, tc, tt;
   int rc;
+  if (!aligned32(p.out)) return fail(kErrInvalidArgument, "%s: output tensors must be 32-byte aligned", what);
   if ((rc = bind_device_of(R, what))) return rc;
   if ((rc = make_tmap_3d(&tr, R, Cfg::BF16, Cfg::K1, r_len, BH, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tc, C, Cfg::BF16, Cfg::K1, c_len, BH, 64, 128))) return rc;

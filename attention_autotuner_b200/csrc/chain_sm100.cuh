@@ -26,8 +26,9 @@
 //     the thread that owns the row / column) or a per-head decay gamma, M[i,j] = gamma^(i-j) for i>=j,
 //     computed in registers, with the all-zero blocks above the diagonal skipped.
 //
-// Roles: warps 0-3 element-wise warpgroup (thread t owns TMEM lane t), warp 4 issues every tcgen05.mma
-// (converged warp, one elected lane), warp 5 lane 0 is the TMA producer. Z is double buffered in tensor
+// Roles: warps 0-3 element-wise warpgroup (thread t owns TMEM lane t), warp 4 issues GEMM1 and warp 5 GEMM2
+// (converged warps, one elected lane each), warp 6 lane 0 is the TMA producer, warp 7 the scout that turns
+// per-item ring arrivals into one arrival per operand tile, warps 8-11 the epilogue warpgroup. Z is double buffered in tensor
 // memory so that GEMM1 of block t+1 runs while the warpgroup works on block t. All streamed operands
 // travel through one ring of 32 KB items (two boxes of 128 rows x 64 columns, 128-byte swizzle).
 #pragma once
@@ -79,12 +80,12 @@ struct ChainConfig {
   static constexpr int NSLOT_FIT = (232448 - 1024 - AUX_BYTES - R_BYTES) / ITEM_BYTES;
   static constexpr int NSLOT = NSLOT_FIT > 6 ? 6 : NSLOT_FIT;
   static constexpr int SMEM_BYTES = 1024 + R_BYTES + NSLOT * ITEM_BYTES + AUX_BYTES;
-  static constexpr int NTHREADS = 192;  // element-wise warpgroup + MMA issuer warp + TMA producer warp
+  static constexpr int NTHREADS = 384;  // element-wise warpgroup + {GEMM1, GEMM2, TMA producer, scout} + epilogue warpgroup
   static constexpr int TMEM_COLS = 512;  // 2 x 128 (Z) + N2
   static_assert(K1 % 64 == 0 && K1 >= 64 && K1 <= 512, "K1");
   static_assert(N2 % 64 == 0 && N2 >= 64 && N2 <= 256, "N2");
   static_assert(NSLOT >= 3, "ring too small");
-  static_assert(2 * NSLOT + 10 <= 64, "barrier area");
+  static_assert(2 * NSLOT + 20 <= 96, "barrier area");
 };
 
 // Optional event trace (compile with -DAB200_TRACE), see fa_fwd_sm100.cuh: CTA (0,0,0) only.
@@ -100,7 +101,7 @@ __device__ long long g_chain_trace[2][kChainTraceIters][8];
 #endif
 
 enum ChainTag : int {
-  kCtR = 11, kCtSlotFull = 12, kCtSlotEmpty = 13, kCtZFull = 14, kCtWFull = 15, kCtAccDone = 16, kCtAccFree = 17, kCtRFree = 18
+  kCtR = 11, kCtSlotFull = 12, kCtSlotEmpty = 13, kCtZFull = 14, kCtWFull = 15, kCtAccDone = 16, kCtAccFree = 17, kCtRFree = 18, kCtZFree = 19
 };
 
 template <class Cfg>
@@ -117,7 +118,8 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
   uint8_t* sR = smem;
   uint8_t* sRing = smem + Cfg::R_BYTES;
   float* cf = reinterpret_cast<float*>(sRing + NSLOT * ITEM);  // [2][128] column factors
-  uint64_t* bars = reinterpret_cast<uint64_t*>(cf + 256);
+  float* rs = cf + 256;                                         // [128] row sums of the finished item (forward)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(rs + 128);
   uint64_t* r_full = bars;                    // [1]
   uint64_t* slot_full = bars + 1;             // [NSLOT]
   uint64_t* slot_empty = slot_full + NSLOT;   // [NSLOT]
@@ -126,7 +128,10 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
   uint64_t* acc_done = w_full + 2;            // [1] GEMM2 of an item complete        (MMA -> element-wise)
   uint64_t* acc_free = acc_done + 1;          // [1] accumulator drained by the epilogue (element-wise -> MMA)
   uint64_t* r_free = acc_free + 1;            // [1] GEMM1 of an item complete: R may be overwritten (MMA -> TMA)
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(r_free + 1);
+  uint64_t* z_free = r_free + 1;              // [2] GEMM2 of a block complete: its Z/W buffer may be rewritten
+  uint64_t* c_ready = z_free + 2;             // [4] all ring items of a C tile have landed (scout -> GEMM1 warp)
+  uint64_t* t_ready = c_ready + 4;            // [4] same for a T tile                      (scout -> GEMM2 warp)
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(t_ready + 4);
   CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 1);
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // provably warp-uniform
@@ -177,6 +182,11 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
     mbar_init(acc_done, 1);
     mbar_init(acc_free, 128);
     mbar_init(r_free, 1);
+    for (int i = 0; i < 2; ++i) mbar_init(&z_free[i], 1);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&c_ready[i], 1);
+      mbar_init(&t_ready[i], 1);
+    }
     ab->flag = 0;
     fence_mbar_init();
   }
@@ -184,7 +194,7 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
     tmem_alloc(tmem_base_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
-  if (warp == 5 && lane == 0) {
+  if (warp == 6 && lane == 0) {
     tma_prefetch_desc(&tmR);
     tma_prefetch_desc(&tmC);
     tma_prefetch_desc(&tmT);
@@ -196,7 +206,17 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
   const uint32_t tZ0 = tmem_base;          // Z buffers at columns [0,128) and [128,256); W overlays the first 64
   const uint32_t tACC = tmem_base + 256;   // [256, 256+N2)
 
-  if (warp == 5) {
+  // Register budget per role (setmaxnreg): the element-wise threads of the forward and of the mask-tensor flavours
+  // need more than the 168 registers per thread that 384 threads get at launch. AB200_CHAIN_REBAL: 0 = never,
+  // 1 = every flavour, 2 = only those flavours. Measured at config 4 in one session (forward + backward):
+  // 1.244 / 1.225 / 1.40 ms for 0 / 1 / 2, so 1 is the default.
+#ifndef AB200_CHAIN_REBAL
+#define AB200_CHAIN_REBAL 1
+#endif
+  constexpr bool kRebalance = AB200_CHAIN_REBAL == 1 || (AB200_CHAIN_REBAL == 2 && ((MODE == kChainFwd) || GENERAL));
+  if (warp >= 4 && warp < 8) {
+  if constexpr (kRebalance) asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+  if (warp == 6) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       bool ok = true;
@@ -242,106 +262,161 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
           if (bi > slot) mbar_wait_drain(&slot_full[slot], ((bi - 1 - slot) / NSLOT) & 1, 2000000ull);
       }
     }
-  } else if (warp == 4) {
-    // ------------------------------------------------------------------ MMA issuer
-    // The whole warp runs converged (waits included) and one elected lane issues, so that addresses and
-    // descriptors stay warp-uniform. (Splitting GEMM1 and GEMM2 over two issuing warps was measured and
-    // does not pay.)
+  } else if (warp == 7) {
+    // ------------------------------------------------------------------ scout
+    // Walks the ring in order, waits for every item to land and posts ONE arrival per operand tile
+    // (c_ready / t_ready). The MMA warps then wait once per GEMM instead of once per ring item, and each ring
+    // barrier keeps a single in-order waiter (two waiters on one parity-tracked barrier could alias phases).
     {
-      constexpr uint32_t idesc_z = umma_idesc(128, 128, BF16, false, false);
-      constexpr uint32_t idesc_acc2 = umma_idesc(128, 128, BF16, false, true);  // two boxes: N = 128
-      constexpr uint32_t idesc_acc1 = umma_idesc(128, 64, BF16, false, true);   // one box:   N = 64
       bool ok = true;
-      int bi = 0;    // ring items consumed so far
-      int g0 = 0;    // 128-wide blocks processed before the current work item (selects the Z buffer)
-      int kacc = 0;  // non-empty work items finished so far
-      auto take = [&](int& slot) -> uint32_t {
-        slot = bi % NSLOT;
-        ok = mbar_wait_warp(&slot_full[slot], (bi / NSLOT) & 1, ab, kCtSlotFull);
-        ++bi;
-        return smem_u32(sRing) + slot * ITEM;
-      };
-      const uint32_t r_addr = smem_u32(sR);
-      // Z(block g) = R C^T; last_of_item: GEMM1 of this work item is complete after it
-      auto issue_z = [&](int g, bool last_of_item) {
-        const uint32_t tz = tZ0 + (g & 1) * 128;
-#pragma unroll
-        for (int i = 0; i < CI; ++i) {
-          int slot;
-          const uint32_t a = take(slot);
-          if (!ok) return;
-          const int nb = (K1B - 2 * i) >= 2 ? 2 : 1;
-          if (elect_one()) {
-#pragma unroll
-            for (int b = 0; b < 2; ++b) {
-              if (b < nb) {
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                  umma_ss(tz, umma_smem_desc(r_addr + (2 * i + b) * BOX + ks * 32, 16, 1024),
-                          umma_smem_desc(a + b * BOX + ks * 32, 16, 1024), idesc_z, (i > 0 || b > 0 || ks > 0) ? 1u : 0u);
-              }
-            }
-            tc_commit(&slot_empty[slot]);
-            if (i == CI - 1) {
-              tc_commit(&z_full[g & 1]);
-              if (last_of_item) tc_commit(r_free);
-            }
-          }
+      int bi = 0;
+      int cg = 0, tg = 0;  // groups posted so far (a group = up to two ring items = up to 128 columns)
+      auto post = [&](int nitems, uint64_t* ready, int& counter) {
+        for (int i0 = 0; i0 < nitems && ok; i0 += 2) {
+          for (int i = i0; i < nitems && i < i0 + 2 && ok; ++i, ++bi)
+            ok = mbar_wait_warp(&slot_full[bi % NSLOT], (bi / NSLOT) & 1, ab, kCtSlotFull);
+          if (ok && elect_one()) mbar_arrive(&ready[counter & 3]);
           __syncwarp();
-        }
-      };
-      // ACC (+)= W(block g) T; first / last of the work item
-      auto issue_acc = [&](int g, bool first, bool last) {
-        ok = mbar_wait_warp(&w_full[g & 1], (g >> 1) & 1, ab, kCtWFull);
-        if (!ok) return;
-        if (lane == 0) AB200_CTR(1, g, 2);
-        tc_fence_after();
-        const uint32_t tw = tZ0 + (g & 1) * 128;
-#pragma unroll
-        for (int i = 0; i < TI; ++i) {
-          int slot;
-          const uint32_t a = take(slot);
-          if (!ok) return;
-          const bool two = (N2B - 2 * i) >= 2;
-          if (elect_one()) {
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-              umma_ts(tACC + i * 128, tw + ks * 8, umma_smem_desc(a + ks * 2048, BOX, 1024), two ? idesc_acc2 : idesc_acc1,
-                      (!first || ks > 0) ? 1u : 0u);
-            tc_commit(&slot_empty[slot]);
-            if (i == TI - 1 && last) tc_commit(acc_done);
-          }
-          __syncwarp();
+          ++counter;
         }
       };
       for (int w = blockIdx.x; w < p.total_items && ok; w += gridDim.x) {
         const ChainItem it = decode(w);
         const int n = it.n_iter;
-        if (n == 0) continue;
-        ok = mbar_wait_warp(r_full, kacc & 1, ab, kCtR);
-        if (!ok) break;
-        tc_fence_after();
-        issue_z(g0, n == 1);
-        for (int t = 0; t < n && ok; ++t) {
-          if (lane == 0) AB200_CTR(1, g0 + t, 0);
-          if (t + 1 < n) issue_z(g0 + t + 1, t + 2 == n);
-          if (lane == 0) AB200_CTR(1, g0 + t, 1);
-          if (!ok) break;
-          if (t == 0 && kacc > 0) {
-            // the first GEMM2 overwrites the accumulator: the previous item's epilogue must have read it
-            ok = mbar_wait_warp(acc_free, (kacc - 1) & 1, ab, kCtAccFree);
-            if (!ok) break;
-            tc_fence_after();
-          }
-          issue_acc(g0 + t, t == 0, t + 1 == n);
-          if (lane == 0) AB200_CTR(1, g0 + t, 3);
+        for (int t = 0; t <= n && ok && n > 0; ++t) {
+          if (t < n) post(CI, c_ready, cg);
+          if (t >= 1) post(TI, t_ready, tg);
         }
+      }
+    }
+  } else if (warp == 4 || warp == 5) {
+    // ------------------------------------------------------------------ MMA issuers
+    // Warp 4 issues GEMM1 (Z), warp 5 issues GEMM2 (ACC). Measured on B200: the tensor pipe accepts only a
+    // short queue of MMAs, so every barrier wait (~100 cycles even when already complete) and every commit
+    // (~65 cycles) of a single issuing thread leaves the pipe idle; with two issuing warps the overhead of one
+    // runs under the MMAs of the other. Each warp runs converged and one elected lane issues, so addresses and
+    // descriptors stay warp-uniform. Ring items are consumed in a fixed order, so each warp computes the slots
+    // of its own tiles:  C_0 at b0;  C_t at b0 + CI + (t-1)(CI+TI);  T_t right after C_{t+1}, except the last
+    // T_{n-1}, which follows T_{n-2} directly.
+    {
+      constexpr uint32_t idesc_z = umma_idesc(128, 128, BF16, false, false);
+      constexpr uint32_t idesc_acc2 = umma_idesc(128, 128, BF16, false, true);  // two boxes: N = 128
+      constexpr uint32_t idesc_acc1 = umma_idesc(128, 64, BF16, false, true);   // one box:   N = 64
+      bool ok = true;
+      int b0 = 0;    // ring items of earlier work items
+      int g0 = 0;    // 128-wide blocks of earlier work items (selects Z buffer and ready barrier)
+      int kacc = 0;  // non-empty work items finished so far
+      int cg = 0, tg = 0;  // operand groups consumed so far (as the scout counts them)
+      const uint32_t r_addr = smem_u32(sR);
+      const uint32_t ring_addr = smem_u32(sRing);
+      for (int w = blockIdx.x; w < p.total_items && ok; w += gridDim.x) {
+        const ChainItem it = decode(w);
+        const int n = it.n_iter;
+        if (n == 0) continue;
+        if (warp == 4) {
+          ok = mbar_wait_warp(r_full, kacc & 1, ab, kCtR);
+          for (int t = 0; t < n && ok; ++t) {
+            const int g = g0 + t;
+            if (g >= 2) {
+              // Z buffer g&1 still holds W(g-2) until GEMM2 of block g-2 has read it
+              ok = mbar_wait_warp(&z_free[g & 1], ((g - 2) >> 1) & 1, ab, kCtZFree);
+              if (!ok) break;
+            }
+            if (lane == 0) AB200_CTR(1, g, 0);
+            const uint32_t tz = tZ0 + (g & 1) * 128;
+            const int base = b0 + (t == 0 ? 0 : CI + (t - 1) * (CI + TI));
+#pragma unroll
+            for (int i0 = 0; i0 < CI; i0 += 2) {
+              ok = mbar_wait_warp(&c_ready[cg & 3], (cg >> 2) & 1, ab, kCtSlotFull);
+              ++cg;
+              if (!ok) break;
+              tc_fence_after();
+              if (elect_one()) {
+#pragma unroll
+                for (int i = i0; i < i0 + 2; ++i) {
+                  if (i < CI) {
+                    const int slot = (base + i) % NSLOT;
+                    const uint32_t a = ring_addr + slot * ITEM;
+                    const int nb = (K1B - 2 * i) >= 2 ? 2 : 1;
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                      if (b < nb) {
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks)
+                          umma_ss(tz, umma_smem_desc(r_addr + (2 * i + b) * BOX + ks * 32, 16, 1024),
+                                  umma_smem_desc(a + b * BOX + ks * 32, 16, 1024), idesc_z,
+                                  (i > 0 || b > 0 || ks > 0) ? 1u : 0u);
+                      }
+                    }
+                    tc_commit(&slot_empty[slot]);
+                  }
+                }
+                if (i0 + 2 >= CI) {
+                  tc_commit(&z_full[g & 1]);
+                  if (t + 1 == n) tc_commit(r_free);
+                }
+              }
+              __syncwarp();
+            }
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) AB200_CTR(1, g, 1);
+          }
+        } else {
+          for (int t = 0; t < n && ok; ++t) {
+            const int g = g0 + t;
+            if (t == 0 && kacc > 0) {
+              // the first GEMM2 overwrites the accumulator: the previous item's epilogue must have read it
+              ok = mbar_wait_warp(acc_free, (kacc - 1) & 1, ab, kCtAccFree);
+              if (!ok) break;
+            }
+            ok = mbar_wait_warp(&w_full[g & 1], (g >> 1) & 1, ab, kCtWFull);
+            if (!ok) break;
+            if (lane == 0) AB200_CTR(1, g, 2);
+            tc_fence_after();
+            const uint32_t tw = tZ0 + (g & 1) * 128;
+            const int base = b0 + CI + t * (CI + TI) + (t + 1 < n ? CI : 0);
+#pragma unroll
+            for (int i0 = 0; i0 < TI; i0 += 2) {
+              ok = mbar_wait_warp(&t_ready[tg & 3], (tg >> 2) & 1, ab, kCtSlotFull);
+              ++tg;
+              if (!ok) break;
+              tc_fence_after();
+              if (elect_one()) {
+#pragma unroll
+                for (int i = i0; i < i0 + 2; ++i) {
+                  if (i < TI) {
+                    const int slot = (base + i) % NSLOT;
+                    const uint32_t a = ring_addr + slot * ITEM;
+                    const bool two = (N2B - 2 * i) >= 2;
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks)
+                      umma_ts(tACC + i * 128, tw + ks * 8, umma_smem_desc(a + ks * 2048, BOX, 1024),
+                              two ? idesc_acc2 : idesc_acc1, (t > 0 || ks > 0) ? 1u : 0u);
+                    tc_commit(&slot_empty[slot]);
+                  }
+                }
+                if (i0 + 2 >= TI) {
+                  tc_commit(&z_free[g & 1]);
+                  if (t + 1 == n) tc_commit(acc_done);
+                }
+              }
+              __syncwarp();
+            }
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) AB200_CTR(1, g, 3);
+          }
+        }
+        b0 += n * (CI + TI);
         g0 += n;
         ++kacc;
       }
     }
+  }
   } else if (warp < 4) {
     // ------------------------------------------------------------------ element-wise warpgroup
+    if constexpr (kRebalance) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int tid = threadIdx.x;  // 0..127 = TMEM lane = row of the resident tile
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32);
     const bool decay_mode = !GENERAL;
@@ -475,6 +550,15 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
         }
         tmem_st16(tz + qd * 16, pk);
       }
+      if (MODE == kChainFwd && t + 1 == n_iter) {
+        // hand the row sums to the epilogue warpgroup (single buffer: the previous item's epilogue, which
+        // signals acc_free after reading it, must be through)
+        if (kacc > 0) {
+          ok = mbar_wait_warp(acc_free, (kacc - 1) & 1, ab, kCtAccFree);
+          if (!ok) break;
+        }
+        rs[tid] = rsum;
+      }
       if (tid == 0) AB200_CTR(0, g, 2);
       tc_wait_st();
       tc_fence_before();
@@ -482,16 +566,31 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
       if (tid == 0) AB200_CTR(0, g, 3);
     }
       if (!ok) break;
-
-      // ---- epilogue of the work item: ACC -> scale -> 16-bit -> global; then hand the accumulator back
+      g0 += n_iter;
+      ++kacc;
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warpgroup
+    if constexpr (kRebalance) asm volatile("setmaxnreg.dec.sync.aligned.u32 112;");
+    // Drains the accumulator of a finished work item (ACC -> scale -> 16-bit -> global) while the other roles
+    // are already working on the next item; thread t owns TMEM lane t.
+    const int tid = threadIdx.x - 256;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32);
+    bool ok = true;
+    int kacc = 0;
+    for (int w = blockIdx.x; w < p.total_items && ok; w += gridDim.x) {
+      const ChainItem it = decode(w);
+      if (it.n_iter == 0) continue;  // the element-wise warpgroup writes the zeros of an empty tile
+      const int grow = it.row0 + tid;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + (static_cast<size_t>(it.bh) * rows_len + grow) * p.ld_out + it.n_off;
       ok = mbar_wait_warp(acc_done, kacc & 1, ab, kCtAccDone);
       if (!ok) break;
       tc_fence_after();
       float osc = 1.0f;
       if (MODE == kChainFwd) {
-        const float r = fmaxf(rsum, 1.0f);
+        const float r = fmaxf(rs[tid], 1.0f);
         osc = 1.0f / r;
-        if (n_off == 0 && grow < rows_len) p.r_out[static_cast<size_t>(bh) * p.Lq + grow] = r;
+        if (it.n_off == 0 && grow < rows_len) p.r_out[static_cast<size_t>(it.bh) * p.Lq + grow] = r;
       }
       const uint32_t ta = tmem_addr(tACC, lane_base, 0);
 #pragma unroll
@@ -506,17 +605,15 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
         }
         if (grow < rows_len) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 v;
-            v.x = pack2<BF16>(__uint_as_float(rr[i + 0]) * osc, __uint_as_float(rr[i + 1]) * osc);
-            v.y = pack2<BF16>(__uint_as_float(rr[i + 2]) * osc, __uint_as_float(rr[i + 3]) * osc);
-            v.z = pack2<BF16>(__uint_as_float(rr[i + 4]) * osc, __uint_as_float(rr[i + 5]) * osc);
-            v.w = pack2<BF16>(__uint_as_float(rr[i + 6]) * osc, __uint_as_float(rr[i + 7]) * osc);
-            *reinterpret_cast<uint4*>(orow + c0 + i) = v;
+          for (int i = 0; i < 32; i += 16) {
+            uint32_t v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              v[e] = pack2<BF16>(__uint_as_float(rr[i + 2 * e]) * osc, __uint_as_float(rr[i + 2 * e + 1]) * osc);
+            st_global_v8(orow + c0 + i, v);
           }
         }
       }
-      g0 += n_iter;
       ++kacc;
     }
   }

@@ -28,8 +28,8 @@ int fa_fwd_launch(const FaFwdArgs& a, cudaStream_t stream) {
   if (a.BH > 65535) return fail(kErrInvalidArgument, "fa_fwd: batch*heads %d exceeds 65535", a.BH);
   if (a.dv % Cfg::DV != 0) return fail(kErrUnsupported, "fa_fwd: dv %d is not a multiple of the tile's %d", a.dv, Cfg::DV);
   if (!(a.scale > 0.f) || !isfinite(a.scale)) return fail(kErrInvalidArgument, "fa_fwd: scale must be positive and finite");
-  if (!aligned16(a.q) || !aligned16(a.k) || !aligned16(a.v) || !aligned16(a.o))
-    return fail(kErrInvalidArgument, "fa_fwd: tensors must be 16-byte aligned");
+  if (!aligned16(a.q) || !aligned16(a.k) || !aligned16(a.v) || !aligned32(a.o))
+    return fail(kErrInvalidArgument, "fa_fwd: inputs must be 16-byte aligned and the output 32-byte aligned");
 
   CUtensorMap tq, tk, tv;
   int rc;

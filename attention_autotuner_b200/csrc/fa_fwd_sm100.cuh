@@ -450,13 +450,12 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tc_wait_ld();
           if (row < p.Lq) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 v;
-              v.x = pack2<BF16>(__uint_as_float(r[i + 0]) * inv_l, __uint_as_float(r[i + 1]) * inv_l);
-              v.y = pack2<BF16>(__uint_as_float(r[i + 2]) * inv_l, __uint_as_float(r[i + 3]) * inv_l);
-              v.z = pack2<BF16>(__uint_as_float(r[i + 4]) * inv_l, __uint_as_float(r[i + 5]) * inv_l);
-              v.w = pack2<BF16>(__uint_as_float(r[i + 6]) * inv_l, __uint_as_float(r[i + 7]) * inv_l);
-              *reinterpret_cast<uint4*>(orow + c0 + i) = v;
+            for (int i = 0; i < 32; i += 16) {
+              uint32_t v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                v[e] = pack2<BF16>(__uint_as_float(r[i + 2 * e]) * inv_l, __uint_as_float(r[i + 2 * e + 1]) * inv_l);
+              st_global_v8(orow + c0 + i, v);
             }
           }
         }

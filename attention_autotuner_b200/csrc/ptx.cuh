@@ -388,6 +388,13 @@ __device__ __forceinline__ void exp2_poly2(uint64_t x2, float& e0, float& e1) {
   e1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
 }
 
+// 256-bit global store (sm_100): one full 32-byte sector per lane. The address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t* r) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+               "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
 // Packs two fp32 into one 32-bit register of two 16-bit floats: low half = lo, high half = hi.
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {

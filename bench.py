@@ -47,6 +47,9 @@ WORKLOADS = {
 METRIC = "attn fwd TFLOPS at B=8,H=16,L=4096,d=128 fp16"
 UNIT = "TFLOP/s"
 RETNET = {"C3": "fwd", "C4": "fwd+bwd"}
+# dram__bytes_read.sum + dram__bytes_write.sum per step from the ncu captures summarised under profiles/
+# (fa_fwd_sm100_kernel_C2_fp16.md, chain_sm100_kernel_C4_retnet_fp16.md); None where no capture was taken
+NCU_TRAFFIC_BYTES = {"C2": 518.6e6, "C3": 378.5e6, "C4": 1543.0e6}
 
 
 def metric_name(workload):
@@ -336,7 +339,7 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": dtype, "data": "synthetic", "config": config,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
-                         "frac": achieved / peak_tf, "traffic": None,
+                         "frac": achieved / peak_tf, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                          "peak_source": f"{peak_src} (cuBLAS bf16 burst; the timed region is a burst of a few tens of ms)",
                          "peak_sustained": peak_sus, "frac_of_sustained": (achieved / peak_sus if peak_sus else None),
                          "flops_per_step": fl_gpu, "launches_per_step": launches_per_step,
