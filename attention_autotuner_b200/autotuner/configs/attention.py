@@ -11,12 +11,14 @@ class AttnConfig(BaseConfig):
     Blackwell knobs (keyword-only):
       q_tiles    query tiles of 128 rows per CTA (1, or 2 ping-ponging); Br = 128 * q_tiles
       kv_stages  depth of the shared-memory ring of K / V tiles fed by TMA
-      dv_chunk   columns of V / O per CTA (grid z = D / dv_chunk)
+      dv_chunk   columns of V / O per CTA (grid y = D / dv_chunk)
+      softmax_split  softmax warpgroups per query tile (1, or 2: two threads share a score row; needs q_tiles == 2)
+      exp_emu    of every 8 pairs of scores, how many use the FMA-pipe exp2 polynomial instead of MUFU (0..8)
     """
 
     def __init__(self, Br, Bc, Kd, D, BlockKSmem=256, BlockKSmem2=64, num_stages_qk=1, num_stages_v=1,
                  Nthreads=256, unrollLastIter: bool = True, warps_mma1_n=None, warps_mma_n=None, *,
-                 q_tiles=None, kv_stages=None, dv_chunk=None, dtype: str = "fp16") -> None:
+                 q_tiles=None, kv_stages=None, dv_chunk=None, softmax_split=1, exp_emu=0, dtype: str = "fp16") -> None:
         super().__init__(Br, Bc, Kd, D, BlockKSmem, num_stages_qk, Nthreads, unrollLastIter, dtype=dtype)
         self.BlockKSmem2 = BlockKSmem2
         self.num_stages_v = num_stages_v
@@ -27,9 +29,11 @@ class AttnConfig(BaseConfig):
         self.dv_chunk = dv_chunk if dv_chunk is not None else dv_chunk_for(D)
         self.q_tiles = q_tiles if q_tiles is not None else (2 if Br >= 256 else 1)
         self.kv_stages = kv_stages if kv_stages is not None else max(2, num_stages_qk + num_stages_v)
+        self.softmax_split = softmax_split
+        self.exp_emu = exp_emu
         self.Br = 128 * self.q_tiles
         self.Bc = 128
-        self.Nthreads = 128 * self.q_tiles + 128
+        self.Nthreads = 128 * self.q_tiles * self.softmax_split + 128
         self.operation = "attn"
         self.template_dir = os.path.join(CSRC_DIR, "kernels", "attention")
 
@@ -37,15 +41,16 @@ class AttnConfig(BaseConfig):
     def smem_bytes(self) -> int:
         q = self.q_tiles * 128 * self.Kd * 2
         slot = max(128 * self.Kd * 2, 128 * self.dv_chunk * 2)
-        return q + self.kv_stages * slot + 1024 + 256
+        return q + self.kv_stages * slot + 1024 + 256 + (self.q_tiles * 3072 if self.softmax_split == 2 else 0)
 
     def tmem_columns(self) -> int:
         return self.q_tiles * (128 + self.dv_chunk)
 
     def __repr__(self) -> str:
-        return ("Config(fuse_type={}, Br={}, Bc={}, Kd={}, D={}, q_tiles={}, kv_stages={}, dv_chunk={}, dtype={})"
-                .format(self.fuse_type, self.Br, self.Bc, self.Kd, self.D, self.q_tiles, self.kv_stages,
-                        self.dv_chunk, self.dtype))
+        return ("Config(fuse_type={}, Br={}, Bc={}, Kd={}, D={}, q_tiles={}, kv_stages={}, dv_chunk={}, softmax_split={}, "
+                "exp_emu={}, dtype={})".format(self.fuse_type, self.Br, self.Bc, self.Kd, self.D, self.q_tiles,
+                                               self.kv_stages, self.dv_chunk, self.softmax_split, self.exp_emu, self.dtype))
 
     def __str__(self) -> str:
-        return f"attn_{self.fuse_type}_{self.Br}_{self.Bc}_{self.Kd}_{self.D}_{self.q_tiles}_{self.kv_stages}_{self.dv_chunk}_{self.dtype}"
+        return (f"attn_{self.fuse_type}_{self.Br}_{self.Bc}_{self.Kd}_{self.D}_{self.q_tiles}_{self.kv_stages}_{self.dv_chunk}_"
+                f"{self.softmax_split}_{self.exp_emu}_{self.dtype}")

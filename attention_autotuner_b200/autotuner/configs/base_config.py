@@ -86,4 +86,7 @@ class BaseConfig:
         cc.__dict__.update(dd)
         cc.__dict__.setdefault("dtype", "fp16")
         cc.__dict__.setdefault("fuse_type", "tmem")
+        if cc.__dict__.get("operation") == "attn":
+            cc.__dict__.setdefault("softmax_split", 1)
+            cc.__dict__.setdefault("exp_emu", 0)
         return cc

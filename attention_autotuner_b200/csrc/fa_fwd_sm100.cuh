@@ -35,8 +35,13 @@ struct FaFwdParams {
   float scale_log2;    // scale * log2(e)
 };
 
-template <int DQK_, int DV_, int NQ_, int NSTAGE_, bool BF16_, int EXP_EMU_ = 0>
+template <int DQK_, int DV_, int NQ_, int NSTAGE_, bool BF16_, int EXP_EMU_ = 0, int SPLIT_ = 1>
 struct FaFwdConfig {
+  // softmax warpgroups per query tile: 1 (a thread owns a whole 128-column score row) or 2 (two threads share a
+  // row, 64 columns each, and exchange the row maximum through shared memory): halves the serial softmax time of
+  // a tile, which is what the tensor pipe waits for
+  static constexpr int SPLIT = SPLIT_;
+  static_assert(SPLIT_ == 1 || (SPLIT_ == 2 && NQ_ == 2 && DV_ % 64 == 0), "SPLIT");
   // of every 8 pairs of scores, how many take the FMA-pipe exponential instead of MUFU ex2 (0..8). Measured
   // on B200 at d = 128: every non-zero setting is slower (the softmax warps are issue/latency bound, not
   // MUFU bound), so the default is 0; kept as a tuning knob.
@@ -48,7 +53,7 @@ struct FaFwdConfig {
   static constexpr bool BF16 = BF16_;
   static constexpr int BM = 128;          // rows per query tile
   static constexpr int BN = 128;          // keys per KV block
-  static constexpr int NTHREADS = 128 * NQ + 128;  // softmax warpgroups + one auxiliary warpgroup (MMA, TMA, 2 idle warps)
+  static constexpr int NTHREADS = 128 * NQ * SPLIT + 128;  // softmax warpgroups + one auxiliary warpgroup (MMA, TMA, 2 idle warps)
   static constexpr int Q_TILE_BYTES = BM * DQK * 2;
   static constexpr int K_TILE_BYTES = BN * DQK * 2;
   static constexpr int V_TILE_BYTES = BN * DV * 2;
@@ -56,7 +61,8 @@ struct FaFwdConfig {
   static constexpr int TMEM_COLS_USED = NQ * (128 + DV);
   static constexpr int TMEM_COLS = TMEM_COLS_USED <= 32 ? 32 : TMEM_COLS_USED <= 64 ? 64 : TMEM_COLS_USED <= 128 ? 128 : TMEM_COLS_USED <= 256 ? 256 : 512;
   static constexpr int SMEM_TILES = NQ * Q_TILE_BYTES + NSTAGE * KV_SLOT_BYTES;
-  static constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int XCHG_BYTES = SPLIT == 2 ? NQ * 3 * 2 * 128 * 4 : 0;  // row max (double buffered) and row sum exchange
+  static constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/ + XCHG_BYTES;
   static_assert(DQK % 64 == 0 && DV % 64 == 0, "head dims must be multiples of 64");
   static_assert(TMEM_COLS_USED <= 512, "TMEM overflow: NQ*(128+DV) must be <= 512 columns");
   static_assert(DV <= 256, "one PV MMA covers at most N=256");
@@ -100,11 +106,13 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* o_done = p_full + NQ;            // [NQ]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(o_done + NQ);
   CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 1);
+  float* xchg = reinterpret_cast<float*>(smem + Cfg::SMEM_TILES + 256);  // [NQ][3][2][128], SPLIT == 2 only
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // provably warp-uniform
   const int lane = threadIdx.x & 31;
-  constexpr int kMmaWarp = 4 * NQ;
-  constexpr int kTmaWarp = 4 * NQ + 1;
+  constexpr int SPLIT = Cfg::SPLIT;
+  constexpr int kMmaWarp = 4 * NQ * SPLIT;
+  constexpr int kTmaWarp = 4 * NQ * SPLIT + 1;
 
   // Heaviest (latest) query blocks first under a causal mask.
   const int qblk = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
@@ -134,7 +142,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int i = 0; i < NQ; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
+      mbar_init(&p_full[i], 128 * SPLIT);
       mbar_init(&o_done[i], 1);
     }
     for (int i = 0; i < NSTAGE; ++i) {
@@ -160,8 +168,8 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   // With three warpgroups the launch-time register split (168/thread) starves the softmax threads, which
   // hold a full 128-column score row; each role branch moves registers accordingly (setmaxnreg).
-  if (warp >= 4 * NQ) {
-    if constexpr (NQ == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+  if (warp >= kMmaWarp) {
+    if constexpr (NQ == 2 && SPLIT == 1) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -257,7 +265,10 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (elect_one()) {
 #pragma unroll
           for (int ks = 0; ks < BN / 16; ++ks) {
-            umma_ts(tmem_base + NQ * 128 + s * DV, tmem_base + s * 128 + ks * 8,
+            // P sits in the first 64 columns of the S region; with two softmax warpgroups per tile each half keeps
+            // its 32 P columns inside its own score columns: [0,32) and [64,96)
+            const uint32_t pcol = (SPLIT == 2 && ks >= 4) ? 64 + (ks - 4) * 8 : ks * 8;
+            umma_ts(tmem_base + NQ * 128 + s * DV, tmem_base + s * 128 + pcol,
                     umma_smem_desc(va + ks * 2048, BN * 128, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
           }
           tc_commit(&o_done[s]);
@@ -312,6 +323,9 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
     }
   }
+  } else if constexpr (SPLIT == 2) {
+    // ------------------------------------------------------------------ softmax warpgroups, two per query tile
+#include "fa_fwd_softmax_split.cuh"
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
     if constexpr (NQ == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");

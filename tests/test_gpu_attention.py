@@ -202,3 +202,22 @@ def test_legacy_kernel_entry_symbol():
     so.profile.restype = ctypes.c_float
     ms = so.profile(P(qd), P(kd), P(vd), P(o), 1, 2, 256, 640)
     assert 0 < ms < 10
+
+
+@pytest.mark.parametrize("split,emu", [(2, 0), (2, 3), (1, 3)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_softmax_split_and_exp_emulation_knobs(split, emu, causal):
+    """Tuner knobs that change the softmax code path: two warpgroups per query tile (two threads per score row
+    exchanging the row maximum) and the FMA-pipe exp2 polynomial for part of the exponentials."""
+    from attention_autotuner_b200.autotuner.configs import AttnConfig
+    from attention_autotuner_b200.autotuner.runtime import Runtime
+    q, k, v = rand_qkv(29, 1, 3, 700, 900, 128, 128, torch.float16)
+    k = (k.float() * torch.linspace(0.5, 2.0, 900)[None, None, :, None]).half()   # growing scores: rescales happen
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    o = torch.zeros(1, 3, 700, 128, device="cuda", dtype=torch.float16)
+    lse = torch.zeros(1, 3, 700, device="cuda")
+    rt = Runtime(B200(), AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, softmax_split=split, exp_emu=emu))
+    rt.apply([qd, kd, vd, o], scale=0.11, causal=causal, extra_ptrs=(lse.data_ptr(),))
+    torch.cuda.synchronize()
+    assert rt.device_status() == 0
+    check(o.cpu(), lse.cpu(), q, k, v, 0.11, causal, "fp16")
