@@ -13,12 +13,13 @@ class AttnConfig(BaseConfig):
       kv_stages  depth of the shared-memory ring of K / V tiles fed by TMA
       dv_chunk   columns of V / O per CTA (grid y = D / dv_chunk)
       softmax_split  softmax warpgroups per query tile (1, or 2: two threads share a score row; needs q_tiles == 2)
+      mma_warps  MMA-issuing warps: 1, or 2 taking strict turns, one per query tile (needs q_tiles == 2)
       exp_emu    of every 8 pairs of scores, how many use the FMA-pipe exp2 polynomial instead of MUFU (0..8)
     """
 
     def __init__(self, Br, Bc, Kd, D, BlockKSmem=256, BlockKSmem2=64, num_stages_qk=1, num_stages_v=1,
                  Nthreads=256, unrollLastIter: bool = True, warps_mma1_n=None, warps_mma_n=None, *,
-                 q_tiles=None, kv_stages=None, dv_chunk=None, softmax_split=1, exp_emu=0, dtype: str = "fp16") -> None:
+                 q_tiles=None, kv_stages=None, dv_chunk=None, softmax_split=1, exp_emu=0, mma_warps=1, dtype: str = "fp16") -> None:
         super().__init__(Br, Bc, Kd, D, BlockKSmem, num_stages_qk, Nthreads, unrollLastIter, dtype=dtype)
         self.BlockKSmem2 = BlockKSmem2
         self.num_stages_v = num_stages_v
@@ -31,6 +32,7 @@ class AttnConfig(BaseConfig):
         self.kv_stages = kv_stages if kv_stages is not None else max(2, num_stages_qk + num_stages_v)
         self.softmax_split = softmax_split
         self.exp_emu = exp_emu
+        self.mma_warps = mma_warps
         self.Br = 128 * self.q_tiles
         self.Bc = 128
         self.Nthreads = 128 * self.q_tiles * self.softmax_split + 128
@@ -48,9 +50,10 @@ class AttnConfig(BaseConfig):
 
     def __repr__(self) -> str:
         return ("Config(fuse_type={}, Br={}, Bc={}, Kd={}, D={}, q_tiles={}, kv_stages={}, dv_chunk={}, softmax_split={}, "
-                "exp_emu={}, dtype={})".format(self.fuse_type, self.Br, self.Bc, self.Kd, self.D, self.q_tiles,
-                                               self.kv_stages, self.dv_chunk, self.softmax_split, self.exp_emu, self.dtype))
+                "exp_emu={}, mma_warps={}, dtype={})".format(self.fuse_type, self.Br, self.Bc, self.Kd, self.D, self.q_tiles,
+                                                             self.kv_stages, self.dv_chunk, self.softmax_split, self.exp_emu,
+                                                             self.mma_warps, self.dtype))
 
     def __str__(self) -> str:
         return (f"attn_{self.fuse_type}_{self.Br}_{self.Bc}_{self.Kd}_{self.D}_{self.q_tiles}_{self.kv_stages}_{self.dv_chunk}_"
-                f"{self.softmax_split}_{self.exp_emu}_{self.dtype}")
+                f"{self.softmax_split}_{self.exp_emu}_{self.mma_warps}_{self.dtype}")

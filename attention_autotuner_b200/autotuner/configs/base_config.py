@@ -89,4 +89,5 @@ class BaseConfig:
         if cc.__dict__.get("operation") == "attn":
             cc.__dict__.setdefault("softmax_split", 1)
             cc.__dict__.setdefault("exp_emu", 0)
+            cc.__dict__.setdefault("mma_warps", 1)
         return cc

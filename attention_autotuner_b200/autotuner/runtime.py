@@ -45,6 +45,22 @@ def source_tag() -> str:
     return _source_tag_cache
 
 
+def prune_stale(jit_dir: str = None) -> int:
+    """Delete per-config sources and libraries whose name carries another source hash than the current one
+    (they can never be selected again). Returns the number of files removed."""
+    jit_dir = jit_dir or DEFAULT_JIT_DIR
+    if not os.path.isdir(jit_dir):
+        return 0
+    keep = "_" + source_tag()
+    removed = 0
+    for name in os.listdir(jit_dir):
+        stem, ext = os.path.splitext(name)
+        if ext in (".cu", ".so") and not stem.endswith(keep):
+            os.remove(os.path.join(jit_dir, name))
+            removed += 1
+    return removed
+
+
 _handles: dict = {}
 _handles_lock = threading.Lock()
 

@@ -35,6 +35,8 @@ class AttnTunner(BaseTunner):
             return False
         if config.softmax_split == 2 and (config.q_tiles != 2 or config.dv_chunk % 64 != 0):
             return False
+        if config.mma_warps == 2 and config.q_tiles != 2:
+            return False
         return True
 
     def generate_configs(self, Br: int, Bc: int, dim_qk: int, dim_v: int):
@@ -46,11 +48,11 @@ class AttnTunner(BaseTunner):
                 configs.append(AttnConfig(Br, Bc, dim_qk, dim_v, q_tiles=q_tiles, kv_stages=kv_stages,
                                           dv_chunk=dv_chunk, dtype=self.dtype))
             if q_tiles == 2:
-                # second-order knobs around the usual ring depth: two softmax warpgroups per tile, and part of the
-                # exponentials on the FMA pipes
-                for split, emu in ((2, 0), (2, 2), (1, 2)):
+                # second-order knobs around the usual ring depth: two softmax warpgroups per tile, part of the
+                # exponentials on the FMA pipes, two MMA-issuing warps taking turns
+                for split, emu, mw in ((2, 0, 1), (2, 2, 1), (1, 2, 1), (1, 0, 2), (2, 0, 2)):
                     configs.append(AttnConfig(Br, Bc, dim_qk, dim_v, q_tiles=2, kv_stages=4, dv_chunk=dv_chunk,
-                                              softmax_split=split, exp_emu=emu, dtype=self.dtype))
+                                              softmax_split=split, exp_emu=emu, mma_warps=mw, dtype=self.dtype))
         return configs
 
     def default_config(self):

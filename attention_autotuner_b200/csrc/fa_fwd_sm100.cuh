@@ -35,8 +35,11 @@ struct FaFwdParams {
   float scale_log2;    // scale * log2(e)
 };
 
-template <int DQK_, int DV_, int NQ_, int NSTAGE_, bool BF16_, int EXP_EMU_ = 0, int SPLIT_ = 1>
+template <int DQK_, int DV_, int NQ_, int NSTAGE_, bool BF16_, int EXP_EMU_ = 0, int SPLIT_ = 1, int NMMA_ = 1>
 struct FaFwdConfig {
+  // MMA-issuing warps: 1, or 2 taking strict turns, one per query tile (see fa_fwd_mma_pair.cuh)
+  static constexpr int NMMA = NMMA_;
+  static_assert(NMMA_ == 1 || (NMMA_ == 2 && NQ_ == 2), "NMMA");
   // softmax warpgroups per query tile: 1 (a thread owns a whole 128-column score row) or 2 (two threads share a
   // row, 64 columns each, and exchange the row maximum through shared memory): halves the serial softmax time of
   // a tile, which is what the tensor pipe waits for
@@ -83,7 +86,7 @@ __device__ long long g_trace[5][kTraceIters][8];
 #endif
 
 // Barrier tags reported with a timeout status.
-enum FaTag : int { kTagQ = 1, kTagKvFull = 2, kTagKvEmpty = 3, kTagSFull = 4, kTagPFull = 5, kTagODone = 6 };
+enum FaTag : int { kTagQ = 1, kTagKvFull = 2, kTagKvEmpty = 3, kTagSFull = 4, kTagPFull = 5, kTagODone = 6, kTagTurn = 7 };
 
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
@@ -104,7 +107,8 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* s_full = kv_empty + NSTAGE;      // [NQ]
   uint64_t* p_full = s_full + NQ;            // [NQ]
   uint64_t* o_done = p_full + NQ;            // [NQ]
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(o_done + NQ);
+  uint64_t* turn = o_done + NQ;              // [2] issue turns of the two MMA warps (NMMA == 2)
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(turn + 2);
   CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 1);
   float* xchg = reinterpret_cast<float*>(smem + Cfg::SMEM_TILES + 256);  // [NQ][3][2][128], SPLIT == 2 only
 
@@ -112,7 +116,8 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int lane = threadIdx.x & 31;
   constexpr int SPLIT = Cfg::SPLIT;
   constexpr int kMmaWarp = 4 * NQ * SPLIT;
-  constexpr int kTmaWarp = 4 * NQ * SPLIT + 1;
+  constexpr int NMMA = Cfg::NMMA;
+  constexpr int kTmaWarp = 4 * NQ * SPLIT + NMMA;
 
   // Heaviest (latest) query blocks first under a causal mask.
   const int qblk = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
@@ -147,8 +152,10 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     for (int i = 0; i < NSTAGE; ++i) {
       mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&kv_empty[i], NMMA);
     }
+    mbar_init(&turn[0], 1);
+    mbar_init(&turn[1], 1);
     ab->flag = 0;
     fence_mbar_init();
   }
@@ -218,7 +225,12 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
     }
-  } else if (warp == kMmaWarp) {
+  } else if (NMMA == 2 && warp < kMmaWarp + 2) {
+    // ------------------------------------------------------------------ MMA issuers, one per query tile
+    if constexpr (NMMA == 2) {
+#include "fa_fwd_mma_pair.cuh"
+    }
+  } else if (NMMA == 1 && warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
     // The whole warp runs this role converged (waits included); one elected lane issues each batch of
     // tcgen05.mma + commits, so that addresses and descriptors stay warp-uniform.

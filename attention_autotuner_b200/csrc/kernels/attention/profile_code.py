@@ -9,7 +9,7 @@ take scale, causal flag, LSE pointer and stream."""
 global_vars = """
 #include "fa_fwd_launch.cuh"
 using namespace ab200;
-using Cfg = FaFwdConfig<{Kd}, {dv_chunk}, {q_tiles}, {kv_stages}, {bf16}, {exp_emu}, {softmax_split}>;
+using Cfg = FaFwdConfig<{Kd}, {dv_chunk}, {q_tiles}, {kv_stages}, {bf16}, {exp_emu}, {softmax_split}, {mma_warps}>;
 constexpr int kDv = {D};
 static int run(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H, int Seq_k, int Seq_q,
                float scale, int causal, void* stream) {{

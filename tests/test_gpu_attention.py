@@ -204,11 +204,11 @@ def test_legacy_kernel_entry_symbol():
     assert 0 < ms < 10
 
 
-@pytest.mark.parametrize("split,emu", [(2, 0), (2, 3), (1, 3)])
+@pytest.mark.parametrize("split,emu,mw", [(2, 0, 1), (2, 3, 1), (1, 3, 1), (1, 0, 2), (2, 0, 2)])
 @pytest.mark.parametrize("causal", [False, True])
-def test_softmax_split_and_exp_emulation_knobs(split, emu, causal):
+def test_softmax_split_and_exp_emulation_knobs(split, emu, mw, causal):
     """Tuner knobs that change the softmax code path: two warpgroups per query tile (two threads per score row
-    exchanging the row maximum) and the FMA-pipe exp2 polynomial for part of the exponentials."""
+    exchanging the row maximum), the FMA-pipe exp2 polynomial for part of the exponentials, two MMA warps taking turns."""
     from attention_autotuner_b200.autotuner.configs import AttnConfig
     from attention_autotuner_b200.autotuner.runtime import Runtime
     q, k, v = rand_qkv(29, 1, 3, 700, 900, 128, 128, torch.float16)
@@ -216,7 +216,7 @@ def test_softmax_split_and_exp_emulation_knobs(split, emu, causal):
     qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
     o = torch.zeros(1, 3, 700, 128, device="cuda", dtype=torch.float16)
     lse = torch.zeros(1, 3, 700, device="cuda")
-    rt = Runtime(B200(), AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, softmax_split=split, exp_emu=emu))
+    rt = Runtime(B200(), AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, softmax_split=split, exp_emu=emu, mma_warps=mw))
     rt.apply([qd, kd, vd, o], scale=0.11, causal=causal, extra_ptrs=(lse.data_ptr(),))
     torch.cuda.synchronize()
     assert rt.device_status() == 0
