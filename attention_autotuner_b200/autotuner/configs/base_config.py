@@ -72,6 +72,7 @@ class BaseConfig:
     def substitution_map(self) -> dict:
         d = dict(self.__dict__)
         d["bf16"] = "true" if self.dtype == "bf16" else "false"
+        d["cta_pair_bool"] = "true" if getattr(self, "cta_pair", 0) else "false"
         return d
 
     def __eq__(self, other):
@@ -90,4 +91,6 @@ class BaseConfig:
             cc.__dict__.setdefault("softmax_split", 1)
             cc.__dict__.setdefault("exp_emu", 0)
             cc.__dict__.setdefault("mma_warps", 1)
+        if cc.__dict__.get("operation") in ("ret", "ret_bwd"):
+            cc.__dict__.setdefault("cta_pair", 0)  # entries cached before the knob existed were single-CTA
         return cc

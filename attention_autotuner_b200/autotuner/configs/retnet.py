@@ -13,6 +13,12 @@ def _chain_smem(k1: int) -> int:
     return 1024 + r_bytes + nslot * 32768 + 2048, nslot
 
 
+def pair_ok(*chunks) -> bool:
+    """The CTA-pair chain kernel splits the streamed T tile by columns between the two CTAs in 64-column
+    boxes: every output chunk must be 128 or 256 columns wide."""
+    return all(c in (128, 256) for c in chunks)
+
+
 class RetConfig(BaseConfig):
     """RetNet parallel forward tile configuration (reference: python/autotuner/configs/retnet.py).
 
@@ -22,7 +28,7 @@ class RetConfig(BaseConfig):
 
     def __init__(self, Br, Bc, Kd, D, BlockKSmem=256, BlockKSmem2=64, num_stages_qk=1, num_stages_mask=1,
                  num_stages_v=1, Nthreads=256, unrollLastIter: bool = True, warps_mma1_n=None, warps_mma_n=None, *,
-                 dv_chunk=None, dtype: str = "fp16") -> None:
+                 dv_chunk=None, cta_pair=None, dtype: str = "fp16") -> None:
         super().__init__(Br, Bc, Kd, D, BlockKSmem, num_stages_qk, Nthreads, unrollLastIter, dtype=dtype)
         self.BlockKSmem2 = BlockKSmem2
         self.num_stages_v = num_stages_v
@@ -32,6 +38,9 @@ class RetConfig(BaseConfig):
         if warps_mma_n is not None:
             self.warps_mma_n = warps_mma_n
         self.dv_chunk = dv_chunk if dv_chunk is not None else dv_chunk_for(D)
+        # cta_pair: two CTAs (one cluster, the two SMs of a TPC) share a 256-row tile with cta_group::2 MMAs;
+        # needs dv_chunk in {128, 256}. Default: on whenever the chunk allows it.
+        self.cta_pair = int(pair_ok(self.dv_chunk) if cta_pair is None else cta_pair)
         self.Br = 128
         self.Bc = 128
         self.Nthreads = 384
@@ -48,8 +57,8 @@ class RetConfig(BaseConfig):
         return 256 + self.dv_chunk
 
     def __repr__(self) -> str:
-        return "Config(fuse_type={}, Br={}, Bc={}, Kd={}, D={}, dv_chunk={}, dtype={})".format(
-            self.fuse_type, self.Br, self.Bc, self.Kd, self.D, self.dv_chunk, self.dtype)
+        return "Config(fuse_type={}, Br={}, Bc={}, Kd={}, D={}, dv_chunk={}, cta_pair={}, dtype={})".format(
+            self.fuse_type, self.Br, self.Bc, self.Kd, self.D, self.dv_chunk, self.cta_pair, self.dtype)
 
     def __str__(self) -> str:
-        return f"ret_{self.fuse_type}_{self.Br}_{self.Bc}_{self.Kd}_{self.D}_{self.dv_chunk}_{self.dtype}"
+        return f"ret_{self.fuse_type}_{self.Br}_{self.Bc}_{self.Kd}_{self.D}_{self.dv_chunk}_{self.cta_pair}_{self.dtype}"

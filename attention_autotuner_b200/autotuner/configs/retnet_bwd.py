@@ -1,7 +1,7 @@
 import os
 
 from .base_config import BaseConfig, dv_chunk_for
-from .retnet import CSRC_DIR, _chain_smem
+from .retnet import CSRC_DIR, _chain_smem, pair_ok
 
 
 class RetBwdConfig(BaseConfig):
@@ -14,7 +14,7 @@ class RetBwdConfig(BaseConfig):
     def __init__(self, Br, Bc, Kd, D, mmawarpsN=None, mmawarpsN_dv=None, mmawarpsN_dk=None, mmawarpsN_dq=None,
                  Nthreads=256, unrollLastIter: bool = True, BlockKSmem=256, num_stages_qk=1, num_stages_mask=1,
                  num_stages_dv=1, num_stages_ds=1, num_stages_dq=1, *, dv_chunk=None, dq_chunk=None,
-                 dtype: str = "fp16") -> None:
+                 cta_pair=None, dtype: str = "fp16") -> None:
         super().__init__(Br, Bc, Kd, D, BlockKSmem, num_stages_qk, Nthreads, unrollLastIter, dtype=dtype)
         self.num_stages_mask = num_stages_mask
         self.mmawarpsN = mmawarpsN
@@ -26,6 +26,8 @@ class RetBwdConfig(BaseConfig):
         self.num_stages_dq = num_stages_dq
         self.dv_chunk = dv_chunk if dv_chunk is not None else dv_chunk_for(D)
         self.dq_chunk = dq_chunk if dq_chunk is not None else dv_chunk_for(Kd)
+        # cta_pair: all three kernels as CTA pairs on 256-row tiles (needs both chunks in {128, 256})
+        self.cta_pair = int(pair_ok(self.dv_chunk, self.dq_chunk) if cta_pair is None else cta_pair)
         self.Br = 128
         self.Bc = 128
         self.Nthreads = 384
@@ -42,8 +44,8 @@ class RetBwdConfig(BaseConfig):
         return 256 + max(self.dv_chunk, self.dq_chunk)
 
     def __repr__(self) -> str:
-        return "RetBwdConfig(Br={}, Bc={}, Kd={}, D={}, dv_chunk={}, dq_chunk={}, dtype={})".format(
-            self.Br, self.Bc, self.Kd, self.D, self.dv_chunk, self.dq_chunk, self.dtype)
+        return "RetBwdConfig(Br={}, Bc={}, Kd={}, D={}, dv_chunk={}, dq_chunk={}, cta_pair={}, dtype={})".format(
+            self.Br, self.Bc, self.Kd, self.D, self.dv_chunk, self.dq_chunk, self.cta_pair, self.dtype)
 
     def __str__(self) -> str:
-        return f"{self.operation}_{self.Br}_{self.Bc}_{self.Kd}_{self.D}_{self.dv_chunk}_{self.dq_chunk}_{self.dtype}"
+        return f"{self.operation}_{self.Br}_{self.Bc}_{self.Kd}_{self.D}_{self.dv_chunk}_{self.dq_chunk}_{self.cta_pair}_{self.dtype}"

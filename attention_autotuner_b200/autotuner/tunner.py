@@ -8,6 +8,7 @@ import ctypes
 from .base_tunner import BaseTunner, CompileResult  # noqa: F401
 from .configs import AttnConfig, RetBwdConfig, RetConfig  # noqa: F401
 from .configs.base_config import dv_chunk_for, find_best_pair, find_factor_pairs  # noqa: F401
+from .configs.retnet import pair_ok
 
 
 def _flops_fwd(t, causal):
@@ -110,6 +111,8 @@ class RetTunner(_RetBase):
         super().__init__(arch, torch_array, "retnet", scale=scale, causal=causal, decay=decay)
 
     def validate_kernel(self, config):
+        if config.cta_pair and not pair_ok(config.dv_chunk):
+            return False
         return (config.Kd % 64 == 0 and config.D % config.dv_chunk == 0 and config.dv_chunk <= 256
                 and config.smem_bytes() <= self.arch.smem_cap + 1024
                 and config.tmem_columns() <= getattr(self.arch, "tmem_columns", 512) and config.ring_slots() >= 3)
@@ -118,7 +121,8 @@ class RetTunner(_RetBase):
         if Br != 128:
             return []
         from .configs import RetConfig
-        return [RetConfig(Br, Bc, dim_qk, dim_v, dv_chunk=c, dtype=self.dtype) for c in _chunks(dim_v)]
+        return [RetConfig(Br, Bc, dim_qk, dim_v, dv_chunk=c, cta_pair=pr, dtype=self.dtype)
+                for c in _chunks(dim_v) for pr in ((0, 1) if pair_ok(c) else (0,))]
 
     def default_config(self):
         from .configs import RetConfig
@@ -139,6 +143,8 @@ class RetBwdTunner(_RetBase):
         super().__init__(arch, torch_array, "retnet_bwd", scale=scale, causal=causal, decay=decay)
 
     def validate_kernel(self, config):
+        if config.cta_pair and not pair_ok(config.dv_chunk, config.dq_chunk):
+            return False
         return (config.Kd % 64 == 0 and config.D % 64 == 0 and config.D <= 512 and config.D % config.dv_chunk == 0
                 and config.Kd % config.dq_chunk == 0 and config.smem_bytes() <= self.arch.smem_cap + 1024
                 and config.tmem_columns() <= getattr(self.arch, "tmem_columns", 512) and config.ring_slots() >= 3)
@@ -147,8 +153,8 @@ class RetBwdTunner(_RetBase):
         if Br != 128:
             return []
         from .configs import RetBwdConfig
-        return [RetBwdConfig(Br, Bc, dim_qk, dim_v, dv_chunk=cv, dq_chunk=cq, dtype=self.dtype)
-                for cv in _chunks(dim_v) for cq in _chunks(dim_qk)]
+        return [RetBwdConfig(Br, Bc, dim_qk, dim_v, dv_chunk=cv, dq_chunk=cq, cta_pair=pr, dtype=self.dtype)
+                for cv in _chunks(dim_v) for cq in _chunks(dim_qk) for pr in ((0, 1) if pair_ok(cv, cq) else (0,))]
 
     def default_config(self):
         from .configs import RetBwdConfig

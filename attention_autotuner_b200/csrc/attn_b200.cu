@@ -7,6 +7,7 @@
 #include "chain_launch.cuh"
 #include "fa_fwd_launch.cuh"
 #include "selftest.cuh"
+#include "selftest_pair.cuh"
 
 using namespace ab200;
 
@@ -56,13 +57,16 @@ int fa_fwd_common(const void* q, const void* k, const void* v, void* o, float* l
 
 // RetNet head-dim pairs built into this library (others: per-config libraries from the tuner).
 constexpr int chunk_of(int d) { return d % 256 == 0 ? 256 : d % 128 == 0 ? 128 : 64; }
+// CTA pairs (cta_group::2, 256-row tiles) wherever the output chunks are wide enough to be split between two CTAs
+constexpr bool pair_of(int chunk_a, int chunk_b) { return chunk_a >= 128 && chunk_b >= 128; }
 
 template <bool BF16, bool BWD>
 int ret_dispatch(const RetArgs& a, cudaStream_t st) {
 #define AB200_RET_CASE(DQK, DV)                                                                        \
   if (a.dqk == DQK && a.dv == DV) {                                                                    \
-    if constexpr (BWD) return ret_bwd_launch<DQK, DV, chunk_of(DV), chunk_of(DQK), BF16>(a, st);       \
-    else return ret_fwd_launch<DQK, chunk_of(DV), BF16>(a, st);                                        \
+    if constexpr (BWD)                                                                                 \
+      return ret_bwd_launch<DQK, DV, chunk_of(DV), chunk_of(DQK), BF16, pair_of(chunk_of(DV), chunk_of(DQK))>(a, st); \
+    else return ret_fwd_launch<DQK, chunk_of(DV), BF16, pair_of(chunk_of(DV), 128)>(a, st);              \
   }
   AB200_RET_CASE(64, 64)
   AB200_RET_CASE(64, 128)
@@ -166,6 +170,11 @@ int attn_b200_selftest_gemm_ss(const void* a, const void* b, float* d, int N, in
 }
 int attn_b200_selftest_gemm_ts(const void* p, const void* v, float* d, int N, int dtype, void* stream) {
   return selftest_gemm_ts(p, v, d, N, dtype, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int attn_b200_selftest_pair(const void* a, const void* b, const void* t, float* z, float* d, int K, int N2, int dtype,
+                            void* stream) {
+  return selftest_pair(a, b, t, z, d, K, N2, dtype, reinterpret_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -1,0 +1,131 @@
+// Declarations shared by the two-GEMM chain kernels (single CTA: chain_sm100.cuh, CTA pair:
+// chain_pair_sm100.cuh): work-item description, kernel parameters and the element-wise step
+//     W = Z .* mask .* scale (./ r)
+// that runs between the two GEMMs on one 128 x 128 block held in tensor memory.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace ab200 {
+
+enum ChainMode : int { kChainFwd = 0, kChainRowQ = 1, kChainRowK = 2 };
+
+struct ChainParams {
+  void* out;             // [BH, rows, ld_out] 16-bit; this CTA writes columns [z*N2, z*N2+N2)
+  int ld_out;
+  float* r_out;          // Fwd: [BH, Lq] normaliser r = max(sum_j |S~|, 1), written by z == 0
+  const float* r_in;     // RowQ / RowK: [BH, Lq]
+  const uint16_t* mask;  // general mask [H, Lq, Lkv] (16-bit, same dtype as the operands) or nullptr
+  const float* decay;    // per-head gamma [H] or nullptr (exactly one of mask / decay is set)
+  int H, Lq, Lkv;
+  float scale;
+  int skip_upper;        // 1: blocks strictly above the diagonal are all zero and are skipped
+  // work list of the persistent grid: item w = (bh * ny + chunk) * nrb + row-block index
+  int nrb;               // 128-row blocks on the row side
+  int ny;                // column chunks of the output (n2_total / N2)
+  int total_items;       // nrb * ny * BH
+};
+
+// One unit of work of the persistent chain kernel: a 128-row tile x one output-column chunk of one slice.
+struct ChainItem {
+  int bh, n_off, row0, t_start, n_iter;
+};
+
+// Optional event trace (compile with -DAB200_TRACE), see fa_fwd_sm100.cuh: CTA (0,0,0) only.
+#ifdef AB200_TRACE
+constexpr int kChainTraceIters = 48;
+__device__ long long g_chain_trace[2][kChainTraceIters][8];
+#define AB200_CTR(who, j, ev)                                                                            \
+  do {                                                                                                   \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < kChainTraceIters) g_chain_trace[who][j][ev] = clock64(); \
+  } while (0)
+#else
+#define AB200_CTR(who, j, ev) do {} while (0)
+#endif
+
+// Tags of the bounded waits (reported in the device status detail word)
+enum ChainTag : int {
+  kCtR = 11, kCtSlotFull = 12, kCtSlotEmpty = 13, kCtZFull = 14, kCtWFull = 15, kCtAccDone = 16, kCtAccFree = 17, kCtRFree = 18, kCtZFree = 19
+};
+
+// Element-wise step of one block for the thread that owns TMEM lane (row) `tz >> 16`: reads the 128 fp32
+// values of its row of Z at `tz`, applies the row factor, the mask (general 16-bit tensor, or the decay factor
+// table `cft` with the triangular predicate `dlim` on blocks that straddle the diagonal), and writes the 64
+// packed 16-bit pairs of W over the first 64 columns of the same buffer. The forward accumulates sum |W|.
+//   grow = global row of this thread on the row side, col0 = first global column of the block, h = head.
+template <int MODE, bool GENERAL, bool BF16>
+__device__ __forceinline__ void chain_ew_block(const ChainParams& p, uint32_t tz, const float* cft, float rowf,
+                                               bool straddle, int dlim, int grow, int col0, int h, float& rsum) {
+#pragma unroll
+  for (int qd = 0; qd < 4; ++qd) {
+    uint32_t zr[32];
+    tmem_ld32(tz + qd * 32, zr);
+    float mk[32];
+    if (GENERAL) {
+      if (MODE != kChainRowK) {
+        // row of the mask owned by this thread: M[h, grow, col0 + qd*32 ...], 16-byte vectors
+        const uint16_t* mp = p.mask + (static_cast<size_t>(h) * p.Lq + grow) * p.Lkv + col0 + qd * 32;
+#pragma unroll
+        for (int v8 = 0; v8 < 4; ++v8) {
+          uint4 u = make_uint4(0, 0, 0, 0);
+          if (grow < p.Lq && col0 + qd * 32 + v8 * 8 < p.Lkv) u = __ldg(reinterpret_cast<const uint4*>(mp) + v8);
+          const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            if constexpr (BF16) {
+              mk[v8 * 8 + 2 * e] = __uint_as_float(w4[e] << 16);
+              mk[v8 * 8 + 2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
+            } else {
+              const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w4[e]));
+              mk[v8 * 8 + 2 * e] = f2.x;
+              mk[v8 * 8 + 2 * e + 1] = f2.y;
+            }
+          }
+        }
+      } else {
+        // column of the mask: M[h, col0 + c, grow]; consecutive threads read consecutive keys
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int qi = col0 + qd * 32 + c;
+          uint16_t u = 0;
+          if (qi < p.Lq && grow < p.Lkv) u = __ldg(p.mask + (static_cast<size_t>(h) * p.Lq + qi) * p.Lkv + grow);
+          if constexpr (BF16) {
+            mk[c] = __uint_as_float(static_cast<uint32_t>(u) << 16);
+          } else {
+            mk[c] = __half2float(__ushort_as_half(u));
+          }
+        }
+      }
+    }
+    tc_wait_ld();
+    uint32_t pk[16];
+#pragma unroll
+    for (int c = 0; c < 32; c += 2) {
+      float w0 = __uint_as_float(zr[c]) * rowf;
+      float w1 = __uint_as_float(zr[c + 1]) * rowf;
+      if (GENERAL) {
+        w0 *= mk[c];
+        w1 *= mk[c + 1];
+      }
+      if (MODE == kChainRowK || (!GENERAL)) {
+        w0 *= cft[qd * 32 + c];
+        w1 *= cft[qd * 32 + c + 1];
+      }
+      if (straddle) {
+        const int cc = qd * 32 + c;
+        if (MODE == kChainRowK) {
+          if (cc < dlim) w0 = 0.f;
+          if (cc + 1 < dlim) w1 = 0.f;
+        } else {
+          if (cc > dlim) w0 = 0.f;
+          if (cc + 1 > dlim) w1 = 0.f;
+        }
+      }
+      if (MODE == kChainFwd) rsum += fabsf(w0) + fabsf(w1);
+      pk[c >> 1] = pack2<BF16>(w0, w1);
+    }
+    tmem_st16(tz + qd * 16, pk);
+  }
+}
+
+}  // namespace ab200

@@ -7,6 +7,7 @@
 
 #include <type_traits>
 
+#include "chain_pair_sm100.cuh"
 #include "chain_sm100.cuh"
 #include "fa_fwd_launch.cuh"  // profile_loop
 #include "host_common.cuh"
@@ -87,6 +88,61 @@ int chain_launch(const void* R, int r_len, const void* C, int c_len, const void*
   return check_launch(what);
 }
 
+// One launch of the CTA-pair chain kernel: clusters of two CTAs, each cluster a 256-row tile. The persistent grid
+// holds as many clusters as can be resident at once (asked from the occupancy API, since pairs need both SMs
+// of a TPC), reduced to a count coprime to the period of the work list.
+template <class Cfg>
+int chain_pair_launch(const void* R, int r_len, const void* C, int c_len, const void* T, int n2_total, ChainParams p, int BH,
+                      cudaStream_t stream, const char* what) {
+  CUtensorMap tr, tc, tt;
+  int rc;
+  if (!aligned32(p.out)) return fail(kErrInvalidArgument, "%s: output tensors must be 32-byte aligned", what);
+  if ((rc = bind_device_of(R, what))) return rc;
+  if ((rc = make_tmap_3d(&tr, R, Cfg::BF16, Cfg::K1, r_len, BH, 64, 128))) return rc;
+  if ((rc = make_tmap_3d(&tc, C, Cfg::BF16, Cfg::K1, c_len, BH, 64, 64))) return rc;
+  if ((rc = make_tmap_3d(&tt, T, Cfg::BF16, n2_total, c_len, BH, 64, 128))) return rc;
+  auto kernel = &chain_pair_sm100_kernel<Cfg>;
+  // The attribute belongs to this library's copy of the kernel and is set on every launch: a function-local
+  // static of a template is one object per PROCESS (unique symbol), shared by every loaded library that holds
+  // the same instantiation, so it may only cache what is the same for all of them (the occupancy answer).
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+  if (e != cudaSuccess) return fail(kErrCuda, "%s: cudaFuncSetAttribute: %s", what, cudaGetErrorString(e));
+  static int max_clusters = 0;
+  if (max_clusters == 0) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2, 1, 1);
+    cfg.blockDim = dim3(Cfg::NTHREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+    if (e != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      return fail(kErrCuda, "%s: no CTA pair can be resident (%s)", what, e != cudaSuccess ? cudaGetErrorString(e) : "0 clusters");
+    }
+    max_clusters = n;
+  }
+  p.nrb = (r_len + 255) / 256;
+  p.ny = n2_total / Cfg::N2;
+  const long long total = static_cast<long long>(p.nrb) * p.ny * BH;
+  if (total > 0x7fffffffLL) return fail(kErrInvalidArgument, "%s: too many tiles", what);
+  p.total_items = static_cast<int>(total);
+  int clusters = p.total_items < max_clusters ? p.total_items : max_clusters;
+  if (p.total_items > max_clusters) {
+    auto gcd = [](int a, int b) { while (b) { int t = a % b; a = b; b = t; } return a; };
+    for (int g = max_clusters; g > max_clusters / 2; --g)
+      if (gcd(g, p.nrb * p.ny) == 1) { clusters = g; break; }
+  }
+  kernel<<<2 * clusters, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tr, tc, tt, p);
+  return check_launch(what);
+}
+
 inline ChainParams ret_params(const RetArgs& a) {
   ChainParams p{};
   p.mask = reinterpret_cast<const uint16_t*>(a.mask);
@@ -99,8 +155,19 @@ inline ChainParams ret_params(const RetArgs& a) {
   return p;
 }
 
-// Forward. DQK = head dim of q/k, DVC = columns of V per CTA (divides dv).
-template <int DQK, int DVC, bool BF16>
+// Launch of either family: PAIR = true runs the CTA-pair kernel (N2 must be 128 or 256).
+template <bool PAIR, int K1, int N2, int MODE, bool GENERAL, bool BF16>
+int chain_go(const void* R, int r_len, const void* C, int c_len, const void* T, int n2_total, const ChainParams& p, int BH,
+             cudaStream_t stream, const char* what) {
+  if constexpr (PAIR) {
+    return chain_pair_launch<ChainPairConfig<K1, N2, MODE, GENERAL, BF16>>(R, r_len, C, c_len, T, n2_total, p, BH, stream, what);
+  } else {
+    return chain_launch<ChainConfig<K1, N2, MODE, GENERAL, BF16>>(R, r_len, C, c_len, T, n2_total, p, BH, stream, what);
+  }
+}
+
+// Forward. DQK = head dim of q/k, DVC = columns of V per CTA or CTA pair (divides dv).
+template <int DQK, int DVC, bool BF16, bool PAIR = false>
 int ret_fwd_launch(const RetArgs& a, cudaStream_t stream) {
   int rc = ret_check_common(a, "ret_fwd");
   if (rc) return rc;
@@ -111,13 +178,13 @@ int ret_fwd_launch(const RetArgs& a, cudaStream_t stream) {
   p.ld_out = a.dv;
   p.r_out = a.r;
   if (a.mask)
-    return chain_launch<ChainConfig<DQK, DVC, kChainFwd, true, BF16>>(a.q, a.Lq, a.k, a.Lkv, a.v, a.dv, p, a.BH, stream, "ret_fwd");
-  return chain_launch<ChainConfig<DQK, DVC, kChainFwd, false, BF16>>(a.q, a.Lq, a.k, a.Lkv, a.v, a.dv, p, a.BH, stream, "ret_fwd");
+    return chain_go<PAIR, DQK, DVC, kChainFwd, true, BF16>(a.q, a.Lq, a.k, a.Lkv, a.v, a.dv, p, a.BH, stream, "ret_fwd");
+  return chain_go<PAIR, DQK, DVC, kChainFwd, false, BF16>(a.q, a.Lq, a.k, a.Lkv, a.v, a.dv, p, a.BH, stream, "ret_fwd");
 }
 
 // Backward: dV, dK, dQ as three launches on the same stream. DV = full head dim of v (contraction length
 // of the dK and dQ kernels), DVC / DQC = output columns per CTA of the dV kernel / of the dK and dQ kernels.
-template <int DQK, int DV, int DVC, int DQC, bool BF16>
+template <int DQK, int DV, int DVC, int DQC, bool BF16, bool PAIR = false>
 int ret_bwd_launch(const RetArgs& a, cudaStream_t stream) {
   int rc = ret_check_common(a, "ret_bwd");
   if (rc) return rc;
@@ -131,17 +198,17 @@ int ret_bwd_launch(const RetArgs& a, cudaStream_t stream) {
     ChainParams pv = p;
     pv.out = a.dv_out;
     pv.ld_out = a.dv;
-    int r1 = chain_launch<ChainConfig<DQK, DVC, kChainRowK, G, BF16>>(a.k, a.Lkv, a.q, a.Lq, a.dout, a.dv, pv, a.BH, stream, "ret_bwd dV");
+    int r1 = chain_go<PAIR, DQK, DVC, kChainRowK, G, BF16>(a.k, a.Lkv, a.q, a.Lq, a.dout, a.dv, pv, a.BH, stream, "ret_bwd dV");
     if (r1) return r1;
     ChainParams pk = p;
     pk.out = a.dk;
     pk.ld_out = a.dqk;
-    r1 = chain_launch<ChainConfig<DV, DQC, kChainRowK, G, BF16>>(a.v, a.Lkv, a.dout, a.Lq, a.q, a.dqk, pk, a.BH, stream, "ret_bwd dK");
+    r1 = chain_go<PAIR, DV, DQC, kChainRowK, G, BF16>(a.v, a.Lkv, a.dout, a.Lq, a.q, a.dqk, pk, a.BH, stream, "ret_bwd dK");
     if (r1) return r1;
     ChainParams pq = p;
     pq.out = a.dq;
     pq.ld_out = a.dqk;
-    return chain_launch<ChainConfig<DV, DQC, kChainRowQ, G, BF16>>(a.dout, a.Lq, a.v, a.Lkv, a.k, a.dqk, pq, a.BH, stream, "ret_bwd dQ");
+    return chain_go<PAIR, DV, DQC, kChainRowQ, G, BF16>(a.dout, a.Lq, a.v, a.Lkv, a.k, a.dqk, pq, a.BH, stream, "ret_bwd dQ");
   };
   return a.mask ? go(std::true_type{}) : go(std::false_type{});
 }

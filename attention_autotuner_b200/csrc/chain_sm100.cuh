@@ -33,32 +33,9 @@
 // travel through one ring of 32 KB items (two boxes of 128 rows x 64 columns, 128-byte swizzle).
 #pragma once
 
-#include "ptx.cuh"
+#include "chain_common.cuh"
 
 namespace ab200 {
-
-enum ChainMode : int { kChainFwd = 0, kChainRowQ = 1, kChainRowK = 2 };
-
-struct ChainParams {
-  void* out;             // [BH, rows, ld_out] 16-bit; this CTA writes columns [z*N2, z*N2+N2)
-  int ld_out;
-  float* r_out;          // Fwd: [BH, Lq] normaliser r = max(sum_j |S~|, 1), written by z == 0
-  const float* r_in;     // RowQ / RowK: [BH, Lq]
-  const uint16_t* mask;  // general mask [H, Lq, Lkv] (16-bit, same dtype as the operands) or nullptr
-  const float* decay;    // per-head gamma [H] or nullptr (exactly one of mask / decay is set)
-  int H, Lq, Lkv;
-  float scale;
-  int skip_upper;        // 1: blocks strictly above the diagonal are all zero and are skipped
-  // work list of the persistent grid: item w = (bh * ny + chunk) * nrb + row-block index
-  int nrb;               // 128-row blocks on the row side
-  int ny;                // column chunks of the output (n2_total / N2)
-  int total_items;       // nrb * ny * BH
-};
-
-// One unit of work of the persistent chain kernel: a 128-row tile x one output-column chunk of one slice.
-struct ChainItem {
-  int bh, n_off, row0, t_start, n_iter;
-};
 
 template <int K1_, int N2_, int MODE_, bool GENERAL_, bool BF16_>
 struct ChainConfig {
@@ -88,21 +65,7 @@ struct ChainConfig {
   static_assert(2 * NSLOT + 20 <= 96, "barrier area");
 };
 
-// Optional event trace (compile with -DAB200_TRACE), see fa_fwd_sm100.cuh: CTA (0,0,0) only.
-#ifdef AB200_TRACE
-constexpr int kChainTraceIters = 48;
-__device__ long long g_chain_trace[2][kChainTraceIters][8];
-#define AB200_CTR(who, j, ev)                                                                            \
-  do {                                                                                                   \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < kChainTraceIters) g_chain_trace[who][j][ev] = clock64(); \
-  } while (0)
-#else
-#define AB200_CTR(who, j, ev) do {} while (0)
-#endif
 
-enum ChainTag : int {
-  kCtR = 11, kCtSlotFull = 12, kCtSlotEmpty = 13, kCtZFull = 14, kCtWFull = 15, kCtAccDone = 16, kCtAccFree = 17, kCtRFree = 18, kCtZFree = 19
-};
 
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
@@ -480,76 +443,7 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
       if (tid == 0) AB200_CTR(0, g, 1);
       tc_fence_after();
       const uint32_t tz = tmem_addr(tZ0 + (g & 1) * 128, lane_base, 0);
-#pragma unroll
-      for (int qd = 0; qd < 4; ++qd) {
-        uint32_t zr[32];
-        tmem_ld32(tz + qd * 32, zr);
-        float mk[32];
-        if (GENERAL) {
-          if (MODE != kChainRowK) {
-            // row of the mask owned by this thread: M[h, grow, col0 + qd*32 ...], 16-byte vectors
-            const uint16_t* mp = p.mask + (static_cast<size_t>(h) * p.Lq + grow) * p.Lkv + col0 + qd * 32;
-#pragma unroll
-            for (int v8 = 0; v8 < 4; ++v8) {
-              uint4 u = make_uint4(0, 0, 0, 0);
-              if (grow < p.Lq && col0 + qd * 32 + v8 * 8 < p.Lkv) u = __ldg(reinterpret_cast<const uint4*>(mp) + v8);
-              const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                if constexpr (BF16) {
-                  mk[v8 * 8 + 2 * e] = __uint_as_float(w4[e] << 16);
-                  mk[v8 * 8 + 2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
-                } else {
-                  const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w4[e]));
-                  mk[v8 * 8 + 2 * e] = f2.x;
-                  mk[v8 * 8 + 2 * e + 1] = f2.y;
-                }
-              }
-            }
-          } else {
-            // column of the mask: M[h, col0 + c, grow]; consecutive threads read consecutive keys
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-              const int qi = col0 + qd * 32 + c;
-              uint16_t u = 0;
-              if (qi < p.Lq && grow < p.Lkv) u = __ldg(p.mask + (static_cast<size_t>(h) * p.Lq + qi) * p.Lkv + grow);
-              if constexpr (BF16) {
-                mk[c] = __uint_as_float(static_cast<uint32_t>(u) << 16);
-              } else {
-                mk[c] = __half2float(__ushort_as_half(u));
-              }
-            }
-          }
-        }
-        tc_wait_ld();
-        uint32_t pk[16];
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float w0 = __uint_as_float(zr[c]) * rowf;
-          float w1 = __uint_as_float(zr[c + 1]) * rowf;
-          if (GENERAL) {
-            w0 *= mk[c];
-            w1 *= mk[c + 1];
-          }
-          if (MODE == kChainRowK || decay_mode) {
-            w0 *= cft[qd * 32 + c];
-            w1 *= cft[qd * 32 + c + 1];
-          }
-          if (straddle) {
-            const int cc = qd * 32 + c;
-            if (MODE == kChainRowK) {
-              if (cc < dlim) w0 = 0.f;
-              if (cc + 1 < dlim) w1 = 0.f;
-            } else {
-              if (cc > dlim) w0 = 0.f;
-              if (cc + 1 > dlim) w1 = 0.f;
-            }
-          }
-          if (MODE == kChainFwd) rsum += fabsf(w0) + fabsf(w1);
-          pk[c >> 1] = pack2<BF16>(w0, w1);
-        }
-        tmem_st16(tz + qd * 16, pk);
-      }
+      chain_ew_block<MODE, GENERAL, BF16>(p, tz, cft, rowf, straddle, dlim, grow, col0, h, rsum);
       if (MODE == kChainFwd && t + 1 == n_iter) {
         // hand the row sums to the epilogue warpgroup (single buffer: the previous item's epilogue, which
         // signals acc_free after reading it, must be through)

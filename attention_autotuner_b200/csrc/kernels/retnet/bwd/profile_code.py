@@ -14,7 +14,7 @@ static int run(const void* q, const void* k, const void* v, const void* mask, co
   a.q = q; a.k = k; a.v = v; a.mask = mask; a.decay = decay; a.r = const_cast<float*>(r);
   a.dout = dout; a.dq = dq; a.dk = dk; a.dv_out = dv;
   a.BH = B * H; a.H = H; a.Lq = Seq_q; a.Lkv = Seq_k; a.dqk = {Kd}; a.dv = {D}; a.scale = scale; a.causal = causal;
-  return ret_bwd_launch<{Kd}, {D}, {dv_chunk}, {dq_chunk}, {bf16}>(a, reinterpret_cast<cudaStream_t>(stream));
+  return ret_bwd_launch<{Kd}, {D}, {dv_chunk}, {dq_chunk}, {bf16}, {cta_pair_bool}>(a, reinterpret_cast<cudaStream_t>(stream));
 }}
 extern "C" const char* last_error() {{ return error_buffer(); }}
 extern "C" int device_status(int clear) {{ int det = 0; return read_device_status(clear, &det); }}

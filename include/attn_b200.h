@@ -108,6 +108,15 @@ float attn_b200_ret_bwd_profile(const void* q, const void* k, const void* v, con
 int attn_b200_selftest_gemm_ss(const void* a, const void* b, float* d, int N, int K, int dtype, void* stream);
 int attn_b200_selftest_gemm_ts(const void* p, const void* v, float* d, int N, int dtype, void* stream);
 
+/*
+ * CTA-pair building block (one cluster of two CTAs, tcgen05 cta_group::2), the RetNet chain in miniature:
+ *   z[256,128] = a[256,K] * b[128,K]^T     K in {64,128,192,256}
+ *   d[256,N2]  = w[256,128] * t[128,N2]    w = 16-bit copy of z kept in tensor memory, N2 in {128,256}
+ * a, b, t are 16-bit (dtype), z and d fp32. No counterpart in the reference.
+ */
+int attn_b200_selftest_pair(const void* a, const void* b, const void* t, float* z, float* d, int K, int N2, int dtype,
+                            void* stream);
+
 #ifdef __cplusplus
 }
 #endif

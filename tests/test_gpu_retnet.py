@@ -195,6 +195,31 @@ def test_python_operator_forward_backward(lib):
         assert oracle.within(oracle.error_stats(a.cpu(), b), "fp16", scale_by_peak=True)
 
 
+@pytest.mark.parametrize("pair", [0, 1])
+def test_cta_pair_knob_through_the_tuner_runtime(pair, tmp_path):
+    """The same problem through per-config libraries with and without CTA pairs (cta_group::2 on 256-row
+    tiles): both must meet the oracle; lengths are not multiples of 256, so the second CTA of the last pair
+    owns a partly (forward: 72 rows) filled tile."""
+    from attention_autotuner_b200.autotuner.configs import RetBwdConfig, RetConfig
+    from attention_autotuner_b200.autotuner.runtime import Runtime
+    B, H, L, dqk, dv = 1, 2, 456, 128, 256
+    q, k, v, do, _ = rand_case(23, B, H, L, L, dqk, dv)
+    gam = oracle.decay_gammas(H)
+    qd, kd, vd, dod = (t.cuda() for t in (q, k, v, do))
+    o = torch.full((B, H, L, dv), float("nan"), device="cuda", dtype=torch.float16)
+    r = torch.full((B, H, L), float("nan"), device="cuda")
+    dq, dk, dvo = torch.full_like(qd, float("nan")), torch.full_like(kd, float("nan")), torch.full_like(vd, float("nan"))
+    dec = gam.float().cuda()
+    fwd = Runtime(B200(), RetConfig(128, 128, dqk, dv, dv_chunk=128, cta_pair=pair), tmp_dir=str(tmp_path))
+    bwd = Runtime(B200(), RetBwdConfig(128, 128, dqk, dv, dv_chunk=256, dq_chunk=128, cta_pair=pair), tmp_dir=str(tmp_path))
+    fwd.apply([qd, kd, vd, None, o, r], scale=0.1, causal=True, decay=dec)
+    bwd.apply([qd, kd, vd, None, dod, r, dq, dk, dvo, None], scale=0.1, causal=True, decay=dec)
+    torch.cuda.synchronize()
+    assert fwd.device_status() == 0 and bwd.device_status() == 0
+    m = oracle.decay_mask(H, L, L, gam)
+    check_all((o.cpu(), r.cpu(), dq.cpu(), dk.cpu(), dvo.cpu()), q, k, v, do, m, 0.1)
+
+
 def test_argument_errors(lib):
     x = torch.zeros(1, 1, 128, 64, device="cuda", dtype=torch.float16)
     r = torch.zeros(1, 1, 128, device="cuda")
