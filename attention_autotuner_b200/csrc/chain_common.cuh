@@ -53,11 +53,14 @@ enum ChainTag : int {
 // table `cft` with the triangular predicate `dlim` on blocks that straddle the diagonal), and writes the 64
 // packed 16-bit pairs of W over the first 64 columns of the same buffer. The forward accumulates sum |W|.
 //   grow = global row of this thread on the row side, col0 = first global column of the block, h = head.
-template <int MODE, bool GENERAL, bool BF16>
+// QD0..QD1 selects the 32-column chunks this thread handles (all four by default). With SPLITW two threads share
+// a row (chunks 0-1 and 2-3) and each keeps its 32 packed W columns inside its own half of the buffer: W of
+// chunks 0-1 at columns [0,32), of chunks 2-3 at [64,96).
+template <int MODE, bool GENERAL, bool BF16, int QD0 = 0, int QD1 = 4, bool SPLITW = false>
 __device__ __forceinline__ void chain_ew_block(const ChainParams& p, uint32_t tz, const float* cft, float rowf,
                                                bool straddle, int dlim, int grow, int col0, int h, float& rsum) {
 #pragma unroll
-  for (int qd = 0; qd < 4; ++qd) {
+  for (int qd = QD0; qd < QD1; ++qd) {
     uint32_t zr[32];
     tmem_ld32(tz + qd * 32, zr);
     float mk[32];
@@ -124,8 +127,94 @@ __device__ __forceinline__ void chain_ew_block(const ChainParams& p, uint32_t tz
       if (MODE == kChainFwd) rsum += fabsf(w0) + fabsf(w1);
       pk[c >> 1] = pack2<BF16>(w0, w1);
     }
-    tmem_st16(tz + qd * 16, pk);
+    tmem_st16(tz + (SPLITW ? (qd >> 1) * 64 + (qd & 1) * 16 : qd * 16), pk);
   }
+}
+
+// The same step for the decay flavours (no mask tensor), two 32-column chunks (QD0, QD0 + 1) per call, written for
+// instruction count and without shared-memory reads. Measured alone on one SM, cycles per 128 x 128 block
+// with two threads per row: 980 for the loop above; 534 for this version; and with SS MMAs streaming their
+// operands from shared memory on the same SM the loop above (one broadcast table read per 4 columns) took
+// 2611 cycles against 550 here: the tensor core saturates the shared-memory bandwidth and starves LDS.
+//   * Fwd / RowQ: the column factor gamma^(-c) is a running product, two columns per packed multiply,
+//     restarted from an exact value at every chunk (32 steps of fp32 rounding at most);
+//   * RowK: the column factor gamma^c / r[c] of column (chunk, lane) sits in a register of that lane
+//     (colf0 / colf1 for the two chunks) and travels by warp shuffle;
+//   * both TMEM loads are issued before the first wait; the row sum uses four independent accumulators.
+// rowf is the per-row factor; lg = log2(gamma).
+template <int MODE, bool BF16, int QD0, bool SPLITW>
+__device__ __forceinline__ void chain_ew_decay2(uint32_t tz, float rowf, float lg, float colf0, float colf1, bool straddle,
+                                                int dlim, float& rsum) {
+  uint32_t zr[2][32];
+  tmem_ld32(tz + QD0 * 32, zr[0]);
+  tmem_ld32(tz + (QD0 + 1) * 32, zr[1]);
+  const uint64_t rf2 = f2_pack(rowf, rowf);
+  const float ginv = exp2f(-lg);
+  const uint64_t step2 = f2_pack(ginv * ginv, ginv * ginv);
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  tc_wait_ld();
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    uint32_t pk[16];
+    uint64_t g = 0;
+    if (MODE != kChainRowK) {
+      const float f0 = rowf * exp2f(-((QD0 + q) * 32) * lg);
+      g = f2_pack(f0, f0 * ginv);
+    }
+    const float colf = q == 0 ? colf0 : colf1;
+#pragma unroll
+    for (int c4 = 0; c4 < 8; ++c4) {
+      uint64_t a = f2_pack(__uint_as_float(zr[q][4 * c4]), __uint_as_float(zr[q][4 * c4 + 1]));
+      uint64_t b = f2_pack(__uint_as_float(zr[q][4 * c4 + 2]), __uint_as_float(zr[q][4 * c4 + 3]));
+      if (MODE == kChainRowK) {
+        const float fa = __shfl_sync(0xffffffffu, colf, 4 * c4), fb = __shfl_sync(0xffffffffu, colf, 4 * c4 + 1);
+        const float fc = __shfl_sync(0xffffffffu, colf, 4 * c4 + 2), fd = __shfl_sync(0xffffffffu, colf, 4 * c4 + 3);
+        a = fmul2(fmul2(a, rf2), f2_pack(fa, fb));
+        b = fmul2(fmul2(b, rf2), f2_pack(fc, fd));
+      } else {
+        a = fmul2(a, g);
+        g = fmul2(g, step2);
+        b = fmul2(b, g);
+        g = fmul2(g, step2);
+      }
+      float w0, w1, w2, w3;
+      f2_unpack(a, w0, w1);
+      f2_unpack(b, w2, w3);
+      if (straddle) {  // warp-uniform: only blocks on the diagonal pay for the triangular predicate
+        const int cc = (QD0 + q) * 32 + 4 * c4;
+        if (MODE == kChainRowK) {
+          if (cc < dlim) w0 = 0.f;
+          if (cc + 1 < dlim) w1 = 0.f;
+          if (cc + 2 < dlim) w2 = 0.f;
+          if (cc + 3 < dlim) w3 = 0.f;
+        } else {
+          if (cc > dlim) w0 = 0.f;
+          if (cc + 1 > dlim) w1 = 0.f;
+          if (cc + 2 > dlim) w2 = 0.f;
+          if (cc + 3 > dlim) w3 = 0.f;
+        }
+      }
+      if (MODE == kChainFwd) {
+        s0 += fabsf(w0);
+        s1 += fabsf(w1);
+        s2 += fabsf(w2);
+        s3 += fabsf(w3);
+      }
+      pk[2 * c4] = pack2<BF16>(w0, w1);
+      pk[2 * c4 + 1] = pack2<BF16>(w2, w3);
+    }
+    tmem_st16(tz + (SPLITW ? (QD0 >> 1) * 64 + q * 16 : (QD0 + q) * 16), pk);
+  }
+  if (MODE == kChainFwd) rsum += (s0 + s1) + (s2 + s3);
+}
+
+// Column factor of the RowK flavours for the decay mask: gamma^c / r[query col0 + c], for the lane's column of
+// 32-column chunk `chunk` (0 for queries past the end).
+__device__ __forceinline__ float chain_rowk_colf(const ChainParams& p, int bh, int col0, int chunk, int lane, float lg) {
+  const int c = chunk * 32 + lane;
+  const int qi = col0 + c;
+  const float f = (qi < p.Lq) ? 1.0f / p.r_in[static_cast<size_t>(bh) * p.Lq + qi] : 0.f;
+  return f * exp2f(c * lg);
 }
 
 }  // namespace ab200

@@ -94,13 +94,14 @@ int chain_launch(const void* R, int r_len, const void* C, int c_len, const void*
 template <class Cfg>
 int chain_pair_launch(const void* R, int r_len, const void* C, int c_len, const void* T, int n2_total, ChainParams p, int BH,
                       cudaStream_t stream, const char* what) {
-  CUtensorMap tr, tc, tt;
+  CUtensorMap tr, tc, tt, to;
   int rc;
   if (!aligned32(p.out)) return fail(kErrInvalidArgument, "%s: output tensors must be 32-byte aligned", what);
   if ((rc = bind_device_of(R, what))) return rc;
   if ((rc = make_tmap_3d(&tr, R, Cfg::BF16, Cfg::K1, r_len, BH, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tc, C, Cfg::BF16, Cfg::K1, c_len, BH, 64, 64))) return rc;
   if ((rc = make_tmap_3d(&tt, T, Cfg::BF16, n2_total, c_len, BH, 64, 128))) return rc;
+  if ((rc = make_tmap_3d(&to, p.out, Cfg::BF16, p.ld_out, r_len, BH, 64, 128))) return rc;
   auto kernel = &chain_pair_sm100_kernel<Cfg>;
   // The attribute belongs to this library's copy of the kernel and is set on every launch: a function-local
   // static of a template is one object per PROCESS (unique symbol), shared by every loaded library that holds
@@ -139,7 +140,7 @@ int chain_pair_launch(const void* R, int r_len, const void* C, int c_len, const 
     for (int g = max_clusters; g > max_clusters / 2; --g)
       if (gcd(g, p.nrb * p.ny) == 1) { clusters = g; break; }
   }
-  kernel<<<2 * clusters, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tr, tc, tt, p);
+  kernel<<<2 * clusters, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tr, tc, tt, to, p);
   return check_launch(what);
 }
 

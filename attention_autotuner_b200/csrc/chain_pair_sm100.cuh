@@ -3,17 +3,28 @@
 //
 //     Z[256,128]  = R[256,K1] * C_t[128,K1]^T     each CTA: its 128 rows of R, 64 of the 128 rows of C_t
 //     W           = Z .* mask .* scale (./ r)      each CTA: its 128 rows, in its own tensor memory
-//     ACC[256,N2] += W[256,128] * T_t[128,N2]      each CTA: its 128 rows of ACC, N2/2 columns of T_t
+//     ACC[256,N2] += W[256,128] * T_t[128,N2]      each CTA: its 128 rows of ACC, half of the columns of T_t
 //
 // Against the single-CTA kernel every CTA streams half of the C and T bytes per block, so the ring of the
 // same size buffers twice as many blocks (with K1 = 512 the resident tile leaves 96 KB: half a block for one
 // CTA, a whole block for a pair) and the L2 -> SM traffic halves; one MMA instruction drives both SMs, so the
 // issuing thread is no longer a limit.
 //
-// Roles per CTA as in the single-CTA kernel; the MMA warps (4: GEMM1, 5: GEMM2) work in the leader CTA
-// (cluster rank 0) only. Every CTA loads its own halves with plain TMA loads; its scout warp waits for them
-// and arrives on the LEADER's ready barriers (two arrivals per operand group). Completions of MMAs are
-// reported with one tcgen05.commit per CTA that waits for them (own barrier and the peer's, via mapa).
+// 16 warps per CTA:
+//   0-3   element-wise warpgroup A: thread t owns row t, columns [0,64) of the block
+//   4, 5  MMA issuers (GEMM1, GEMM2): leader CTA (cluster rank 0) only, converged warps, one elected lane
+//   6     TMA producer (lane 0): this CTA's halves of the operands, ring of 16 KB items
+//   7     scout: waits for this CTA's ring items and arrives on the LEADER's ready barriers (2 arrivals per group)
+//   8-11  element-wise warpgroup B: row t, columns [64,128)
+//   12-15 epilogue warpgroup: accumulator -> 16-bit -> shared memory -> TMA store
+// Two threads per row halve the latency of the element-wise step, which sits on the critical chain
+// GEMM1(t) -> W(t) -> GEMM2(t) -> GEMM1(t+2) (the block buffers in tensor memory are only two deep).
+// The epilogue stages its output in the ring slots that held the last T tile of the work item (GEMM2 leaves
+// them to the epilogue instead of returning them to the producer) and writes it with TMA stores: per-row
+// global stores from registers (one 32-byte sector per lane) kept the accumulator busy for ~4500 cycles and
+// slowed the element-wise warps of the next item through the shared load/store path.
+// Completions of MMAs are reported with one tcgen05.commit per CTA that waits for them (own barrier and the
+// peer's, via mapa); every CTA loads its own operand halves with plain TMA loads.
 #pragma once
 
 #include "chain_common.cuh"
@@ -24,35 +35,43 @@ namespace ab200 {
 template <int K1_, int N2_, int MODE_, bool GENERAL_, bool BF16_>
 struct ChainPairConfig {
   static constexpr int K1 = K1_;      // contraction length of GEMM1 (multiple of 64, <= 512)
-  static constexpr int N2 = N2_;      // accumulator columns per pair (128 or 256); each CTA streams N2/2 of T
+  static constexpr int N2 = N2_;      // accumulator columns per pair (128 or 256)
   static constexpr int MODE = MODE_;
   static constexpr bool GENERAL = GENERAL_;
   static constexpr bool BF16 = BF16_;
   static constexpr int K1B = K1 / 64;          // boxes per half C tile (64 rows x 64 columns, 8 KB)
-  static constexpr int T2B = N2 / 128;         // boxes per half T tile (128 rows x 64 columns, 16 KB)
   static constexpr int CBOX_BYTES = 64 * 128;
   static constexpr int TBOX_BYTES = 128 * 128;
-  static constexpr int ITEM_BYTES = 32768;     // a ring item: up to 4 C boxes (256 columns of K1) or the half T tile
-  static constexpr int CI = (K1B + 3) / 4;     // ring items per half C tile
-  static constexpr int TI = 1;
+  static constexpr int ITEM_BYTES = 16384;     // a ring item: two C boxes (128 columns of K1) or one T box (64 columns)
+  static constexpr int CI = (K1B + 1) / 2;     // ring items per half C tile
+  static constexpr int TI = N2 / 128;          // ring items per half T tile: item j feeds ACC columns [128j, 128j+128)
   static constexpr int R_BYTES = 128 * K1 * 2;
   static constexpr int AUX_BYTES = 2048;
   static constexpr int NSLOT_FIT = (232448 - 1024 - AUX_BYTES - R_BYTES) / ITEM_BYTES;
-  static constexpr int NSLOT = NSLOT_FIT > 6 ? 6 : NSLOT_FIT;
+  static constexpr int NSLOT = NSLOT_FIT > 12 ? 12 : NSLOT_FIT;
+  static constexpr int NREADY = 8;             // depth of the ready-barrier rings (groups of up to two items)
   static constexpr int SMEM_BYTES = 1024 + R_BYTES + NSLOT * ITEM_BYTES + AUX_BYTES;
-  static constexpr int NTHREADS = 384;
+  // Output staging of the epilogue: 2 * TI boxes of 16 KB. With a deep ring the boxes of a work item are staged at
+  // once, in the slots of its last T tile and of the first TI items of its last C tile; with a shallow ring
+  // (K1 = 512) in two rounds through the T slots only, so that the next item's first C tile is not held up.
+#ifndef AB200_PAIR_ONE_ROUND
+#define AB200_PAIR_ONE_ROUND 1
+#endif
+  static constexpr bool ONE_ROUND = AB200_PAIR_ONE_ROUND && (CI >= TI) && (NSLOT >= 2 * (CI + TI));
+  static constexpr int NTHREADS = 512;
   static constexpr int TMEM_COLS = 512;  // 2 x 128 (Z) + N2
   static_assert(K1 % 64 == 0 && K1 >= 64 && K1 <= 512, "K1");
   static_assert(N2 == 128 || N2 == 256, "N2");
-  static_assert(NSLOT >= 3, "ring too small");
-  static_assert(2 * NSLOT + 24 <= 96, "barrier area");
+  static_assert(NSLOT >= CI + TI, "ring too small");
+  static_assert(1536 + (2 * NSLOT + 2 * NREADY + 14) * 8 + 16 <= AUX_BYTES, "barrier area");
 };
 
 template <class Cfg>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg::NTHREADS, 1)
 chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constant__ CUtensorMap tmC,
-                        const __grid_constant__ CUtensorMap tmT, const ChainParams p) {
-  constexpr int K1B = Cfg::K1B, T2B = Cfg::T2B, N2 = Cfg::N2, NSLOT = Cfg::NSLOT, MODE = Cfg::MODE;
+                        const __grid_constant__ CUtensorMap tmT, const __grid_constant__ CUtensorMap tmO,
+                        const ChainParams p) {
+  constexpr int K1B = Cfg::K1B, N2 = Cfg::N2, NSLOT = Cfg::NSLOT, MODE = Cfg::MODE, NREADY = Cfg::NREADY;
   constexpr int CI = Cfg::CI, TI = Cfg::TI, ITEM = Cfg::ITEM_BYTES;
   constexpr bool GENERAL = Cfg::GENERAL, BF16 = Cfg::BF16;
   constexpr int CBOX = Cfg::CBOX_BYTES, TBOX = Cfg::TBOX_BYTES;
@@ -68,18 +87,18 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
   // CTAs arrive on it.
   uint64_t* r_full = bars;                    // own    [1] resident tile landed (transaction count)
   uint64_t* slot_full = bars + 1;             // own    [NSLOT]
-  uint64_t* slot_empty = slot_full + NSLOT;   // own    [NSLOT] MMAs that read the slot completed (commit from the leader)
+  uint64_t* slot_empty = slot_full + NSLOT;   // own    [NSLOT] slot may be refilled (commit from the leader, or the own epilogue)
   uint64_t* z_full = slot_empty + NSLOT;      // own    [2] GEMM1 of a block complete
-  uint64_t* w_full = z_full + 2;              // leader [2] W written by the 256 element-wise threads of the pair
+  uint64_t* w_full = z_full + 2;              // leader [2] W written by the 512 element-wise threads of the pair
   uint64_t* acc_done = w_full + 2;            // own    [1] GEMM2 of a work item complete
   uint64_t* acc_free = acc_done + 1;          // leader [1] accumulators drained by the 256 epilogue threads
   uint64_t* r_free = acc_free + 1;            // own    [1] GEMM1 of a work item complete: R may be overwritten
   uint64_t* z_free = r_free + 1;              // leader [2] GEMM2 of a block complete: its Z/W buffer may be rewritten
-  uint64_t* c_ready = z_free + 2;             // leader [4] a C operand group landed in both CTAs (2 arrivals)
-  uint64_t* t_ready = c_ready + 4;            // leader [4] same for a T tile
-  uint64_t* r_ready = t_ready + 4;            // leader [1] resident tiles of both CTAs landed (2 arrivals)
-  uint64_t* rs_free = r_ready + 1;            // own    [1] forward: row sums read by the own epilogue (128 arrivals)
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(rs_free + 1);
+  uint64_t* r_ready = z_free + 2;             // leader [1] resident tiles of both CTAs landed (2 arrivals)
+  uint64_t* rs_free = r_ready + 1;            // own    [1] forward: row sums consumed by the own epilogue (128 arrivals)
+  uint64_t* c_ready = rs_free + 1;            // leader [NREADY] a C operand group landed in both CTAs (2 arrivals)
+  uint64_t* t_ready = c_ready + NREADY;       // leader [NREADY] same for a T tile
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(t_ready + NREADY);
   CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 1);
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // provably warp-uniform
@@ -122,21 +141,22 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&z_full[i], 1);
-      mbar_init(&w_full[i], 256);
+      mbar_init(&w_full[i], 512);
       mbar_init(&z_free[i], 1);
     }
     mbar_init(acc_done, 1);
     mbar_init(acc_free, 256);
     mbar_init(r_free, 1);
-    for (int i = 0; i < 4; ++i) {
+    mbar_init(r_ready, 2);
+    mbar_init(rs_free, 128);
+    for (int i = 0; i < NREADY; ++i) {
       mbar_init(&c_ready[i], 2);
       mbar_init(&t_ready[i], 2);
     }
-    mbar_init(r_ready, 2);
-    mbar_init(rs_free, 128);
     ab->flag = 0;
     fence_mbar_init();
   }
+  if (threadIdx.x < 128) rs[threadIdx.x] = 0.f;
   if (warp == 4) {
     tmem_alloc2(tmem_base_slot, Cfg::TMEM_COLS);
     tmem_relinquish2();
@@ -145,12 +165,14 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
     tma_prefetch_desc(&tmR);
     tma_prefetch_desc(&tmC);
     tma_prefetch_desc(&tmT);
+    tma_prefetch_desc(&tmO);
   }
   tc_fence_before();
+  __syncthreads();
   cluster_sync();  // the barriers of both CTAs exist before anyone arrives on the peer's
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
-  const uint32_t tZ0 = tmem_base;          // Z buffers at columns [0,128) and [128,256); W overlays the first 64
+  const uint32_t tZ0 = tmem_base;          // Z buffers at columns [0,128) and [128,256); W overlays [0,32) and [64,96)
   const uint32_t tACC = tmem_base + 256;   // [256, 256+N2)
   // leader's copies of the shared barriers, as shared::cluster addresses usable from both CTAs
   const uint32_t l_w_full = mapa_shared(smem_u32(w_full), 0);
@@ -159,8 +181,6 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
   const uint32_t l_t_ready = mapa_shared(smem_u32(t_ready), 0);
   const uint32_t l_r_ready = mapa_shared(smem_u32(r_ready), 0);
 
-  if (warp >= 4 && warp < 8) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
   if (warp == 6) {
     // ------------------------------------------------------------------ TMA producer (own halves)
     if (lane == 0) {
@@ -179,6 +199,7 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
         // the resident tile may be overwritten once GEMM1 of the previous item has completed
         if (kacc > 0) ok = mbar_wait(r_free, (kacc - 1) & 1, ab, kCtRFree);
         if (!ok) break;
+        AB200_CTR(1, kacc, 4);
         mbar_expect_tx(r_full, Cfg::R_BYTES);
 #pragma unroll
         for (int c = 0; c < K1B; ++c) tma_load_3d(sR + c * TBOX, &tmR, r_full, c * 64, it.row0 + rank * 128, it.bh);
@@ -197,22 +218,23 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
             for (int i = 0; i < CI && ok; ++i) {
               const int slot = acquire();
               if (!ok) break;
-              const int nb = (K1B - 4 * i) >= 4 ? 4 : (K1B - 4 * i);
+              const int nb = (K1B - 2 * i) >= 2 ? 2 : 1;
               mbar_expect_tx(&slot_full[slot], nb * CBOX);
               for (int b = 0; b < nb; ++b)
-                tma_load_3d(sRing + slot * ITEM + b * CBOX, &tmC, &slot_full[slot], (4 * i + b) * 64,
+                tma_load_3d(sRing + slot * ITEM + b * CBOX, &tmC, &slot_full[slot], (2 * i + b) * 64,
                             (it.t_start + t) * 128 + rank * 64, it.bh);
               ++bi;
             }
           }
-          if (t >= 1 && ok) {
-            const int slot = acquire();
-            if (!ok) break;
-            mbar_expect_tx(&slot_full[slot], T2B * TBOX);
-            for (int b = 0; b < T2B; ++b)
-              tma_load_3d(sRing + slot * ITEM + b * TBOX, &tmT, &slot_full[slot], it.n_off + rank * (N2 / 2) + b * 64,
+          if (t >= 1) {
+            for (int j = 0; j < TI && ok; ++j) {
+              const int slot = acquire();
+              if (!ok) break;
+              mbar_expect_tx(&slot_full[slot], TBOX);
+              tma_load_3d(sRing + slot * ITEM, &tmT, &slot_full[slot], it.n_off + j * 128 + rank * 64,
                           (it.t_start + t - 1) * 128, it.bh);
-            ++bi;
+              ++bi;
+            }
           }
         }
       }
@@ -225,8 +247,8 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
     }
   } else if (warp == 7) {
     // ------------------------------------------------------------------ scout (own halves -> leader's barriers)
-    // Walks the ring in order, waits for every own item to land and arrives once per operand group on the
-    // leader's ready barrier, which completes when both CTAs have arrived.
+    // Walks the ring in order, waits for every own item to land and arrives once per operand group (up to two
+    // items) on the leader's ready barrier, which completes when both CTAs have arrived.
     bool ok = true;
     int bi = 0;
     int cg = 0, tg = 0, kacc = 0;
@@ -234,7 +256,7 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
       for (int i0 = 0; i0 < nitems && ok; i0 += 2) {
         for (int i = i0; i < nitems && i < i0 + 2 && ok; ++i, ++bi)
           ok = mbar_wait_warp(&slot_full[bi % NSLOT], (bi / NSLOT) & 1, ab, kCtSlotFull);
-        if (ok && elect_one()) mbar_arrive_cluster(ready_base + (counter & 3) * 8);
+        if (ok && elect_one()) mbar_arrive_cluster(ready_base + (counter % NREADY) * 8);
         __syncwarp();
         ++counter;
       }
@@ -244,6 +266,7 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
       const int n = it.n_iter;
       if (n == 0) continue;
       ok = mbar_wait_warp(r_full, kacc & 1, ab, kCtR);
+      if (lane == 0) AB200_CTR(1, kacc, 5);
       if (ok && elect_one()) mbar_arrive_cluster(l_r_ready);
       __syncwarp();
       ++kacc;
@@ -252,15 +275,14 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
         if (t >= 1) post(TI, l_t_ready, tg);
       }
     }
-  }
-  else if ((warp == 4 || warp == 5) && rank == 0) {
+  } else if ((warp == 4 || warp == 5) && rank == 0) {
     // ------------------------------------------------------------------ MMA issuers (leader CTA only)
     // Warp 4 issues GEMM1 (Z), warp 5 GEMM2 (ACC); converged warps, one elected lane issues. Ring items are
     // consumed in a fixed order:  C_0 at b0;  C_t at b0 + CI + (t-1)(CI+TI);  T_t right after C_{t+1}, except
     // the last T_{n-1}, which follows T_{n-2} directly. Both CTAs keep identical rings, so one slot index
     // addresses the operand halves of both.
     constexpr uint32_t idesc_z = umma_idesc(256, 128, BF16, false, false);
-    constexpr uint32_t idesc_acc = umma_idesc(256, N2, BF16, false, true);
+    constexpr uint32_t idesc_acc = umma_idesc(256, 128, BF16, false, true);
     bool ok = true;
     int b0 = 0;    // ring items of earlier work items
     int g0 = 0;    // 128-wide blocks of earlier work items (selects Z buffer and ready barrier)
@@ -274,6 +296,7 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
       if (n == 0) continue;
       if (warp == 4) {
         ok = mbar_wait_warp(r_ready, kacc & 1, ab, kCtR);
+        if (lane == 0) AB200_CTR(1, kacc, 6);
         for (int t = 0; t < n && ok; ++t) {
           const int g = g0 + t;
           if (g >= 2) {
@@ -286,7 +309,7 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
           const int base = b0 + (t == 0 ? 0 : CI + (t - 1) * (CI + TI));
 #pragma unroll
           for (int i0 = 0; i0 < CI; i0 += 2) {
-            ok = mbar_wait_warp(&c_ready[cg & 3], (cg >> 2) & 1, ab, kCtSlotFull);
+            ok = mbar_wait_warp(&c_ready[cg % NREADY], (cg / NREADY) & 1, ab, kCtSlotFull);
             ++cg;
             if (!ok) break;
             tc_fence_after();
@@ -296,18 +319,19 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
                 if (i < CI) {
                   const int slot = (base + i) % NSLOT;
                   const uint32_t a = ring_addr + slot * ITEM;
-                  const int nb = (K1B - 4 * i) >= 4 ? 4 : (K1B - 4 * i);
+                  const int nb = (K1B - 2 * i) >= 2 ? 2 : 1;
 #pragma unroll
-                  for (int b = 0; b < 4; ++b) {
+                  for (int b = 0; b < 2; ++b) {
                     if (b < nb) {
 #pragma unroll
                       for (int ks = 0; ks < 4; ++ks)
-                        umma_ss2(tz, umma_smem_desc(r_addr + (4 * i + b) * TBOX + ks * 32, 16, 1024),
+                        umma_ss2(tz, umma_smem_desc(r_addr + (2 * i + b) * TBOX + ks * 32, 16, 1024),
                                  umma_smem_desc(a + b * CBOX + ks * 32, 16, 1024), idesc_z,
                                  (i > 0 || b > 0 || ks > 0) ? 1u : 0u);
                     }
                   }
-                  tc_commit2_both(&slot_empty[slot]);
+                  // (the first slots of a work item's last C tile may go to the epilogues, like those of its last T tile)
+                  if (!(Cfg::ONE_ROUND && t + 1 == n && i < TI)) tc_commit2_both(&slot_empty[slot]);
                 }
               }
               if (i0 + 2 >= CI) {
@@ -328,23 +352,29 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
             // the first GEMM2 overwrites the accumulators: both epilogues of the previous item must have read them
             ok = mbar_wait_warp(acc_free, (kacc - 1) & 1, ab, kCtAccFree);
             if (!ok) break;
+            if (lane == 0) AB200_CTR(1, kacc, 7);
           }
           ok = mbar_wait_warp(&w_full[g & 1], (g >> 1) & 1, ab, kCtWFull);
           if (!ok) break;
           if (lane == 0) AB200_CTR(1, g, 2);
           const uint32_t tw = tZ0 + (g & 1) * 128;
           const int base = b0 + CI + t * (CI + TI) + (t + 1 < n ? CI : 0);
-          ok = mbar_wait_warp(&t_ready[tg & 3], (tg >> 2) & 1, ab, kCtSlotFull);
+          ok = mbar_wait_warp(&t_ready[tg % NREADY], (tg / NREADY) & 1, ab, kCtSlotFull);
           ++tg;
           if (!ok) break;
           tc_fence_after();
           if (elect_one()) {
-            const int slot = base % NSLOT;
-            const uint32_t a = ring_addr + slot * ITEM;
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-              umma_ts2(tACC, tw + ks * 8, umma_smem_desc(a + ks * 2048, TBOX, 1024), idesc_acc, (t > 0 || ks > 0) ? 1u : 0u);
-            tc_commit2_both(&slot_empty[slot]);
+            for (int j = 0; j < TI; ++j) {
+              const int slot = (base + j) % NSLOT;
+              const uint32_t a = ring_addr + slot * ITEM;
+#pragma unroll
+              for (int ks = 0; ks < 8; ++ks)
+                umma_ts2(tACC + j * 128, tw + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8), umma_smem_desc(a + ks * 2048, TBOX, 1024),
+                         idesc_acc, (t > 0 || ks > 0) ? 1u : 0u);
+              // the slots of the last T tile go to the epilogues (output staging), which hand them back
+              if (t + 1 < n) tc_commit2_both(&slot_empty[slot]);
+            }
             tc_commit2(smem_u32(&z_free[g & 1]));
             if (t + 1 == n) tc_commit2_both(acc_done);
           }
@@ -356,17 +386,22 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
       g0 += n;
       ++kacc;
     }
-  }
-  } else if (warp < 4) {
-    // ------------------------------------------------------------------ element-wise warpgroup (own 128 rows)
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
-    const int tid = threadIdx.x;  // 0..127 = TMEM lane = row of the CTA's tile
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32);
+  } else if (warp < 4 || (warp >= 8 && warp < 12)) {
+    // ------------------------------------------------------------------ element-wise warpgroups (own 128 rows)
+    // Warpgroup hh = 0 (warps 0-3) handles columns [0,64) of every block, hh = 1 (warps 8-11) columns [64,128).
+    const int hh = warp >= 8 ? 1 : 0;
+    const int tid = threadIdx.x & 127;  // TMEM lane = row of the CTA's tile
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32);
     constexpr bool decay_mode = !GENERAL;
+    const int mycol = hh * 64 + (tid & 63);  // column whose factor this thread computes (threads tid < 64)
     bool ok = true;
     int g0 = 0;     // blocks processed before the current work item
     int kacc = 0;   // non-empty work items finished so far
     int kitem = 0;  // work items seen so far (selects the per-item column-factor table)
+    auto wg_sync = [&]() {
+      if (hh == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+      else asm volatile("bar.sync 2, 128;" ::: "memory");
+    };
 
     for (int w = cluster_id; w < p.total_items && ok; w += n_clusters, ++kitem) {
       const ChainItem it = decode(w);
@@ -379,15 +414,11 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
       float rowf_base = p.scale;
       if (decay_mode) rowf_base *= exp2f((MODE == kChainRowK ? -tid : tid) * lg);
       if (MODE == kChainRowQ) rowf_base *= (grow < p.Lq) ? 1.0f / p.r_in[static_cast<size_t>(bh) * p.Lq + grow] : 0.f;
-      const float* cf_item = cf + (kitem & 1) * 128;
-      if (MODE != kChainRowK && decay_mode) {
-        cf[(kitem & 1) * 128 + tid] = exp2f(-tid * lg);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-      }
+      const float* cf_item = cf + (kitem & 1) * 128;  // used by the mask-tensor flavours of RowK only
       float rsum = 0.f;
       if (n_iter == 0) {
         // no block contributes to this tile: zeros (and r = 1 in the forward)
-        if (grow < rows_len) {
+        if (hh == 0 && grow < rows_len) {
           uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + (static_cast<size_t>(bh) * rows_len + grow) * p.ld_out + n_off;
           for (int c = 0; c < N2; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
           if (MODE == kChainFwd && n_off == 0) p.r_out[static_cast<size_t>(bh) * p.Lq + grow] = 1.0f;
@@ -399,14 +430,20 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
         const int g = g0 + t;  // running block index: Z buffer g & 1
         const int col0 = (t_start + t) * 128;
         const float* cft = cf_item;
+        float colf0 = 0.f, colf1 = 0.f;
         if (MODE == kChainRowK) {
-          // column factor: 1/r of the block's queries (times gamma^c under decay)
-          const int qi = col0 + tid;
-          float f = (qi < p.Lq) ? 1.0f / p.r_in[static_cast<size_t>(bh) * p.Lq + qi] : 0.f;
-          if (decay_mode) f *= exp2f(tid * lg);
-          cf[(g & 1) * 128 + tid] = f;
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          cft = cf + (g & 1) * 128;
+          if constexpr (GENERAL) {
+            // column factor table: 1/r of the block's queries
+            if (tid < 64) {
+              const int qi = col0 + mycol;
+              cf[(g & 1) * 128 + mycol] = (qi < p.Lq) ? 1.0f / p.r_in[static_cast<size_t>(bh) * p.Lq + qi] : 0.f;
+            }
+            wg_sync();
+            cft = cf + (g & 1) * 128;
+          } else {
+            colf0 = chain_rowk_colf(p, bh, col0, 2 * hh, lane, lg);
+            colf1 = chain_rowk_colf(p, bh, col0, 2 * hh + 1, lane, lg);
+          }
         }
         float rowf = rowf_base;
         if (decay_mode) rowf *= exp2f((MODE == kChainRowK ? (col0 - row0) : (row0 - col0)) * lg);
@@ -414,81 +451,131 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
         const bool straddle = decay_mode && (MODE == kChainRowK ? (col0 < row0 + 127) : (col0 + 127 > row0));
         const int dlim = grow - col0;
 
-        if (tid == 0) AB200_CTR(0, g, 0);
+        if (tid == 0 && hh == 0) AB200_CTR(0, g, 0);
         ok = mbar_wait_warp(&z_full[g & 1], (g >> 1) & 1, ab, kCtZFull);
         if (!ok) break;
-        if (tid == 0) AB200_CTR(0, g, 1);
+        if (tid == 0 && hh == 0) AB200_CTR(0, g, 1);
         tc_fence_after();
         const uint32_t tz = tmem_addr(tZ0 + (g & 1) * 128, lane_base, 0);
-        chain_ew_block<MODE, GENERAL, BF16>(p, tz, cft, rowf, straddle, dlim, grow, col0, h, rsum);
+        if constexpr (GENERAL) {
+          if (hh == 0) chain_ew_block<MODE, GENERAL, BF16, 0, 2, true>(p, tz, cft, rowf, straddle, dlim, grow, col0, h, rsum);
+          else chain_ew_block<MODE, GENERAL, BF16, 2, 4, true>(p, tz, cft, rowf, straddle, dlim, grow, col0, h, rsum);
+        } else {
+          if (hh == 0) chain_ew_decay2<MODE, BF16, 0, true>(tz, rowf, lg, colf0, colf1, straddle, dlim, rsum);
+          else chain_ew_decay2<MODE, BF16, 2, true>(tz, rowf, lg, colf0, colf1, straddle, dlim, rsum);
+        }
         if (MODE == kChainFwd && t + 1 == n_iter) {
-          // hand the row sums to the own epilogue warpgroup (single buffer: it must have read the previous ones)
+          // both halves add their partial row sums into the (zeroed) buffer the own epilogue reads; it must have
+          // consumed the previous item's sums
           if (kacc > 0) {
             ok = mbar_wait_warp(rs_free, (kacc - 1) & 1, ab, kCtAccFree);
             if (!ok) break;
           }
-          rs[tid] = rsum;
+          atomicAdd(&rs[tid], rsum);
         }
-        if (tid == 0) AB200_CTR(0, g, 2);
+        if (tid == 0 && hh == 0) AB200_CTR(0, g, 2);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive_cluster(l_w_full + (g & 1) * 8);
-        if (tid == 0) AB200_CTR(0, g, 3);
+        if (tid == 0 && hh == 0) AB200_CTR(0, g, 3);
       }
       if (!ok) break;
       g0 += n_iter;
       ++kacc;
     }
-  } else {
+  } else if (warp >= 12) {
     // ------------------------------------------------------------------ epilogue warpgroup (own 128 rows)
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 112;");
-    const int tid = threadIdx.x - 256;
+    // ACC -> scale -> 16-bit -> shared memory (128-byte swizzle, 64-column boxes) -> TMA store, in two rounds of
+    // TI boxes staged in the ring slots of the work item's last T tile.
+    const int tid = threadIdx.x - 384;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32);
     bool ok = true;
     int kacc = 0;
+    int b0 = 0;
     for (int w = cluster_id; w < p.total_items && ok; w += n_clusters) {
       const ChainItem it = decode(w);
-      if (it.n_iter == 0) continue;  // the element-wise warpgroup writes the zeros of an empty tile
-      const int grow = it.row0 + static_cast<int>(rank) * 128 + tid;
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + (static_cast<size_t>(it.bh) * rows_len + grow) * p.ld_out + it.n_off;
+      const int n = it.n_iter;
+      if (n == 0) continue;  // warpgroup A writes the zeros of an empty tile
+      const int row0 = it.row0 + static_cast<int>(rank) * 128;
+      const int grow = row0 + tid;
+      const int tbase = b0 + CI + (n - 1) * (CI + TI);  // ring index of the first item of the last T tile
       ok = mbar_wait_warp(acc_done, kacc & 1, ab, kCtAccDone);
       if (!ok) break;
+      if (tid == 0) AB200_CTR(0, kacc, 4);
       tc_fence_after();
       float osc = 1.0f;
       if (MODE == kChainFwd) {
         const float r = fmaxf(rs[tid], 1.0f);
+        rs[tid] = 0.f;
         mbar_arrive(rs_free);
         osc = 1.0f / r;
         if (it.n_off == 0 && grow < rows_len) p.r_out[static_cast<size_t>(it.bh) * p.Lq + grow] = r;
       }
       const uint32_t ta = tmem_addr(tACC, lane_base, 0);
+      constexpr int NROUND = Cfg::ONE_ROUND ? 1 : 2;
+      constexpr int NBOX = 2 * TI / NROUND;  // 64-column boxes staged per round
+      const int cbase = b0 + (n == 1 ? 0 : CI + (n - 2) * (CI + TI));  // ring index of the first item of the last C tile
+      auto stage_slot = [&](int j) -> int { return ((j < TI ? tbase + j : cbase + (j - TI)) % NSLOT); };
 #pragma unroll
-      for (int c0 = 0; c0 < N2; c0 += 32) {
-        uint32_t rr[32];
-        tmem_ld32(ta + c0, rr);
-        tc_wait_ld();
-        if (c0 + 32 >= N2) {
-          // every column of the accumulator is in registers now: GEMM2 of the next item may overwrite it
-          tc_fence_before();
-          mbar_arrive_cluster(l_acc_free);
+      for (int round = 0; round < NROUND; ++round) {
+        if (round == 1) {
+          // the stores of round 0 must have read the staging slots before they are overwritten
+          if (tid == 0) tma_store_wait_read0();
+          asm volatile("bar.sync 3, 128;" ::: "memory");
         }
-        if (grow < rows_len) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 16) {
-            uint32_t v[8];
+        for (int j = 0; j < NBOX; ++j) {
+          const int box = round * NBOX + j;
+          uint8_t* stage = sRing + stage_slot(j) * ITEM + tid * 128;
 #pragma unroll
-            for (int e = 0; e < 8; ++e)
-              v[e] = pack2<BF16>(__uint_as_float(rr[i + 2 * e]) * osc, __uint_as_float(rr[i + 2 * e + 1]) * osc);
-            st_global_v8(orow + c0 + i, v);
+          for (int half = 0; half < 2; ++half) {
+            uint32_t rr[32];
+            tmem_ld32(ta + box * 64 + half * 32, rr);
+            tc_wait_ld();
+            if (round == NROUND - 1 && j == NBOX - 1 && half == 1) {
+              // every column of the accumulator is in registers now: GEMM2 of the next item may overwrite it
+              tc_fence_before();
+              mbar_arrive_cluster(l_acc_free);
+              if (tid == 0) AB200_CTR(0, kacc, 5);
+            }
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 v;
+              v.x = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 0]) * osc, __uint_as_float(rr[q4 * 8 + 1]) * osc);
+              v.y = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 2]) * osc, __uint_as_float(rr[q4 * 8 + 3]) * osc);
+              v.z = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 4]) * osc, __uint_as_float(rr[q4 * 8 + 5]) * osc);
+              v.w = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 6]) * osc, __uint_as_float(rr[q4 * 8 + 7]) * osc);
+              const int chunk = half * 4 + q4;  // 16-byte chunk of the 128-byte row, XOR-swizzled by the row
+              *reinterpret_cast<uint4*>(stage + ((chunk ^ (tid & 7)) << 4)) = v;
+            }
           }
         }
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 3, 128;" ::: "memory");
+        if (tid == 0 && row0 < rows_len) {  // rows past the end of the tensor are clipped by the store; a tile that lies
+                                            // wholly outside is not stored at all
+#pragma unroll
+          for (int j = 0; j < NBOX; ++j)
+            tma_store_3d(&tmO, sRing + stage_slot(j) * ITEM, it.n_off + (round * NBOX + j) * 64, row0, it.bh);
+          tma_store_commit();
+        }
       }
+      if (tid == 0) {
+        // hand the staging slots back to the producer once the stores have read them
+        tma_store_wait_read0();
+#pragma unroll
+        for (int j = 0; j < NBOX; ++j) mbar_arrive(&slot_empty[stage_slot(j)]);
+        AB200_CTR(0, kacc, 6);
+      }
+      b0 += n * (CI + TI);
       ++kacc;
     }
+    if (tid == 0) tma_store_wait0();  // all output written before the CTA exits
   }
 
   __syncwarp();
   tc_fence_before();
+  __syncthreads();
   cluster_sync();  // no CTA leaves while the other may still arrive on its barriers or its MMAs read this CTA's memory
   if (warp == 4) {
     tc_fence_after();

@@ -399,13 +399,6 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
       float rowf_base = p.scale;
       if (decay_mode) rowf_base *= exp2f((MODE == kChainRowK ? -tid : tid) * lg);
       if (MODE == kChainRowQ) rowf_base *= (grow < p.Lq) ? 1.0f / p.r_in[static_cast<size_t>(bh) * p.Lq + grow] : 0.f;
-      const float* cf_item = cf + (kitem & 1) * 128;
-      if (MODE != kChainRowK && decay_mode) {
-        // gamma^(-c); two tables alternate between work items so that a thread still finishing the previous
-        // item is not overtaken (one named barrier per item keeps the threads within one item of each other)
-        cf[(kitem & 1) * 128 + tid] = exp2f(-tid * lg);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-      }
       float rsum = 0.f;
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + (static_cast<size_t>(bh) * rows_len + grow) * p.ld_out + n_off;
       if (n_iter == 0) {
@@ -420,15 +413,21 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
     for (int t = 0; t < n_iter; ++t) {
       const int g = g0 + t;  // running block index: Z buffer g & 1
       const int col0 = (t_start + t) * 128;
-      const float* cft = cf_item;
+      const float* cft = cf;
+      float colf[4] = {0.f, 0.f, 0.f, 0.f};
       if (MODE == kChainRowK) {
-        // column factor: 1/r of the block's queries (times gamma^c under decay)
-        const int qi = col0 + tid;
-        float f = (qi < p.Lq) ? 1.0f / p.r_in[static_cast<size_t>(bh) * p.Lq + qi] : 0.f;
-        if (decay_mode) f *= exp2f(tid * lg);
-        cf[(g & 1) * 128 + tid] = f;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        cft = cf + (g & 1) * 128;
+        if constexpr (GENERAL) {
+          // column factor table: 1/r of the block's queries (double buffered by block parity; one named barrier
+          // per block keeps the threads within one block of each other)
+          const int qi = col0 + tid;
+          cf[(g & 1) * 128 + tid] = (qi < p.Lq) ? 1.0f / p.r_in[static_cast<size_t>(bh) * p.Lq + qi] : 0.f;
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          cft = cf + (g & 1) * 128;
+        } else {
+          // gamma^c / r[c] of column (chunk, lane) in a register of that lane
+#pragma unroll
+          for (int q = 0; q < 4; ++q) colf[q] = chain_rowk_colf(p, bh, col0, q, lane, lg);
+        }
       }
       float rowf = rowf_base;
       if (decay_mode) rowf *= exp2f((MODE == kChainRowK ? (col0 - row0) : (row0 - col0)) * lg);
@@ -443,7 +442,12 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
       if (tid == 0) AB200_CTR(0, g, 1);
       tc_fence_after();
       const uint32_t tz = tmem_addr(tZ0 + (g & 1) * 128, lane_base, 0);
-      chain_ew_block<MODE, GENERAL, BF16>(p, tz, cft, rowf, straddle, dlim, grow, col0, h, rsum);
+      if constexpr (GENERAL) {
+        chain_ew_block<MODE, GENERAL, BF16>(p, tz, cft, rowf, straddle, dlim, grow, col0, h, rsum);
+      } else {
+        chain_ew_decay2<MODE, BF16, 0, false>(tz, rowf, lg, colf[0], colf[1], straddle, dlim, rsum);
+        chain_ew_decay2<MODE, BF16, 2, false>(tz, rowf, lg, colf[2], colf[3], straddle, dlim, rsum);
+      }
       if (MODE == kChainFwd && t + 1 == n_iter) {
         // hand the row sums to the epilogue warpgroup (single buffer: the previous item's epilogue, which
         // signals acc_free after reading it, must be through)
