@@ -64,11 +64,31 @@ inline int persistent_grid(int total_items, int period) {
   return sms;
 }
 
+// Launch helper: `overlap` marks the kernel as a programmatic dependent of the previous kernel in the stream (it may
+// start while that one drains; the kernels wait for it before they complete).
+#ifndef AB200_PDL
+#define AB200_PDL 1
+#endif
+template <class Kernel, class... Args>
+cudaError_t launch_maybe_overlapped(Kernel kernel, int grid, int block, int smem, cudaStream_t stream, bool overlap, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = (overlap && AB200_PDL) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 // One launch of the chain kernel. r_len / c_len are the lengths of the row / column side; k1 and n2_total
 // the inner extents of the R/C and T tensors.
 template <class Cfg>
 int chain_launch(const void* R, int r_len, const void* C, int c_len, const void* T, int n2_total, ChainParams p, int BH,
-                 cudaStream_t stream, const char* what) {
+                 cudaStream_t stream, const char* what, bool overlap = false) {
   CUtensorMap tr, tc, tt;
   int rc;
   if (!aligned32(p.out)) return fail(kErrInvalidArgument, "%s: output tensors must be 32-byte aligned", what);
@@ -84,16 +104,18 @@ int chain_launch(const void* R, int r_len, const void* C, int c_len, const void*
   const long long total = static_cast<long long>(p.nrb) * p.ny * BH;
   if (total > 0x7fffffffLL) return fail(kErrInvalidArgument, "%s: too many tiles", what);
   p.total_items = static_cast<int>(total);
-  kernel<<<persistent_grid(p.total_items, p.nrb * p.ny), Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tr, tc, tt, p);
+  e = launch_maybe_overlapped(kernel, persistent_grid(p.total_items, p.nrb * p.ny), Cfg::NTHREADS, Cfg::SMEM_BYTES, stream,
+                              overlap, tr, tc, tt, p);
+  if (e != cudaSuccess) return fail(kErrCuda, "%s: %s", what, cudaGetErrorString(e));
   return check_launch(what);
 }
 
 // One launch of the CTA-pair chain kernel: clusters of two CTAs, each cluster a 256-row tile. The persistent grid
 // holds as many clusters as can be resident at once (asked from the occupancy API, since pairs need both SMs
-// of a TPC), reduced to a count coprime to the period of the work list.
+// of a TPC).
 template <class Cfg>
 int chain_pair_launch(const void* R, int r_len, const void* C, int c_len, const void* T, int n2_total, ChainParams p, int BH,
-                      cudaStream_t stream, const char* what) {
+                      cudaStream_t stream, const char* what, bool overlap = false) {
   CUtensorMap tr, tc, tt, to;
   int rc;
   if (!aligned32(p.out)) return fail(kErrInvalidArgument, "%s: output tensors must be 32-byte aligned", what);
@@ -134,13 +156,11 @@ int chain_pair_launch(const void* R, int r_len, const void* C, int c_len, const 
   const long long total = static_cast<long long>(p.nrb) * p.ny * BH;
   if (total > 0x7fffffffLL) return fail(kErrInvalidArgument, "%s: too many tiles", what);
   p.total_items = static_cast<int>(total);
-  int clusters = p.total_items < max_clusters ? p.total_items : max_clusters;
-  if (p.total_items > max_clusters) {
-    auto gcd = [](int a, int b) { while (b) { int t = a % b; a = b; b = t; } return a; };
-    for (int g = max_clusters; g > max_clusters / 2; --g)
-      if (gcd(g, p.nrb * p.ny) == 1) { clusters = g; break; }
-  }
-  kernel<<<2 * clusters, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tr, tc, tt, to, p);
+  // equal-cost super-items (pairs of row blocks) are handed out round-robin: any number of clusters is balanced
+  const int n_super = (p.total_items / p.nrb) * ((p.nrb + 1) / 2);
+  const int clusters = n_super < max_clusters ? n_super : max_clusters;
+  e = launch_maybe_overlapped(kernel, 2 * clusters, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream, overlap, tr, tc, tt, to, p);
+  if (e != cudaSuccess) return fail(kErrCuda, "%s: %s", what, cudaGetErrorString(e));
   return check_launch(what);
 }
 
@@ -159,11 +179,12 @@ inline ChainParams ret_params(const RetArgs& a) {
 // Launch of either family: PAIR = true runs the CTA-pair kernel (N2 must be 128 or 256).
 template <bool PAIR, int K1, int N2, int MODE, bool GENERAL, bool BF16>
 int chain_go(const void* R, int r_len, const void* C, int c_len, const void* T, int n2_total, const ChainParams& p, int BH,
-             cudaStream_t stream, const char* what) {
+             cudaStream_t stream, const char* what, bool overlap = false) {
   if constexpr (PAIR) {
-    return chain_pair_launch<ChainPairConfig<K1, N2, MODE, GENERAL, BF16>>(R, r_len, C, c_len, T, n2_total, p, BH, stream, what);
+    return chain_pair_launch<ChainPairConfig<K1, N2, MODE, GENERAL, BF16>>(R, r_len, C, c_len, T, n2_total, p, BH, stream, what,
+                                                                           overlap);
   } else {
-    return chain_launch<ChainConfig<K1, N2, MODE, GENERAL, BF16>>(R, r_len, C, c_len, T, n2_total, p, BH, stream, what);
+    return chain_launch<ChainConfig<K1, N2, MODE, GENERAL, BF16>>(R, r_len, C, c_len, T, n2_total, p, BH, stream, what, overlap);
   }
 }
 
@@ -204,12 +225,12 @@ int ret_bwd_launch(const RetArgs& a, cudaStream_t stream) {
     ChainParams pk = p;
     pk.out = a.dk;
     pk.ld_out = a.dqk;
-    r1 = chain_go<PAIR, DV, DQC, kChainRowK, G, BF16>(a.v, a.Lkv, a.dout, a.Lq, a.q, a.dqk, pk, a.BH, stream, "ret_bwd dK");
+    r1 = chain_go<PAIR, DV, DQC, kChainRowK, G, BF16>(a.v, a.Lkv, a.dout, a.Lq, a.q, a.dqk, pk, a.BH, stream, "ret_bwd dK", true);
     if (r1) return r1;
     ChainParams pq = p;
     pq.out = a.dq;
     pq.ld_out = a.dqk;
-    return chain_go<PAIR, DV, DQC, kChainRowQ, G, BF16>(a.dout, a.Lq, a.v, a.Lkv, a.k, a.dqk, pq, a.BH, stream, "ret_bwd dQ");
+    return chain_go<PAIR, DV, DQC, kChainRowQ, G, BF16>(a.dout, a.Lq, a.v, a.Lkv, a.k, a.dqk, pq, a.BH, stream, "ret_bwd dQ", true);
   };
   return a.mask ? go(std::true_type{}) : go(std::false_type{});
 }

@@ -166,6 +166,9 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
+  // The next kernel in the stream, if it was launched as a programmatic dependent (the backward's three kernels are
+  // independent of each other), may take over SMs as this kernel's CTAs exit instead of waiting for the whole grid.
+  pdl_launch_dependents();
   const uint32_t tZ0 = tmem_base;          // Z buffers at columns [0,128) and [128,256); W overlays the first 64
   const uint32_t tACC = tmem_base + 256;   // [256, 256+N2)
 
@@ -517,6 +520,9 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
   }
 
   __syncwarp();
+  // A programmatic dependent must not complete before the kernel it overlapped with: completion then stays
+  // ordered along the stream for whatever comes next.
+  if (threadIdx.x == 0) pdl_grid_dependency_wait();
   tc_fence_before();
   __syncthreads();
   if (warp == 4) {

@@ -158,6 +158,15 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, C
 }
 
 // ----------------------------------------------------------------------------------------------
+// Programmatic dependent launch. A kernel launched with the programmatic-stream-serialization attribute may
+// start (as SMs become free) once every CTA of the kernel before it in the stream has executed
+// launch_dependents or exited; grid_dependency_wait blocks until that earlier kernel has completed and its
+// writes are visible. Both are no-ops for a kernel launched the ordinary way.
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ----------------------------------------------------------------------------------------------
 // TMA (tiled bulk tensor copies). Loads complete on an mbarrier (complete_tx bytes); stores use
 // bulk groups. Every x coordinate passed here is a multiple of 64 elements (128 bytes).
 // ----------------------------------------------------------------------------------------------
