@@ -47,21 +47,16 @@ inline int ret_check_common(const RetArgs& a, const char* what) {
   return kOk;
 }
 
-// CTAs of the persistent grid: one per SM (a CTA uses all of shared and tensor memory), reduced to the largest
-// count coprime to `period` (row blocks x column chunks of one slice), so that the round-robin assignment hands
-// every CTA the same mix of light and heavy row blocks.
-inline int persistent_grid(int total_items, int period) {
+// CTAs of the persistent grid: one per SM (a CTA uses all of shared and tensor memory). The kernels hand out
+// equal-cost pairs of row blocks round-robin, so any grid size is balanced.
+inline int persistent_grid(int n_super) {
   static int sms = [] {
     int dev = 0, n = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
       n = 148;
     return n > 0 ? n : 148;
   }();
-  if (total_items <= sms) return total_items;
-  auto gcd = [](int a, int b) { while (b) { int t = a % b; a = b; b = t; } return a; };
-  for (int g = sms; g > sms / 2; --g)
-    if (gcd(g, period) == 1) return g;
-  return sms;
+  return n_super < sms ? n_super : sms;
 }
 
 // Launch helper: `overlap` marks the kernel as a programmatic dependent of the previous kernel in the stream (it may
@@ -104,8 +99,8 @@ int chain_launch(const void* R, int r_len, const void* C, int c_len, const void*
   const long long total = static_cast<long long>(p.nrb) * p.ny * BH;
   if (total > 0x7fffffffLL) return fail(kErrInvalidArgument, "%s: too many tiles", what);
   p.total_items = static_cast<int>(total);
-  e = launch_maybe_overlapped(kernel, persistent_grid(p.total_items, p.nrb * p.ny), Cfg::NTHREADS, Cfg::SMEM_BYTES, stream,
-                              overlap, tr, tc, tt, p);
+  e = launch_maybe_overlapped(kernel, persistent_grid((p.total_items / p.nrb) * ((p.nrb + 1) / 2)), Cfg::NTHREADS,
+                              Cfg::SMEM_BYTES, stream, overlap, tr, tc, tt, p);
   if (e != cudaSuccess) return fail(kErrCuda, "%s: %s", what, cudaGetErrorString(e));
   return check_launch(what);
 }

@@ -99,10 +99,9 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // provably warp-uniform
   const int lane = threadIdx.x & 31;
-  // Persistent grid: CTA c works on items c, c + gridDim.x, ... of the list
-  //   w = (bh * ny + chunk) * nrb + k,   row block = k-th heaviest,
-  // so that the CTAs running at any moment cover a few neighbouring slices (operands shared in L2) and every
-  // CTA gets the same mix of light and heavy row blocks (gridDim.x is chosen coprime to nrb * ny).
+  // Persistent grid. Items are numbered  w = (bh * ny + chunk) * nrb + k,  row block = k-th heaviest, and taken in
+  // an order (decode_step below) in which the CTAs running at any moment cover a few neighbouring slices
+  // (operands shared in L2).
   // Loads, MMAs and element-wise work of consecutive items overlap: the producer prefetches the next item's
   // resident tile as soon as GEMM1 of the current one has finished (r_free), the epilogue of an item runs
   // while GEMM1 of the next one is already in flight, and only the first GEMM2 waits for it (acc_free).
@@ -130,6 +129,22 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
       if (it.n_iter < 0) it.n_iter = 0;
     }
     return it;
+  };
+  // Work list of a CTA. With the blocks above the diagonal skipped the k-th heaviest and the k-th lightest row
+  // block of a slice together always cost the same number of blocks, so the list is made of such pairs
+  // ("super-items", heavy one first) and handed out round-robin: every CTA gets the same work up to one
+  // super-item, whatever the grid size. Step u of a CTA: super-item blockIdx.x + gridDim.x * (u / 2), first or
+  // second member.
+  const int npair = (p.nrb + 1) / 2;
+  const int n_super = (p.total_items / p.nrb) * npair;
+  const int n_steps = static_cast<int>(blockIdx.x) < n_super ? 2 * ((n_super - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+  auto decode_step = [&](int u, ChainItem& it) -> bool {
+    const int sidx = blockIdx.x + gridDim.x * (u >> 1);
+    const int j = sidx % npair;
+    const int k = (u & 1) ? p.nrb - 1 - j : j;
+    if ((u & 1) && k == j) return false;  // the middle row block of an odd count is its own partner
+    it = decode((sidx / npair) * p.nrb + k);
+    return true;
   };
 
   if (threadIdx.x == 0) {
@@ -199,8 +214,9 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
           tma_load_3d(sRing + slot * ITEM + b * BOX, map, &slot_full[slot], x0 + b * 64, y, bh);
         ++bi;
       };
-      for (int w = blockIdx.x; w < p.total_items && ok; w += gridDim.x) {
-        const ChainItem it = decode(w);
+      for (int u = 0; u < n_steps && ok; ++u) {
+        ChainItem it;
+        if (!decode_step(u, it)) continue;
         if (it.n_iter == 0) continue;
         // the resident tile may be overwritten once GEMM1 of the previous item has completed
         if (kacc > 0) ok = mbar_wait(r_free, (kacc - 1) & 1, ab, kCtRFree);
@@ -246,8 +262,9 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
           ++counter;
         }
       };
-      for (int w = blockIdx.x; w < p.total_items && ok; w += gridDim.x) {
-        const ChainItem it = decode(w);
+      for (int u = 0; u < n_steps && ok; ++u) {
+        ChainItem it;
+        if (!decode_step(u, it)) continue;
         const int n = it.n_iter;
         for (int t = 0; t <= n && ok && n > 0; ++t) {
           if (t < n) post(CI, c_ready, cg);
@@ -275,8 +292,9 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
       int cg = 0, tg = 0;  // operand groups consumed so far (as the scout counts them)
       const uint32_t r_addr = smem_u32(sR);
       const uint32_t ring_addr = smem_u32(sRing);
-      for (int w = blockIdx.x; w < p.total_items && ok; w += gridDim.x) {
-        const ChainItem it = decode(w);
+      for (int u = 0; u < n_steps && ok; ++u) {
+        ChainItem it;
+        if (!decode_step(u, it)) continue;
         const int n = it.n_iter;
         if (n == 0) continue;
         if (warp == 4) {
@@ -391,8 +409,9 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
     int kacc = 0;   // non-empty work items finished so far
     int kitem = 0;  // work items seen so far (selects the per-item column-factor table)
 
-    for (int w = blockIdx.x; w < p.total_items && ok; w += gridDim.x, ++kitem) {
-      const ChainItem it = decode(w);
+    for (int u = 0; u < n_steps && ok; ++u, ++kitem) {
+      ChainItem it;
+      if (!decode_step(u, it)) continue;
       const int bh = it.bh, row0 = it.row0, n_off = it.n_off, t_start = it.t_start, n_iter = it.n_iter;
       const int grow = row0 + tid;  // global row index on the row side
       const int h = bh % p.H;
@@ -479,8 +498,9 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32);
     bool ok = true;
     int kacc = 0;
-    for (int w = blockIdx.x; w < p.total_items && ok; w += gridDim.x) {
-      const ChainItem it = decode(w);
+    for (int u = 0; u < n_steps && ok; ++u) {
+      ChainItem it;
+      if (!decode_step(u, it)) continue;
       if (it.n_iter == 0) continue;  // the element-wise warpgroup writes the zeros of an empty tile
       const int grow = it.row0 + tid;
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + (static_cast<size_t>(it.bh) * rows_len + grow) * p.ld_out + it.n_off;

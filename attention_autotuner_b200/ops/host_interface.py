@@ -1,0 +1,140 @@
+"""Host-buffer forms of the two operators: inputs and results live in (pinned) host memory.
+
+    o = flash_attn_host(q, k, v, device_type, causal=False, softmax_scale=None, out=None, device=None)
+    o, dq, dk, dv = retnet_host(q, k, v, device_type, mask=None, decay=None, causal=False, scale=None,
+                                dout=None, outs=None, device=None)      # dout=None: forward only, returns o
+
+The reference has no such entry point: its callers move tensors with ``.cuda()`` / ``.cpu()`` around
+``flash_attn_func`` / ``RetNetAttnFunc`` (python/tests/attntuner_demo.py:50-60). For tensors of benchmark size
+those copies, not the kernels, are the time: at config 2 the kernel takes 1 ms and the copies over PCIe 10 ms.
+Here the batch is cut into chunks that flow through three streams (host -> device copies, the operator, device ->
+host copies), so the two copy directions run at the same time and the kernels disappear under them; the device
+holds a few chunks instead of the whole batch. The operators called per chunk are the public ones of this
+package (same kernels, same tile configurations).
+
+(batch, head) slices are independent, which is what makes the chunking exact; results are bit-identical to one
+call on the whole batch.
+"""
+import torch
+
+from .attention_interface import flash_attn_func
+from .retnet_interface import RetNetAttnFunc
+
+_STREAMS: dict = {}
+
+
+def _streams(dev: torch.device):
+    key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
+    if key not in _STREAMS:
+        _STREAMS[key] = tuple(torch.cuda.Stream(device=dev) for _ in range(3))
+    return _STREAMS[key]
+
+
+def _bounds(batch: int, chunks):
+    n = batch if chunks is None else max(1, min(int(chunks), batch))
+    base, extra = divmod(batch, n)
+    out, b0 = [], 0
+    for i in range(n):
+        b1 = b0 + base + (1 if i < extra else 0)
+        out.append((b0, b1))
+        b0 = b1
+    return out
+
+
+def _check_host(*tensors):
+    for t in tensors:
+        if t is None:
+            continue
+        if t.device.type != "cpu":
+            raise ValueError("host-buffer operators take CPU tensors (pinned memory for asynchronous copies)")
+        if not t.is_contiguous():
+            raise ValueError("host tensors must be contiguous")
+
+
+def _device(device):
+    if not torch.cuda.is_available():
+        raise RuntimeError("a CUDA device is required; there is no CPU path")
+    return torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+
+
+def _host_like(shape, dtype):
+    return torch.empty(shape, dtype=dtype).pin_memory()
+
+
+def flash_attn_host(q, k, v, device_type, causal=False, softmax_scale=None, *, out=None, device=None, chunks=None):
+    """q [B,H,Lq,dqk], k [B,H,Lkv,dqk], v [B,H,Lkv,dv] on the host; returns o [B,H,Lq,dv] on the host (``out`` if
+    given). ``softmax_scale=None`` keeps the reference's 0.125. ``chunks``: pieces of the batch in flight
+    (default: one per batch entry)."""
+    _check_host(q, k, v, out)
+    dev = _device(device)
+    B = q.shape[0]
+    if out is None:
+        out = _host_like((B, q.shape[1], q.shape[2], v.shape[3]), q.dtype)
+    s_in, s_op, s_out = _streams(dev)
+    cur = torch.cuda.current_stream(dev)
+    s_in.wait_stream(cur)
+    s_out.wait_stream(cur)
+    for b0, b1 in _bounds(B, chunks):
+        with torch.cuda.stream(s_in):
+            qd, kd, vd = (t[b0:b1].to(dev, non_blocking=True) for t in (q, k, v))
+            ev_in = s_in.record_event()
+        with torch.cuda.stream(s_op):
+            s_op.wait_event(ev_in)
+            od = flash_attn_func(qd, kd, vd, device_type, causal, softmax_scale)
+            ev_op = s_op.record_event()
+            for t in (qd, kd, vd):
+                t.record_stream(s_op)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_op)
+            out[b0:b1].copy_(od, non_blocking=True)
+            od.record_stream(s_out)
+    cur.wait_stream(s_out)
+    return out
+
+
+def retnet_host(q, k, v, device_type, *, mask=None, decay=None, causal=False, scale=None, dout=None, outs=None,
+                device=None, chunks=None):
+    """RetNet parallel forward (``dout=None``; returns o) or forward + backward (returns o, dq, dk, dv) on host
+    tensors. ``mask`` [H,Lq,Lkv] (host or device; uploaded once) or ``decay`` (H gammas), as RetNetAttnFunc.
+    ``outs``: optional host tensors to receive the results, in the order they are returned."""
+    _check_host(q, k, v, dout)
+    dev = _device(device)
+    B = q.shape[0]
+    backward = dout is not None
+    if outs is None:
+        outs = [_host_like((B, q.shape[1], q.shape[2], v.shape[3]), q.dtype)]
+        if backward:
+            outs += [_host_like(t.shape, t.dtype) for t in (q, k, v)]
+    _check_host(*outs)
+    s_in, s_op, s_out = _streams(dev)
+    cur = torch.cuda.current_stream(dev)
+    for s in (s_in, s_op, s_out):
+        s.wait_stream(cur)
+    with torch.cuda.stream(s_op):
+        maskd = mask.to(dev, non_blocking=True) if mask is not None else None
+        decayd = decay.to(device=dev, dtype=torch.float32) if decay is not None else None
+    for b0, b1 in _bounds(B, chunks):
+        with torch.cuda.stream(s_in):
+            ins = [t[b0:b1].to(dev, non_blocking=True) for t in ((q, k, v, dout) if backward else (q, k, v))]
+            ev_in = s_in.record_event()
+        with torch.cuda.stream(s_op):
+            s_op.wait_event(ev_in)
+            qd, kd, vd = ins[:3]
+            if backward:
+                for t in (qd, kd, vd):
+                    t.requires_grad_(True)
+            od = RetNetAttnFunc(qd, kd, vd, maskd, device_type, causal, scale=scale, decay=decayd)
+            res = [od.detach()]
+            if backward:
+                od.backward(ins[3])
+                res += [qd.grad, kd.grad, vd.grad]
+            ev_op = s_op.record_event()
+            for t in ins:
+                t.record_stream(s_op)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_op)
+            for dst, src in zip(outs, res):
+                dst[b0:b1].copy_(src, non_blocking=True)
+                src.record_stream(s_out)
+    cur.wait_stream(s_out)
+    return tuple(outs) if backward else outs[0]

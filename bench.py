@@ -48,7 +48,7 @@ METRIC = "attn fwd TFLOPS at B=8,H=16,L=4096,d=128 fp16"
 UNIT = "TFLOP/s"
 RETNET = {"C3": "fwd", "C4": "fwd+bwd"}
 # dram__bytes_read.sum + dram__bytes_write.sum per step from the ncu captures summarised under profiles/
-# (fa_fwd_sm100_kernel_C2_fp16.md, chain_sm100_kernel_C4_retnet_fp16.md); None where no capture was taken
+# (fa_fwd_sm100_kernel_C2_fp16.md, chain_pair_sm100_kernel_C4_retnet_fp16.md); None where no capture was taken
 NCU_TRAFFIC_BYTES = {"C2": 518.6e6, "C3": 378.5e6, "C4": 1543.0e6}
 
 
@@ -294,21 +294,17 @@ def main():
             doh = do.cpu().pin_memory()
             gh = [torch.empty(t.shape, dtype=tdt).pin_memory() for t in (q, k, v)]
 
+        from attention_autotuner_b200.ops.host_interface import flash_attn_host, retnet_host
+
         def e2e_step():
-            qd = qh.to(dev, non_blocking=True)
-            kd = kh.to(dev, non_blocking=True)
-            vd = vh.to(dev, non_blocking=True)
+            # host buffers in, host buffers out: the package's host-buffer operators pipeline the copies of the
+            # batch entries with the kernels (three streams); every byte of the step crosses PCIe inside the region
             if not ret:
-                od = flash_attn_func(qd, kd, vd, arch, causal, scale)
+                flash_attn_host(qh, kh, vh, arch, causal, scale, out=oh, device=dev)
+            elif ret == "fwd":
+                retnet_host(qh, kh, vh, arch, decay=gam, causal=True, scale=scale, outs=[oh], device=dev)
             else:
-                if ret == "fwd+bwd":
-                    qd.requires_grad_(True), kd.requires_grad_(True), vd.requires_grad_(True)
-                od = RetNetAttnFunc(qd, kd, vd, None, arch, True, scale=scale, decay=gam)
-                if ret == "fwd+bwd":
-                    od.backward(doh.to(dev, non_blocking=True))
-                    for dst, src in zip(gh, (qd.grad, kd.grad, vd.grad)):
-                        dst.copy_(src, non_blocking=True)
-            oh.copy_(od.detach(), non_blocking=True)
+                retnet_host(qh, kh, vh, arch, decay=gam, causal=True, scale=scale, dout=doh, outs=[oh] + gh, device=dev)
         for _ in range(2):
             e2e_step()
         torch.cuda.synchronize()
@@ -343,7 +339,7 @@ def main():
                          "peak_source": f"{peak_src} (cuBLAS bf16 burst; the timed region is a burst of a few tens of ms)",
                          "peak_sustained": peak_sus, "frac_of_sustained": (achieved / peak_sus if peak_sus else None),
                          "flops_per_step": fl_gpu, "launches_per_step": launches_per_step,
-                         "kernel": "chain_sm100_kernel" if ret else "fa_fwd_sm100_kernel"},
+                         "kernel": "chain_pair_sm100_kernel" if ret else "fa_fwd_sm100_kernel"},
             "clocks": clocks,
             "gpu_launches": launches_per_step * (args.steps + (2 + e2e_steps if e2e_ms is not None else 0)),
         }
@@ -353,8 +349,9 @@ def main():
             d2h = o.numel() * es + ((q.numel() + k.numel() + v.numel()) * es if ret == "fwd+bwd" else 0)
             line["e2e"] = {"value": world * fl_gpu / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
                            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                           "api": "attention_autotuner_b200.ops." + ("retnet_interface.RetNetAttnFunc" if ret
-                                                                      else "attention_interface.flash_attn_func")}
+                           "api": "attention_autotuner_b200.ops.host_interface." + ("retnet_host" if ret else "flash_attn_host")
+                                  + " (per batch entry: " + ("ops.retnet_interface.RetNetAttnFunc" if ret else
+                                                             "ops.attention_interface.flash_attn_func") + ")"}
         if not args.no_cpu_baseline and world == 1:
             r = cpu_reference_run(args.workload, 2, 1, budget_s=15.0)
             line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}

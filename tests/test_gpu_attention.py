@@ -221,3 +221,20 @@ def test_softmax_split_and_exp_emulation_knobs(split, emu, mw, causal):
     torch.cuda.synchronize()
     assert rt.device_status() == 0
     check(o.cpu(), lse.cpu(), q, k, v, 0.11, causal, "fp16")
+
+
+def test_host_buffer_operator_matches_the_device_operator():
+    """flash_attn_host pipelines batch entries through three streams; (batch, head) slices are independent, so the
+    result must be bit-identical to one call on the whole batch, for any chunking."""
+    from attention_autotuner_b200.arch import B200
+    from attention_autotuner_b200.ops.attention_interface import flash_attn_func
+    from attention_autotuner_b200.ops.host_interface import flash_attn_host
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(5, 2, 384, 128, generator=g).half().pin_memory() for _ in range(3))
+    ref = flash_attn_func(q.cuda(), k.cuda(), v.cuda(), B200(), True, 0.1).cpu()
+    for chunks in (None, 2, 1):
+        out = flash_attn_host(q, k, v, B200(), True, 0.1, chunks=chunks)
+        torch.cuda.synchronize()
+        assert torch.equal(out, ref)
+    with pytest.raises(ValueError):
+        flash_attn_host(q.cuda(), k, v, B200())

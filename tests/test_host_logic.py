@@ -140,3 +140,15 @@ def test_per_config_library_builds_and_exports_reference_symbols(tmp_path):
     assert os.path.getmtime(rt.lib_path) == mtime
     with pytest.raises(KernelError):
         rt.apply([torch.zeros(1, 1, 128, 64, dtype=torch.float16)] * 4)  # CPU tensors: no CPU path
+
+
+def test_host_buffer_operators_need_a_gpu_and_split_the_batch_evenly():
+    from attention_autotuner_b200.ops import host_interface as hi
+    assert hi._bounds(8, None) == [(i, i + 1) for i in range(8)]
+    assert hi._bounds(5, 2) == [(0, 3), (3, 5)]
+    assert hi._bounds(3, 10) == [(0, 1), (1, 2), (2, 3)]
+    import torch
+    if not torch.cuda.is_available():
+        x = torch.zeros(1, 1, 128, 64, dtype=torch.float16)
+        with pytest.raises(RuntimeError, match="no CPU path"):
+            hi.flash_attn_host(x, x, x, None)
