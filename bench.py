@@ -49,7 +49,7 @@ UNIT = "TFLOP/s"
 RETNET = {"C3": "fwd", "C4": "fwd+bwd"}
 # dram__bytes_read.sum + dram__bytes_write.sum per step from the ncu captures summarised under profiles/
 # (fa_fwd_sm100_kernel_C2_fp16.md, chain_pair_sm100_kernel_C4_retnet_fp16.md); None where no capture was taken
-NCU_TRAFFIC_BYTES = {"C2": 518.6e6, "C3": 378.5e6, "C4": 1543.0e6}
+NCU_TRAFFIC_BYTES = {"C2": 515.2e6, "C3": 383.6e6, "C4": 1725.3e6}
 
 
 def metric_name(workload):
