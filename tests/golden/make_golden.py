@@ -14,7 +14,9 @@ import sys
 import numpy as np
 import torch
 
-ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_golden.py /path/to/attention_autotuner (a checkout of the reference project)")
+ref_root = sys.argv[1]
 sys.path.insert(0, os.path.join(ref_root, "python"))
 from utils.ref_op import attention_ref, retnet_ref  # noqa: E402  (the reference's module)
 
