@@ -55,7 +55,10 @@ NCU_TRAFFIC_BYTES = {"C2": 515.2e6, "C3": 383.6e6, "C4": 1725.3e6}
 def metric_name(workload):
     if workload in RETNET:
         return "RetNet %s TFLOPS at B=8,H=8,L=2048,dqk=256,dv=512 fp16 (decay mask, unmasked pairs counted)" % RETNET[workload]
-    return METRIC
+    if workload == "C2":
+        return METRIC
+    B, H, Lq, Lkv, dqk, dv, dtype, causal = WORKLOADS[workload]
+    return "attn fwd TFLOPS at B=%d,H=%d,Lq=%d,Lkv=%d,d=%d %s%s" % (B, H, Lq, Lkv, dqk, dtype, " causal" if causal else "")
 
 
 def flops_of(workload):

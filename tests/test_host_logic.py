@@ -152,3 +152,15 @@ def test_host_buffer_operators_need_a_gpu_and_split_the_batch_evenly():
         x = torch.zeros(1, 1, 128, 64, dtype=torch.float16)
         with pytest.raises(RuntimeError, match="no CPU path"):
             hi.flash_attn_host(x, x, x, None)
+
+
+def test_prune_stale_removes_only_libraries_of_other_source_hashes(tmp_path):
+    from attention_autotuner_b200.autotuner.runtime import prune_stale, source_tag
+    keep = tmp_path / f"attn_x_{source_tag()}.so"
+    keep_src = tmp_path / f"attn_x_{source_tag()}.cu"
+    old = tmp_path / "attn_x_0123456789.so"
+    other = tmp_path / "notes.txt"
+    for f in (keep, keep_src, old, other):
+        f.write_text("x")
+    assert prune_stale(str(tmp_path)) == 1
+    assert keep.exists() and keep_src.exists() and other.exists() and not old.exists()
