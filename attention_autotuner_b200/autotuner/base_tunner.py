@@ -44,6 +44,9 @@ def _dtype_name(t: torch.Tensor) -> str:
     return "bf16" if t.dtype == torch.bfloat16 else "fp16"
 
 
+_CACHE_MEMO: dict = {}  # cache file path -> (mtime_ns, parsed configuration or None)
+
+
 class BaseTunner:
     def __init__(self, arch, torch_array: list, op_name, *, scale=None, causal=False, decay=None):
         self.arch = arch
@@ -213,15 +216,23 @@ class BaseTunner:
         old_style = os.path.join(self.cache_path, "best_config_{}_{}_{}.json".format(
             self.op_name, self.problem_key["dim_qk"], self.problem_key["dim_v"]))
         for path in (self._cache_file(), old_style):
-            if os.path.exists(path):
+            try:
+                mtime = os.stat(path).st_mtime_ns
+            except OSError:
+                continue
+            memo = _CACHE_MEMO.get(path)
+            if memo is None or memo[0] != mtime:
+                # parsed once per file version: the operators look the configuration up on every call
                 try:
                     with open(path, "r") as f:
                         d = json.load(f)
-                    cfg = supported_configs[d["operation"]].from_dict(d)
-                    if hasattr(cfg, "dv_chunk") and cfg.dtype == self.dtype:
-                        return cfg
+                    memo = (mtime, supported_configs[d["operation"]].from_dict(d))
                 except (OSError, ValueError, KeyError):
-                    continue
+                    memo = (mtime, None)
+                _CACHE_MEMO[path] = memo
+            cfg = memo[1]
+            if cfg is not None and hasattr(cfg, "dv_chunk") and cfg.dtype == self.dtype:
+                return cfg
         return None
 
     # ------------------------------------------------------------------ hooks

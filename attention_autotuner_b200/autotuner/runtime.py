@@ -62,6 +62,7 @@ def prune_stale(jit_dir: str = None) -> int:
 
 
 _handles: dict = {}
+_built: dict = {}  # (directory, config name) -> library file name
 _handles_lock = threading.Lock()
 
 
@@ -110,11 +111,15 @@ class Runtime:
         self.config = config
         self.tmp_dir = tmp_dir if tmp_dir is not None else DEFAULT_JIT_DIR
         self.libname = libname
-        os.makedirs(self.tmp_dir, exist_ok=True)
         if self.libname is None:
-            self.libname = self.compile()
+            key = (self.tmp_dir, str(config))
+            self.libname = _built.get(key)  # built or found earlier in this process: no file-system calls per launch
             if self.libname is None:
-                raise KernelError(f"nvcc failed for config {config!r} (see {self.tmp_dir})")
+                os.makedirs(self.tmp_dir, exist_ok=True)
+                self.libname = self.compile()
+                if self.libname is None:
+                    raise KernelError(f"nvcc failed for config {config!r} (see {self.tmp_dir})")
+                _built[key] = self.libname
 
     def compile(self, timeout: float = None):
         """Writes <str(config)>.cu and builds <str(config)>.so in tmp_dir (skipped if it exists).

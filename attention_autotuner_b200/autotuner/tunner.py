@@ -97,7 +97,11 @@ class _RetBase(BaseTunner):
         return [ctypes.c_void_p(t.data_ptr() if t is not None else 0) for t in self.torch_array[:n]]
 
     def _key_suffix(self) -> str:
-        return super()._key_suffix() + ("_decay" if self.decay is not None else "")
+        if self.decay is not None:
+            # a decay mask is lower triangular whatever ``causal`` says: one cache entry for both
+            cc = str(getattr(self.arch, "compute_capability", ""))
+            return f"_sm{cc}_{self.dtype}_decay"
+        return super()._key_suffix()
 
     def _pairs_causal(self):
         return self.causal or self.decay is not None

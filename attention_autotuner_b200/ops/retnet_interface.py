@@ -15,6 +15,45 @@ from ..autotuner.runtime import Runtime
 from ..autotuner.tunner import RetBwdTunner, RetTunner
 
 
+def retnet_forward(q, k, v, mask, device_type: Arch, causal=False, scale=None, decay=None):
+    """The forward launch without autograd: returns (o, r, mask, decay) with mask / decay as the kernels took them
+    (contiguous, decay as fp32 on the device). r = max(sum_j |S~|, 1) per row is what the backward needs."""
+    assert q.dtype in (torch.float16, torch.bfloat16) and k.dtype == q.dtype and v.dtype == q.dtype
+    assert (mask is None) != (decay is None), "give either a mask tensor or per-head decay"
+    q, k, v = [x.contiguous() for x in [q, k, v]]
+    batch_size, nheads, seqlen_q, key_dim = q.shape
+    head_dim = v.shape[-1]
+    assert head_dim % 64 == 0 and head_dim <= 512
+    assert key_dim % 64 == 0 and key_dim <= 256
+    maskr = None
+    if mask is not None:
+        assert mask.dtype == q.dtype
+        maskr = mask.detach().contiguous()
+    decayr = None
+    if decay is not None:
+        decayr = decay.detach().to(device=q.device, dtype=torch.float32).contiguous()
+        assert decayr.numel() == nheads
+    o = torch.empty(batch_size, nheads, seqlen_q, head_dim, device=q.device, dtype=q.dtype)
+    r = torch.empty(batch_size, nheads, seqlen_q, device=q.device, dtype=torch.float32)
+    arr = [q, k, v, maskr, o, r]
+    cc = RetTunner(arch=device_type, torch_array=arr, scale=scale, causal=causal, decay=decayr).tune()
+    Runtime(device_type, cc).apply(arr, scale=1.0 if scale is None else scale, causal=causal, decay=decayr)
+    return o, r, maskr, decayr
+
+
+def retnet_backward(q, k, v, mask, do, r, device_type: Arch, causal=False, scale=None, decay=None):
+    """The backward launches without autograd: (dq, dk, dv) from the tensors of retnet_forward. r is a constant
+    (python/utils/ref_op.py:11 detaches it)."""
+    do = do.contiguous()
+    dq = torch.empty_like(q)
+    dk = torch.empty_like(k)
+    dv = torch.empty_like(v)
+    arr = [q, k, v, mask, do, r, dq, dk, dv, None]  # no dq_accum scratch: each output tile has one owner
+    cc = RetBwdTunner(arch=device_type, torch_array=arr, scale=scale, causal=causal, decay=decay).tune()
+    Runtime(device_type, cc).apply(arr, scale=1.0 if scale is None else scale, causal=causal, decay=decay)
+    return dq, dk, dv
+
+
 class RetNetAttn(torch.autograd.Function):
 
     @staticmethod
@@ -22,27 +61,8 @@ class RetNetAttn(torch.autograd.Function):
         causal = bool(opts[0]) if len(opts) > 0 else False
         scale = opts[1] if len(opts) > 1 else None
         decay = opts[2] if len(opts) > 2 else None
-        assert q.dtype in (torch.float16, torch.bfloat16) and k.dtype == q.dtype and v.dtype == q.dtype
-        assert (mask is None) != (decay is None), "give either a mask tensor or per-head decay"
         q, k, v = [x.contiguous() for x in [q, k, v]]
-        batch_size, nheads, seqlen_q, key_dim = q.shape
-        head_dim = v.shape[-1]
-        assert head_dim % 64 == 0 and head_dim <= 512
-        assert key_dim % 64 == 0 and key_dim <= 256
-        maskr = None
-        if mask is not None:
-            assert mask.dtype == q.dtype
-            maskr = mask.detach().contiguous()
-        decayr = None
-        if decay is not None:
-            decayr = decay.detach().to(device=q.device, dtype=torch.float32).contiguous()
-            assert decayr.numel() == nheads
-
-        o = torch.empty(batch_size, nheads, seqlen_q, head_dim, device=q.device, dtype=q.dtype)
-        r = torch.empty(batch_size, nheads, seqlen_q, device=q.device, dtype=torch.float32)
-        arr = [q, k, v, maskr, o, r]
-        cc = RetTunner(arch=device_type, torch_array=arr, scale=scale, causal=causal, decay=decayr).tune()
-        Runtime(device_type, cc).apply(arr, scale=1.0 if scale is None else scale, causal=causal, decay=decayr)
+        o, r, maskr, decayr = retnet_forward(q, k, v, mask, device_type, causal, scale, decay)
         ctx.save_for_backward(q, k, v, maskr, r, decayr)
         ctx.device_type = device_type
         ctx.opts = (causal, scale)
@@ -52,15 +72,8 @@ class RetNetAttn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do):
         q, k, v, mask, r, decay = ctx.saved_tensors
-        device_type = ctx.device_type
         causal, scale = ctx.opts
-        do = do.contiguous()
-        dq = torch.empty_like(q)
-        dk = torch.empty_like(k)
-        dv = torch.empty_like(v)
-        arr = [q, k, v, mask, do, r, dq, dk, dv, None]  # no dq_accum scratch: each output tile has one owner
-        cc = RetBwdTunner(arch=device_type, torch_array=arr, scale=scale, causal=causal, decay=decay).tune()
-        Runtime(device_type, cc).apply(arr, scale=1.0 if scale is None else scale, causal=causal, decay=decay)
+        dq, dk, dv = retnet_backward(q, k, v, mask, do, r, ctx.device_type, causal, scale, decay)
         return (dq, dk, dv, None, None) + (None,) * ctx.n_extra
 
 

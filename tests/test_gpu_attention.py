@@ -232,7 +232,7 @@ def test_host_buffer_operator_matches_the_device_operator():
     g = torch.Generator().manual_seed(5)
     q, k, v = (torch.randn(5, 2, 384, 128, generator=g).half().pin_memory() for _ in range(3))
     ref = flash_attn_func(q.cuda(), k.cuda(), v.cuda(), B200(), True, 0.1).cpu()
-    for chunks in (None, 2, 1):
+    for chunks in (None, 2, 1, 7):
         out = flash_attn_host(q, k, v, B200(), True, 0.1, chunks=chunks)
         torch.cuda.synchronize()
         assert torch.equal(out, ref)

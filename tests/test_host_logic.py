@@ -144,9 +144,14 @@ def test_per_config_library_builds_and_exports_reference_symbols(tmp_path):
 
 def test_host_buffer_operators_need_a_gpu_and_split_the_batch_evenly():
     from attention_autotuner_b200.ops import host_interface as hi
-    assert hi._bounds(8, None) == [(i, i + 1) for i in range(8)]
     assert hi._bounds(5, 2) == [(0, 3), (3, 5)]
     assert hi._bounds(3, 10) == [(0, 1), (1, 2), (2, 3)]
+    assert hi._pieces(2, 4, None) == [(0, 1, 0, 4), (1, 2, 0, 4)]
+    assert hi._pieces(2, 4, 4) == [(0, 1, 0, 2), (0, 1, 2, 4), (1, 2, 0, 2), (1, 2, 2, 4)]
+    assert hi._pieces(1, 3, None) == [(0, 1, 0, 1), (0, 1, 1, 2), (0, 1, 2, 3)]
+    assert hi._pieces(4, 3, 2) == [(0, 2, 0, 3), (2, 4, 0, 3)]
+    assert hi._pieces(2, 1, None) == [(0, 1, 0, 1), (1, 2, 0, 1)]
+    assert hi._pieces(1, 5, 100) == [(0, 1, h, h + 1) for h in range(5)]
     import torch
     if not torch.cuda.is_available():
         x = torch.zeros(1, 1, 128, 64, dtype=torch.float16)
