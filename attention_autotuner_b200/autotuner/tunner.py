@@ -38,6 +38,9 @@ class AttnTunner(BaseTunner):
             return False
         if config.mma_warps == 2 and config.q_tiles != 2:
             return False
+        if config.cta_pair and (config.q_tiles != 2 or config.dv_chunk != 128 or config.softmax_split != 1
+                                or config.exp_emu != 0 or config.mma_warps != 1):
+            return False
         return True
 
     def generate_configs(self, Br: int, Bc: int, dim_qk: int, dim_v: int):
@@ -54,6 +57,10 @@ class AttnTunner(BaseTunner):
                 for split, emu, mw in ((2, 0, 1), (2, 2, 1), (1, 2, 1), (1, 0, 2), (2, 0, 2)):
                     configs.append(AttnConfig(Br, Bc, dim_qk, dim_v, q_tiles=2, kv_stages=4, dv_chunk=dv_chunk,
                                               softmax_split=split, exp_emu=emu, mma_warps=mw, dtype=self.dtype))
+                # CTA pairs (cta_group::2): 512 query rows per cluster
+                for stages in (3, 4):
+                    configs.append(AttnConfig(Br, Bc, dim_qk, dim_v, q_tiles=2, kv_stages=stages, dv_chunk=dv_chunk,
+                                              cta_pair=1, dtype=self.dtype))
         return configs
 
     def default_config(self):

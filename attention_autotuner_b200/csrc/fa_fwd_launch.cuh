@@ -5,6 +5,7 @@
 
 #include <math.h>
 
+#include "fa_fwd_pair_sm100.cuh"
 #include "fa_fwd_sm100.cuh"
 #include "host_common.cuh"
 
@@ -52,6 +53,43 @@ int fa_fwd_launch(const FaFwdArgs& a, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
   if (e != cudaSuccess) return fail(kErrCuda, "fa_fwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   dim3 grid((a.Lq + Cfg::BM * Cfg::NQ - 1) / (Cfg::BM * Cfg::NQ), a.dv / Cfg::DV, a.BH);
+  kernel<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  return check_launch("fa_fwd launch");
+}
+
+// Launcher of the CTA-pair kernel: clusters of two CTAs along x, each cluster a 512-row block of queries.
+template <class Cfg>
+int fa_fwd_pair_launch(const FaFwdArgs& a, cudaStream_t stream) {
+  if (!a.q || !a.k || !a.v || !a.o) return fail(kErrInvalidArgument, "fa_fwd: null tensor pointer");
+  if (a.BH <= 0 || a.Lq <= 0 || a.Lkv <= 0) return fail(kErrInvalidArgument, "fa_fwd: sizes must be positive");
+  if (a.BH > 65535) return fail(kErrInvalidArgument, "fa_fwd: batch*heads %d exceeds 65535", a.BH);
+  if (a.dv % Cfg::DV != 0) return fail(kErrUnsupported, "fa_fwd: dv %d is not a multiple of the tile's %d", a.dv, Cfg::DV);
+  if (!(a.scale > 0.f) || !isfinite(a.scale)) return fail(kErrInvalidArgument, "fa_fwd: scale must be positive and finite");
+  if (!aligned16(a.q) || !aligned16(a.k) || !aligned16(a.v) || !aligned32(a.o))
+    return fail(kErrInvalidArgument, "fa_fwd: inputs must be 16-byte aligned and the output 32-byte aligned");
+
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = bind_device_of(a.q, "fa_fwd"))) return rc;
+  if ((rc = make_tmap_3d(&tq, a.q, Cfg::BF16, Cfg::DQK, a.Lq, a.BH, 64, Cfg::BM))) return rc;
+  if ((rc = make_tmap_3d(&tk, a.k, Cfg::BF16, Cfg::DQK, a.Lkv, a.BH, 64, Cfg::BN / 2))) return rc;  // half of the keys
+  if ((rc = make_tmap_3d(&tv, a.v, Cfg::BF16, a.dv, a.Lkv, a.BH, 64, Cfg::BN))) return rc;          // half of the columns
+
+  FaFwdParams p;
+  p.o = a.o;
+  p.lse = a.lse;
+  p.dv_total = a.dv;
+  p.Lq = a.Lq;
+  p.Lkv = a.Lkv;
+  p.causal = a.causal ? 1 : 0;
+  p.scale = a.scale;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+
+  auto kernel = &fa_fwd_pair_sm100_kernel<Cfg>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+  if (e != cudaSuccess) return fail(kErrCuda, "fa_fwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  const int rows_per_pair = 2 * Cfg::BM * Cfg::NQ;
+  dim3 grid(2 * ((a.Lq + rows_per_pair - 1) / rows_per_pair), a.dv / Cfg::DV, a.BH);
   kernel<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
   return check_launch("fa_fwd launch");
 }

@@ -9,13 +9,13 @@ take scale, causal flag, LSE pointer and stream."""
 global_vars = """
 #include "fa_fwd_launch.cuh"
 using namespace ab200;
-using Cfg = FaFwdConfig<{Kd}, {dv_chunk}, {q_tiles}, {kv_stages}, {bf16}, {exp_emu}, {softmax_split}, {mma_warps}>;
+using Cfg = {cfg_type};
 constexpr int kDv = {D};
 static int run(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H, int Seq_k, int Seq_q,
                float scale, int causal, void* stream) {{
   if (B <= 0 || H <= 0) return fail(kErrInvalidArgument, "B and H must be positive");
   FaFwdArgs a{{q, k, v, o, lse, B * H, Seq_q, Seq_k, kDv, scale, causal}};
-  return fa_fwd_launch<Cfg>(a, reinterpret_cast<cudaStream_t>(stream));
+  return {launcher}<Cfg>(a, reinterpret_cast<cudaStream_t>(stream));
 }}
 extern "C" const char* last_error() {{ return error_buffer(); }}
 extern "C" int device_status(int clear) {{ int det = 0; return read_device_status(clear, &det); }}

@@ -223,6 +223,33 @@ def test_softmax_split_and_exp_emulation_knobs(split, emu, mw, causal):
     check(o.cpu(), lse.cpu(), q, k, v, 0.11, causal, "fp16")
 
 
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("Lq,Lkv", [(512, 512), (640, 384), (200, 328), (1100, 1100)])
+def test_cta_pair_configuration(causal, Lq, Lkv, tmp_path):
+    """Clusters of two CTAs with cta_group::2 MMAs (512 query rows per pair): ragged lengths leave the second CTA of
+    the last pair partly or wholly outside the tensor, causal makes the two CTAs need different block counts."""
+    from attention_autotuner_b200.arch import B200
+    from attention_autotuner_b200.autotuner.configs import AttnConfig
+    from attention_autotuner_b200.autotuner.runtime import Runtime
+    g = torch.Generator().manual_seed(Lq + 3 * Lkv + int(causal))
+    q = torch.randn(1, 3, Lq, 128, generator=g).half()
+    k = torch.randn(1, 3, Lkv, 128, generator=g).half()
+    v = torch.randn(1, 3, Lkv, 256, generator=g).half()
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    o = torch.full((1, 3, Lq, 256), float("nan"), device="cuda", dtype=torch.float16)
+    lse = torch.full((1, 3, Lq), float("nan"), device="cuda")
+    rt = Runtime(B200(), AttnConfig(256, 128, 128, 256, q_tiles=2, kv_stages=4, dv_chunk=128, cta_pair=1), tmp_dir=str(tmp_path))
+    rt.apply([qd, kd, vd, o], scale=0.09, causal=causal, extra_ptrs=(lse.data_ptr(),))
+    torch.cuda.synchronize()
+    assert rt.device_status() == 0
+    oref, lref = oracle.attention_fwd(q, k, v, 0.09, causal)
+    ok_rows = torch.isfinite(lref)
+    st = oracle.error_stats(o.cpu()[ok_rows], oref[ok_rows])
+    assert oracle.within(st, "fp16"), st
+    assert (lse.cpu()[ok_rows] - lref[ok_rows]).abs().max().item() < 1e-3
+    assert not torch.isnan(o).any()
+
+
 def test_host_buffer_operator_matches_the_device_operator():
     """flash_attn_host pipelines batch entries through three streams; (batch, head) slices are independent, so the
     result must be bit-identical to one call on the whole batch, for any chunking."""

@@ -40,7 +40,7 @@ def test_attn_config_legacy_and_new_arguments():
     c.set_fuse_type("shared")
     assert c.fuse_type == "tmem" and c.Br == 128 and c.Bc == 128 and c.q_tiles == 1
     c2 = AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, dtype="bf16")
-    assert str(c2) == "attn_tmem_256_128_128_128_2_4_128_1_0_1_bf16"
+    assert str(c2) == "attn_tmem_256_128_128_128_2_4_128_1_0_1_0_bf16"
     assert c2.tmem_columns() == 512 and c2.smem_bytes() <= B200().smem_cap
     d = json.loads(json.dumps(c2.__dict__))
     c3 = supported_configs[d["operation"]].from_dict(d)
