@@ -468,6 +468,12 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
             colf1 = chain_rowk_colf(p, bh, col0, 2 * hh + 1, lane, lg);
           }
         }
+        uint32_t mk[(GENERAL && MODE != kChainRowK) ? 32 : 1];
+        if constexpr (GENERAL && MODE != kChainRowK) {
+          // the block's mask values of this thread (its row of the mask tensor), fetched before the wait for Z
+          if (hh == 0) chain_mask_prefetch<MODE, 0>(p, h, grow, col0, mk);
+          else chain_mask_prefetch<MODE, 2>(p, h, grow, col0, mk);
+        }
         float rowf = rowf_base;
         if (decay_mode) rowf *= exp2f((MODE == kChainRowK ? (col0 - row0) : (row0 - col0)) * lg);
         //   Fwd/RowQ: column c valid iff col0 + c <= grow ;  RowK: valid iff col0 + c >= grow
@@ -480,7 +486,11 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
         if (tid == 0 && hh == 0) AB200_CTR(0, g, 1);
         tc_fence_after();
         const uint32_t tz = tmem_addr(tZ0 + (g & 1) * 128, lane_base, 0);
-        if constexpr (GENERAL) {
+        if constexpr (GENERAL && MODE != kChainRowK) {
+          if (hh == 0) chain_ew_mask2<MODE, BF16, 0, true>(tz, mk, rowf, rsum);
+          else chain_ew_mask2<MODE, BF16, 2, true>(tz, mk, rowf, rsum);
+        } else if constexpr (GENERAL) {
+          // RowK with a mask tensor: column reads of the mask, chunk by chunk after the wait (see chain_ew_block)
           if (hh == 0) chain_ew_block<MODE, GENERAL, BF16, 0, 2, true>(p, tz, cft, rowf, straddle, dlim, grow, col0, h, rsum);
           else chain_ew_block<MODE, GENERAL, BF16, 2, 4, true>(p, tz, cft, rowf, straddle, dlim, grow, col0, h, rsum);
         } else {
