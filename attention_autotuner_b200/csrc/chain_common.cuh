@@ -236,6 +236,55 @@ __device__ __forceinline__ void chain_mask_prefetch(const ChainParams& p, int h,
   }
 }
 
+// RowK flavours: thread (lane L of its warp) owns key grow0 + L and needs M[h][query][key] for the 64 queries of its
+// two chunks, i.e. a COLUMN of the mask. Reading it with 64 two-byte loads per thread and block cost 0.9 ms of the
+// 1.55 ms backward at config 4 (measured by replacing the loads with a constant). Here the warp reads its
+// 32-query x 32-key tile of every chunk by rows with four 16-byte loads per lane (lane l: key group l / 8, rows
+// 8 i + l % 8) and transposes it in registers: every group of 8 lanes holds an 8 x 8 block of 16-bit values, one row
+// per lane, and exchanges halves three times (lane distance 4, 2, 1; shuffles and byte permutes) until lane j holds
+// column j, packed as (row 2n, row 2n+1) pairs, which is the layout chain_ew_mask2 wants.
+__device__ __forceinline__ void chain_transpose8x8_b16(uint32_t (&r)[4], int lane) {
+  const bool hi = (lane & 4) != 0;
+  // distance 4: swap the 4-column halves; afterwards the lane holds rows (j & 3) and (j & 3) + 4 of 4 columns
+  const uint32_t a0 = __shfl_xor_sync(0xffffffffu, hi ? r[0] : r[2], 4);
+  const uint32_t a1 = __shfl_xor_sync(0xffffffffu, hi ? r[1] : r[3], 4);
+  uint32_t y0 = hi ? a0 : r[0], y1 = hi ? a1 : r[1], y2 = hi ? r[2] : a0, y3 = hi ? r[3] : a1;
+  // distance 2: swap the column pairs; afterwards rows u, u+2, u+4, u+6 (u = j & 1) of one column pair
+  const bool mid = (lane & 2) != 0;
+  const uint32_t b0 = __shfl_xor_sync(0xffffffffu, mid ? y0 : y1, 2);
+  const uint32_t b1 = __shfl_xor_sync(0xffffffffu, mid ? y2 : y3, 2);
+  const uint32_t z0 = mid ? b0 : y0, z1 = mid ? y1 : b0, z2 = mid ? b1 : y2, z3 = mid ? y3 : b1;
+  // distance 1: the even lane keeps the low halves (its column) and sends the high ones, the odd lane the opposite
+  const bool odd = (lane & 1) != 0;
+  const uint32_t c0 = __shfl_xor_sync(0xffffffffu, __byte_perm(z0, z1, odd ? 0x5410 : 0x7632), 1);
+  const uint32_t c1 = __shfl_xor_sync(0xffffffffu, __byte_perm(z2, z3, odd ? 0x5410 : 0x7632), 1);
+  r[0] = __byte_perm(z0, c0, odd ? 0x3254 : 0x5410);  // (row 0 | row 1) of this lane's column
+  r[1] = __byte_perm(z1, c0, odd ? 0x3276 : 0x7610);  // (row 2 | row 3)
+  r[2] = __byte_perm(z2, c1, odd ? 0x3254 : 0x5410);  // (row 4 | row 5)
+  r[3] = __byte_perm(z3, c1, odd ? 0x3276 : 0x7610);  // (row 6 | row 7)
+}
+
+// grow0 = first key of the warp (a multiple of 32); all 32 lanes of the warp must call this together.
+template <int QD0>
+__device__ __forceinline__ void chain_mask_prefetch_rowk(const ChainParams& p, int h, int grow0, int lane, int col0,
+                                                         uint32_t (&mk)[32]) {
+  const int kcol = grow0 + 8 * (lane >> 3);  // first of the 8 keys this lane reads
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int qi = col0 + (QD0 + q) * 32 + 8 * i + (lane & 7);
+      uint4 u = make_uint4(0, 0, 0, 0);
+      if (qi < p.Lq && kcol < p.Lkv)
+        u = __ldg(reinterpret_cast<const uint4*>(p.mask + (static_cast<size_t>(h) * p.Lq + qi) * p.Lkv + kcol));
+      uint32_t r[4] = {u.x, u.y, u.z, u.w};
+      chain_transpose8x8_b16(r, lane);
+#pragma unroll
+      for (int n = 0; n < 4; ++n) mk[q * 16 + 4 * i + n] = r[n];
+    }
+  }
+}
+
 template <bool BF16>
 __device__ __forceinline__ uint64_t chain_unpack_pair(uint32_t packed) {
   if constexpr (BF16) {
@@ -246,13 +295,13 @@ __device__ __forceinline__ uint64_t chain_unpack_pair(uint32_t packed) {
   }
 }
 
-// W = Z * rowf * M for the Fwd / RowQ flavours with a mask tensor, no shared-memory reads; the forward accumulates
-// sum |W|. (Forward at config 4: 0.31-0.32 ms against 0.35 with the loads issued after the wait.) The RowK flavours
-// keep chain_ew_block: their column reads of the mask (32 two-byte loads per chunk) measured twice as slow when
-// packed and fetched this way (backward 3.5 against 1.6 ms).
+// W = Z * rowf * M with a mask tensor (mk: this thread's 64 mask values, packed in pairs, fetched ahead of the wait
+// for Z), no shared-memory reads; the forward accumulates sum |W|. RowK: times 1/r of the column, which travels by
+// shuffle from colf0 / colf1 (one column per lane and chunk) as in chain_ew_decay2.
+// Config 4 with a mask tensor: forward 0.31 against 0.35 ms with the loads issued after the wait.
 template <int MODE, bool BF16, int QD0, bool SPLITW>
-__device__ __forceinline__ void chain_ew_mask2(uint32_t tz, const uint32_t (&mk)[32], float rowf, float& rsum) {
-  static_assert(MODE != kChainRowK, "row reads only");
+__device__ __forceinline__ void chain_ew_mask2(uint32_t tz, const uint32_t (&mk)[32], float rowf, float colf0, float colf1,
+                                               float& rsum) {
   uint32_t zr[2][32];
   tmem_ld32(tz + QD0 * 32, zr[0]);
   tmem_ld32(tz + (QD0 + 1) * 32, zr[1]);
@@ -262,12 +311,19 @@ __device__ __forceinline__ void chain_ew_mask2(uint32_t tz, const uint32_t (&mk)
 #pragma unroll
   for (int q = 0; q < 2; ++q) {
     uint32_t pk[16];
+    const float colf = q == 0 ? colf0 : colf1;
 #pragma unroll
     for (int c4 = 0; c4 < 8; ++c4) {
       uint64_t a = fmul2(f2_pack(__uint_as_float(zr[q][4 * c4]), __uint_as_float(zr[q][4 * c4 + 1])), rf2);
       uint64_t b = fmul2(f2_pack(__uint_as_float(zr[q][4 * c4 + 2]), __uint_as_float(zr[q][4 * c4 + 3])), rf2);
       a = fmul2(a, chain_unpack_pair<BF16>(mk[q * 16 + 2 * c4]));
       b = fmul2(b, chain_unpack_pair<BF16>(mk[q * 16 + 2 * c4 + 1]));
+      if (MODE == kChainRowK) {
+        const float fa = __shfl_sync(0xffffffffu, colf, 4 * c4), fb = __shfl_sync(0xffffffffu, colf, 4 * c4 + 1);
+        const float fc = __shfl_sync(0xffffffffu, colf, 4 * c4 + 2), fd = __shfl_sync(0xffffffffu, colf, 4 * c4 + 3);
+        a = fmul2(a, f2_pack(fa, fb));
+        b = fmul2(b, f2_pack(fc, fd));
+      }
       float w0, w1, w2, w3;
       f2_unpack(a, w0, w1);
       f2_unpack(b, w2, w3);

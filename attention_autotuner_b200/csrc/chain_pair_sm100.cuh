@@ -63,7 +63,7 @@ struct ChainPairConfig {
   static_assert(K1 % 64 == 0 && K1 >= 64 && K1 <= 512, "K1");
   static_assert(N2 == 128 || N2 == 256, "N2");
   static_assert(NSLOT >= CI + TI, "ring too small");
-  static_assert(1536 + (2 * NSLOT + 2 * NREADY + 14) * 8 + 16 <= AUX_BYTES, "barrier area");
+  static_assert(512 + (2 * NSLOT + 2 * NREADY + 14) * 8 + 16 <= AUX_BYTES, "barrier area");
 };
 
 template <class Cfg>
@@ -80,8 +80,7 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sR = smem;
   uint8_t* sRing = smem + Cfg::R_BYTES;
-  float* cf = reinterpret_cast<float*>(sRing + NSLOT * ITEM);  // [2][128] column factors
-  float* rs = cf + 256;                                         // [128] row sums of the finished item (forward)
+  float* rs = reinterpret_cast<float*>(sRing + NSLOT * ITEM);  // [128] row sums of the finished item (forward)
   uint64_t* bars = reinterpret_cast<uint64_t*>(rs + 128);
   // "own": used in both CTAs for their own data. "leader": only the leader's copy is used; threads of both
   // CTAs arrive on it.
@@ -415,17 +414,10 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
     const int tid = threadIdx.x & 127;  // TMEM lane = row of the CTA's tile
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32);
     constexpr bool decay_mode = !GENERAL;
-    const int mycol = hh * 64 + (tid & 63);  // column whose factor this thread computes (threads tid < 64)
     bool ok = true;
     int g0 = 0;     // blocks processed before the current work item
     int kacc = 0;   // non-empty work items finished so far
-    int kitem = 0;  // work items seen so far (selects the per-item column-factor table)
-    auto wg_sync = [&]() {
-      if (hh == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
-      else asm volatile("bar.sync 2, 128;" ::: "memory");
-    };
-
-    for (int u = 0; u < n_steps && ok; ++u, ++kitem) {
+    for (int u = 0; u < n_steps && ok; ++u) {
       ChainItem it;
       if (!decode_step(u, it)) continue;
       const int bh = it.bh, row0 = it.row0 + static_cast<int>(rank) * 128, n_off = it.n_off, t_start = it.t_start;
@@ -437,7 +429,6 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
       float rowf_base = p.scale;
       if (decay_mode) rowf_base *= exp2f((MODE == kChainRowK ? -tid : tid) * lg);
       if (MODE == kChainRowQ) rowf_base *= (grow < p.Lq) ? 1.0f / p.r_in[static_cast<size_t>(bh) * p.Lq + grow] : 0.f;
-      const float* cf_item = cf + (kitem & 1) * 128;  // used by the mask-tensor flavours of RowK only
       float rsum = 0.f;
       if (n_iter == 0) {
         // no block contributes to this tile: zeros (and r = 1 in the forward)
@@ -452,27 +443,21 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
       for (int t = 0; t < n_iter; ++t) {
         const int g = g0 + t;  // running block index: Z buffer g & 1
         const int col0 = (t_start + t) * 128;
-        const float* cft = cf_item;
         float colf0 = 0.f, colf1 = 0.f;
         if (MODE == kChainRowK) {
-          if constexpr (GENERAL) {
-            // column factor table: 1/r of the block's queries
-            if (tid < 64) {
-              const int qi = col0 + mycol;
-              cf[(g & 1) * 128 + mycol] = (qi < p.Lq) ? 1.0f / p.r_in[static_cast<size_t>(bh) * p.Lq + qi] : 0.f;
-            }
-            wg_sync();
-            cft = cf + (g & 1) * 128;
-          } else {
-            colf0 = chain_rowk_colf(p, bh, col0, 2 * hh, lane, lg);
-            colf1 = chain_rowk_colf(p, bh, col0, 2 * hh + 1, lane, lg);
-          }
+          // column factor gamma^c / r[c] (decay) or 1 / r[c] (mask tensor: lg = 0) of column (chunk, lane)
+          colf0 = chain_rowk_colf(p, bh, col0, 2 * hh, lane, lg);
+          colf1 = chain_rowk_colf(p, bh, col0, 2 * hh + 1, lane, lg);
         }
-        uint32_t mk[(GENERAL && MODE != kChainRowK) ? 32 : 1];
+        uint32_t mk[GENERAL ? 32 : 1];
         if constexpr (GENERAL && MODE != kChainRowK) {
           // the block's mask values of this thread (its row of the mask tensor), fetched before the wait for Z
           if (hh == 0) chain_mask_prefetch<MODE, 0>(p, h, grow, col0, mk);
           else chain_mask_prefetch<MODE, 2>(p, h, grow, col0, mk);
+        } else if constexpr (GENERAL) {
+          // RowK: the thread's column of the mask, read by rows by the whole warp and transposed in registers
+          if (hh == 0) chain_mask_prefetch_rowk<0>(p, h, grow - lane, lane, col0, mk);
+          else chain_mask_prefetch_rowk<2>(p, h, grow - lane, lane, col0, mk);
         }
         float rowf = rowf_base;
         if (decay_mode) rowf *= exp2f((MODE == kChainRowK ? (col0 - row0) : (row0 - col0)) * lg);
@@ -486,13 +471,9 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
         if (tid == 0 && hh == 0) AB200_CTR(0, g, 1);
         tc_fence_after();
         const uint32_t tz = tmem_addr(tZ0 + (g & 1) * 128, lane_base, 0);
-        if constexpr (GENERAL && MODE != kChainRowK) {
-          if (hh == 0) chain_ew_mask2<MODE, BF16, 0, true>(tz, mk, rowf, rsum);
-          else chain_ew_mask2<MODE, BF16, 2, true>(tz, mk, rowf, rsum);
-        } else if constexpr (GENERAL) {
-          // RowK with a mask tensor: column reads of the mask, chunk by chunk after the wait (see chain_ew_block)
-          if (hh == 0) chain_ew_block<MODE, GENERAL, BF16, 0, 2, true>(p, tz, cft, rowf, straddle, dlim, grow, col0, h, rsum);
-          else chain_ew_block<MODE, GENERAL, BF16, 2, 4, true>(p, tz, cft, rowf, straddle, dlim, grow, col0, h, rsum);
+        if constexpr (GENERAL) {
+          if (hh == 0) chain_ew_mask2<MODE, BF16, 0, true>(tz, mk, rowf, colf0, colf1, rsum);
+          else chain_ew_mask2<MODE, BF16, 2, true>(tz, mk, rowf, colf0, colf1, rsum);
         } else {
           if (hh == 0) chain_ew_decay2<MODE, BF16, 0, true>(tz, rowf, lg, colf0, colf1, straddle, dlim, rsum);
           else chain_ew_decay2<MODE, BF16, 2, true>(tz, rowf, lg, colf0, colf1, straddle, dlim, rsum);
