@@ -35,6 +35,9 @@ WORKLOADS = {
     # C3 / C4: RetNet parallel forward / forward+backward with the per-head decay mask (FLOPs count the i >= j pairs)
     "C3": (8, 8, 2048, 2048, 256, 512, "fp16", True),
     "C4": (8, 8, 2048, 2048, 256, 512, "fp16", True),
+    # the same decay mask handed over as the reference's [H, Lq, Lkv] mask tensor (device timing only)
+    "C3mask": (8, 8, 2048, 2048, 256, 512, "fp16", True),
+    "C4mask": (8, 8, 2048, 2048, 256, 512, "fp16", True),
     "C1": (2, 4, 512, 512, 64, 64, "fp16", False),
     "C2": (8, 16, 4096, 4096, 128, 128, "fp16", False),
     "C2causal": (8, 16, 4096, 4096, 128, 128, "fp16", True),
@@ -46,7 +49,7 @@ WORKLOADS = {
 }
 METRIC = "attn fwd TFLOPS at B=8,H=16,L=4096,d=128 fp16"
 UNIT = "TFLOP/s"
-RETNET = {"C3": "fwd", "C4": "fwd+bwd"}
+RETNET = {"C3": "fwd", "C4": "fwd+bwd", "C3mask": "fwd", "C4mask": "fwd+bwd"}
 # dram__bytes_read.sum + dram__bytes_write.sum per step from the ncu captures summarised under profiles/
 # (fa_fwd_sm100_kernel_C2_fp16.md, chain_pair_sm100_kernel_C4_retnet_fp16.md); None where no capture was taken
 NCU_TRAFFIC_BYTES = {"C2": 515.2e6, "C3": 383.6e6, "C4": 1725.3e6}
@@ -54,7 +57,8 @@ NCU_TRAFFIC_BYTES = {"C2": 515.2e6, "C3": 383.6e6, "C4": 1725.3e6}
 
 def metric_name(workload):
     if workload in RETNET:
-        return "RetNet %s TFLOPS at B=8,H=8,L=2048,dqk=256,dv=512 fp16 (decay mask, unmasked pairs counted)" % RETNET[workload]
+        return "RetNet %s TFLOPS at B=8,H=8,L=2048,dqk=256,dv=512 fp16 (decay mask%s, unmasked pairs counted)" % (
+            RETNET[workload], " as a mask tensor" if workload.endswith("mask") else "")
     if workload == "C2":
         return METRIC
     B, H, Lq, Lkv, dqk, dv, dtype, causal = WORKLOADS[workload]
@@ -64,7 +68,7 @@ def metric_name(workload):
 def flops_of(workload):
     B, H, Lq, Lkv, dqk, dv, dtype, causal = WORKLOADS[workload]
     f = flops_fwd(B, H, Lq, Lkv, dqk, dv, causal)
-    if workload == "C4":
+    if RETNET.get(workload) == "fwd+bwd":
         f += f / (dqk + dv) * (3 * dqk + 2 * dv)
     return f
 
@@ -249,12 +253,21 @@ def main():
         launches_per_step = 1 if ret == "fwd" else 4
         sp = ctypes.c_void_p(stream.cuda_stream)
 
+        maskd = None
+        if args.workload.endswith("mask"):
+            idx = torch.arange(Lq, device=dev, dtype=torch.float64)
+            diff = idx[:, None] - torch.arange(Lkv, device=dev, dtype=torch.float64)[None, :]
+            maskd = torch.where(diff >= 0, gam.double()[:, None, None] ** diff.clamp(min=0), torch.zeros((), device=dev,
+                                                                                                  dtype=torch.float64)).to(tdt)
+            args.no_e2e = True
+        dec = None if maskd is not None else gam
+
         def step():
-            _lib.check(lib.attn_b200_ret_fwd(P(q), P(k), P(v), None, P(o), P(r), B, H, Lq, Lkv, dqk, dv, code, scale,
-                                             P(gam), 1, sp))
+            _lib.check(lib.attn_b200_ret_fwd(P(q), P(k), P(v), P(maskd), P(o), P(r), B, H, Lq, Lkv, dqk, dv, code, scale,
+                                             P(dec), 1, sp))
             if ret != "fwd":
-                _lib.check(lib.attn_b200_ret_bwd(P(q), P(k), P(v), None, P(do), P(r), P(dq), P(dk), P(dvo), None, B, H,
-                                                 Lq, Lkv, dqk, dv, code, scale, P(gam), 1, sp))
+                _lib.check(lib.attn_b200_ret_bwd(P(q), P(k), P(v), P(maskd), P(do), P(r), P(dq), P(dk), P(dvo), None, B, H,
+                                                 Lq, Lkv, dqk, dv, code, scale, P(dec), 1, sp))
     else:
         def step():
             _lib.check(lib.attn_b200_fa_fwd(P(q), P(k), P(v), P(o), None, B, H, Lq, Lkv, dqk, dv, code, scale,
