@@ -54,10 +54,7 @@ struct ChainPairConfig {
   // Output staging of the epilogue: 2 * TI boxes of 16 KB. With a deep ring the boxes of a work item are staged at
   // once, in the slots of its last T tile and of the first TI items of its last C tile; with a shallow ring
   // (K1 = 512) in two rounds through the T slots only, so that the next item's first C tile is not held up.
-#ifndef AB200_PAIR_ONE_ROUND
-#define AB200_PAIR_ONE_ROUND 1
-#endif
-  static constexpr bool ONE_ROUND = AB200_PAIR_ONE_ROUND && (CI >= TI) && (NSLOT >= 2 * (CI + TI));
+  static constexpr bool ONE_ROUND = (CI >= TI) && (NSLOT >= 2 * (CI + TI));
   static constexpr int NTHREADS = 512;
   static constexpr int TMEM_COLS = 512;  // 2 x 128 (Z) + N2
   static_assert(K1 % 64 == 0 && K1 >= 64 && K1 <= 512, "K1");
