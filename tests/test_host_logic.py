@@ -169,3 +169,33 @@ def test_prune_stale_removes_only_libraries_of_other_source_hashes(tmp_path):
         f.write_text("x")
     assert prune_stale(str(tmp_path)) == 1
     assert keep.exists() and keep_src.exists() and other.exists() and not old.exists()
+
+
+def test_cta_pair_knob_in_configs_and_search_space():
+    """CTA pairing is part of every operator's search space; the tuner rejects pair configurations whose tiles cannot
+    be split between two CTAs, and the generated launch shim selects the pair kernels."""
+    from attention_autotuner_b200.autotuner.configs import RetBwdConfig, RetConfig
+    from attention_autotuner_b200.autotuner.runtime import _create_entry_code
+    from attention_autotuner_b200.autotuner.tunner import RetBwdTunner, RetTunner
+    z = torch.zeros(1, 1, 1, 256, dtype=torch.float16)
+    zv = torch.zeros(1, 1, 1, 512, dtype=torch.float16)
+    at = AttnTunner(B200(), [torch.zeros(1, 1, 1, 128, dtype=torch.float16)] * 4)
+    cfgs = at.get_tuned_configs()
+    assert any(c.cta_pair for c in cfgs) and any(not c.cta_pair for c in cfgs)
+    assert not at.validate_kernel(AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, dv_chunk=64, cta_pair=1))
+    assert not at.validate_kernel(AttnConfig(128, 128, 128, 128, q_tiles=1, kv_stages=4, dv_chunk=128, cta_pair=1))
+    pair = AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, dv_chunk=128, cta_pair=1)
+    assert at.validate_kernel(pair)
+    src = _create_entry_code(pair)
+    assert "FaPairConfig<128, 8, false>" in src and "fa_fwd_pair_launch<Cfg>" in src
+    assert "fa_fwd_launch<Cfg>" in _create_entry_code(AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, dv_chunk=128))
+    rt = RetTunner(B200(), [z, z, zv, None, zv, None], decay=torch.ones(1))
+    assert RetConfig(128, 128, 256, 512).cta_pair == 1 and RetConfig(128, 128, 64, 64).cta_pair == 0
+    assert not rt.validate_kernel(RetConfig(128, 128, 256, 512, dv_chunk=64, cta_pair=1))
+    assert {c.cta_pair for c in rt.get_tuned_configs()} == {0, 1}
+    bt = RetBwdTunner(B200(), [z, z, zv, None, zv, None, z, z, zv, None], decay=torch.ones(1))
+    assert not bt.validate_kernel(RetBwdConfig(128, 128, 256, 512, dv_chunk=256, dq_chunk=64, cta_pair=1))
+    assert "true>(a" in _create_entry_code(RetBwdConfig(128, 128, 256, 512)).replace(" ", "").replace("\n", "") or \
+        ", true>" in _create_entry_code(RetBwdConfig(128, 128, 256, 512))
+    # a decay mask is lower triangular whatever `causal` says: one cache entry
+    assert RetTunner(B200(), [z, z, zv, None, zv, None], causal=True, decay=torch.ones(1))._cache_file() == rt._cache_file()
