@@ -48,94 +48,18 @@ enum ChainTag : int {
   kCtR = 11, kCtSlotFull = 12, kCtSlotEmpty = 13, kCtZFull = 14, kCtWFull = 15, kCtAccDone = 16, kCtAccFree = 17, kCtRFree = 18, kCtZFree = 19
 };
 
-// Element-wise step of one block for the thread that owns TMEM lane (row) `tz >> 16`: reads the 128 fp32
-// values of its row of Z at `tz`, applies the row factor, the mask (general 16-bit tensor, or the decay factor
-// table `cft` with the triangular predicate `dlim` on blocks that straddle the diagonal), and writes the 64
-// packed 16-bit pairs of W over the first 64 columns of the same buffer. The forward accumulates sum |W|.
-//   grow = global row of this thread on the row side, col0 = first global column of the block, h = head.
-// QD0..QD1 selects the 32-column chunks this thread handles (all four by default). With SPLITW two threads share
-// a row (chunks 0-1 and 2-3) and each keeps its 32 packed W columns inside its own half of the buffer: W of
-// chunks 0-1 at columns [0,32), of chunks 2-3 at [64,96).
-template <int MODE, bool GENERAL, bool BF16, int QD0 = 0, int QD1 = 4, bool SPLITW = false>
-__device__ __forceinline__ void chain_ew_block(const ChainParams& p, uint32_t tz, const float* cft, float rowf,
-                                               bool straddle, int dlim, int grow, int col0, int h, float& rsum) {
-#pragma unroll
-  for (int qd = QD0; qd < QD1; ++qd) {
-    uint32_t zr[32];
-    tmem_ld32(tz + qd * 32, zr);
-    float mk[32];
-    if (GENERAL) {
-      if (MODE != kChainRowK) {
-        // row of the mask owned by this thread: M[h, grow, col0 + qd*32 ...], 16-byte vectors
-        const uint16_t* mp = p.mask + (static_cast<size_t>(h) * p.Lq + grow) * p.Lkv + col0 + qd * 32;
-#pragma unroll
-        for (int v8 = 0; v8 < 4; ++v8) {
-          uint4 u = make_uint4(0, 0, 0, 0);
-          if (grow < p.Lq && col0 + qd * 32 + v8 * 8 < p.Lkv) u = __ldg(reinterpret_cast<const uint4*>(mp) + v8);
-          const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            if constexpr (BF16) {
-              mk[v8 * 8 + 2 * e] = __uint_as_float(w4[e] << 16);
-              mk[v8 * 8 + 2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
-            } else {
-              const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w4[e]));
-              mk[v8 * 8 + 2 * e] = f2.x;
-              mk[v8 * 8 + 2 * e + 1] = f2.y;
-            }
-          }
-        }
-      } else {
-        // column of the mask: M[h, col0 + c, grow]; consecutive threads read consecutive keys
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int qi = col0 + qd * 32 + c;
-          uint16_t u = 0;
-          if (qi < p.Lq && grow < p.Lkv) u = __ldg(p.mask + (static_cast<size_t>(h) * p.Lq + qi) * p.Lkv + grow);
-          if constexpr (BF16) {
-            mk[c] = __uint_as_float(static_cast<uint32_t>(u) << 16);
-          } else {
-            mk[c] = __half2float(__ushort_as_half(u));
-          }
-        }
-      }
-    }
-    tc_wait_ld();
-    uint32_t pk[16];
-#pragma unroll
-    for (int c = 0; c < 32; c += 2) {
-      float w0 = __uint_as_float(zr[c]) * rowf;
-      float w1 = __uint_as_float(zr[c + 1]) * rowf;
-      if (GENERAL) {
-        w0 *= mk[c];
-        w1 *= mk[c + 1];
-      }
-      if (MODE == kChainRowK || (!GENERAL)) {
-        w0 *= cft[qd * 32 + c];
-        w1 *= cft[qd * 32 + c + 1];
-      }
-      if (straddle) {
-        const int cc = qd * 32 + c;
-        if (MODE == kChainRowK) {
-          if (cc < dlim) w0 = 0.f;
-          if (cc + 1 < dlim) w1 = 0.f;
-        } else {
-          if (cc > dlim) w0 = 0.f;
-          if (cc + 1 > dlim) w1 = 0.f;
-        }
-      }
-      if (MODE == kChainFwd) rsum += fabsf(w0) + fabsf(w1);
-      pk[c >> 1] = pack2<BF16>(w0, w1);
-    }
-    tmem_st16(tz + (SPLITW ? (qd >> 1) * 64 + (qd & 1) * 16 : qd * 16), pk);
-  }
-}
-
-// The same step for the decay flavours (no mask tensor), two 32-column chunks (QD0, QD0 + 1) per call, written for
-// instruction count and without shared-memory reads. Measured alone on one SM, cycles per 128 x 128 block
-// with two threads per row: 980 for the loop above; 534 for this version; and with SS MMAs streaming their
-// operands from shared memory on the same SM the loop above (one broadcast table read per 4 columns) took
-// 2611 cycles against 550 here: the tensor core saturates the shared-memory bandwidth and starves LDS.
+// Element-wise step of one block, W = Z .* mask .* scale (./ r), for the thread that owns TMEM lane (row) `tz >> 16`:
+// it reads fp32 values of its row of Z at `tz`, applies the row factor and the mask (decay factors built in
+// registers, or a general 16-bit mask tensor) and writes packed 16-bit pairs of W over the first columns of the same
+// buffer; the forward accumulates sum |W|. Every flavour handles two 32-column chunks (QD0, QD0 + 1) per call. With
+// SPLITW two threads share a row (chunks 0-1 and 2-3) and each keeps its 32 packed W columns inside its own half of
+// the buffer: W of chunks 0-1 at columns [0,32), of chunks 2-3 at [64,96); otherwise W sits at columns [0,64).
+//
+// Decay flavours (no mask tensor), written for instruction count and without shared-memory reads. Measured alone on
+// one SM, cycles per 128 x 128 block with two threads per row: 980 for a straightforward loop that reads a
+// column-factor table from shared memory; 534 for this version; and with SS MMAs streaming their operands from
+// shared memory on the same SM the table version (one broadcast read per 4 columns) took 2611 cycles against 550
+// here: the tensor core saturates the shared-memory bandwidth and starves LDS.
 //   * Fwd / RowQ: the column factor gamma^(-c) is a running product, two columns per packed multiply,
 //     restarted from an exact value at every chunk (32 steps of fp32 rounding at most);
 //   * RowK: the column factor gamma^c / r[c] of column (chunk, lane) sits in a register of that lane

@@ -80,8 +80,7 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sR = smem;
   uint8_t* sRing = smem + Cfg::R_BYTES;
-  float* cf = reinterpret_cast<float*>(sRing + NSLOT * ITEM);  // [2][128] column factors
-  float* rs = cf + 256;                                         // [128] row sums of the finished item (forward)
+  float* rs = reinterpret_cast<float*>(sRing + NSLOT * ITEM);  // [128] row sums of the finished item (forward)
   uint64_t* bars = reinterpret_cast<uint64_t*>(rs + 128);
   uint64_t* r_full = bars;                    // [1]
   uint64_t* slot_full = bars + 1;             // [NSLOT]
@@ -407,9 +406,8 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
     bool ok = true;
     int g0 = 0;     // blocks processed before the current work item
     int kacc = 0;   // non-empty work items finished so far
-    int kitem = 0;  // work items seen so far (selects the per-item column-factor table)
 
-    for (int u = 0; u < n_steps && ok; ++u, ++kitem) {
+    for (int u = 0; u < n_steps && ok; ++u) {
       ChainItem it;
       if (!decode_step(u, it)) continue;
       const int bh = it.bh, row0 = it.row0, n_off = it.n_off, t_start = it.t_start, n_iter = it.n_iter;
@@ -435,21 +433,21 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
     for (int t = 0; t < n_iter; ++t) {
       const int g = g0 + t;  // running block index: Z buffer g & 1
       const int col0 = (t_start + t) * 128;
-      const float* cft = cf;
       float colf[4] = {0.f, 0.f, 0.f, 0.f};
       if (MODE == kChainRowK) {
-        if constexpr (GENERAL) {
-          // column factor table: 1/r of the block's queries (double buffered by block parity; one named barrier
-          // per block keeps the threads within one block of each other)
-          const int qi = col0 + tid;
-          cf[(g & 1) * 128 + tid] = (qi < p.Lq) ? 1.0f / p.r_in[static_cast<size_t>(bh) * p.Lq + qi] : 0.f;
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          cft = cf + (g & 1) * 128;
-        } else {
-          // gamma^c / r[c] of column (chunk, lane) in a register of that lane
+        // gamma^c / r[c] (decay) or 1 / r[c] (mask tensor: lg = 0) of column (chunk, lane) in a register of that lane
 #pragma unroll
-          for (int q = 0; q < 4; ++q) colf[q] = chain_rowk_colf(p, bh, col0, q, lane, lg);
-        }
+        for (int q = 0; q < 4; ++q) colf[q] = chain_rowk_colf(p, bh, col0, q, lane, lg);
+      }
+      // mask tensor: this thread's 128 mask values of the block, packed in pairs, fetched before the wait for Z
+      // (Fwd / RowQ: its row of the mask; RowK: its column, read by rows by the whole warp and transposed)
+      uint32_t mk0[GENERAL ? 32 : 1], mk1[GENERAL ? 32 : 1];
+      if constexpr (GENERAL && MODE != kChainRowK) {
+        chain_mask_prefetch<MODE, 0>(p, h, grow, col0, mk0);
+        chain_mask_prefetch<MODE, 2>(p, h, grow, col0, mk1);
+      } else if constexpr (GENERAL) {
+        chain_mask_prefetch_rowk<0>(p, h, grow - lane, lane, col0, mk0);
+        chain_mask_prefetch_rowk<2>(p, h, grow - lane, lane, col0, mk1);
       }
       float rowf = rowf_base;
       if (decay_mode) rowf *= exp2f((MODE == kChainRowK ? (col0 - row0) : (row0 - col0)) * lg);
@@ -465,7 +463,8 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
       tc_fence_after();
       const uint32_t tz = tmem_addr(tZ0 + (g & 1) * 128, lane_base, 0);
       if constexpr (GENERAL) {
-        chain_ew_block<MODE, GENERAL, BF16>(p, tz, cft, rowf, straddle, dlim, grow, col0, h, rsum);
+        chain_ew_mask2<MODE, BF16, 0, false>(tz, mk0, rowf, colf[0], colf[1], rsum);
+        chain_ew_mask2<MODE, BF16, 2, false>(tz, mk1, rowf, colf[2], colf[3], rsum);
       } else {
         chain_ew_decay2<MODE, BF16, 0, false>(tz, rowf, lg, colf[0], colf[1], straddle, dlim, rsum);
         chain_ew_decay2<MODE, BF16, 2, false>(tz, rowf, lg, colf[2], colf[3], straddle, dlim, rsum);
