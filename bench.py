@@ -357,7 +357,9 @@ def main():
                          "flops_per_step": fl_gpu, "launches_per_step": launches_per_step,
                          "kernel": "chain_pair_sm100_kernel" if ret else "fa_fwd_sm100_kernel"},
             "clocks": clocks,
-            "gpu_launches": launches_per_step * (args.steps + (2 + e2e_steps if e2e_ms is not None else 0)),
+            # launches inside the two timed regions; the end-to-end leg launches once per batch entry (the host-buffer
+            # operators cut the batch into B pieces)
+            "gpu_launches": launches_per_step * (args.steps + (e2e_steps * B if e2e_ms is not None else 0)),
         }
         if e2e_ms is not None:
             es = q.element_size()
