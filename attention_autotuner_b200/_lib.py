@@ -33,6 +33,11 @@ def _declare(lib):
     lib.attn_b200_fa_fwd.argtypes = fa
     lib.attn_b200_fa_fwd_profile.restype = cf
     lib.attn_b200_fa_fwd_profile.argtypes = fa
+    fb = [vp] * 9 + [ci] * 6 + [cf, ci, vp]
+    lib.attn_b200_fa_bwd.restype = ci
+    lib.attn_b200_fa_bwd.argtypes = fb
+    lib.attn_b200_fa_bwd_profile.restype = cf
+    lib.attn_b200_fa_bwd_profile.argtypes = fb
     rf = [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, vp, ci, vp]
     lib.attn_b200_ret_fwd.restype = ci
     lib.attn_b200_ret_fwd.argtypes = rf

@@ -5,6 +5,7 @@
 #include "../../include/attn_b200.h"
 
 #include "chain_launch.cuh"
+#include "fa_bwd_launch.cuh"
 #include "fa_fwd_launch.cuh"
 #include "selftest.cuh"
 #include "selftest_pair.cuh"
@@ -53,6 +54,26 @@ int fa_fwd_common(const void* q, const void* k, const void* v, void* o, float* l
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   return dtype == ATTN_B200_BF16 ? fa_fwd_dispatch<true>(a, dqk, st, profile, ms)
                                  : fa_fwd_dispatch<false>(a, dqk, st, profile, ms);
+}
+
+int fa_bwd_common(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse, void* dq,
+                  void* dk, void* dv, int B, int H, int Lq, int Lkv, int d, int dtype, float scale, int causal, void* stream,
+                  bool profile, float* ms) {
+  if (B <= 0 || H <= 0) return fail(kErrInvalidArgument, "fa_bwd: B and H must be positive");
+  if (dtype != ATTN_B200_F16 && dtype != ATTN_B200_BF16) return fail(kErrInvalidArgument, "fa_bwd: dtype %d", dtype);
+  FaBwdArgs a{q, k, v, o, dout, lse, dq, dk, dv, B * H, Lq, Lkv, d, scale, causal};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  auto run = [&](auto d_tag, auto bf16_tag) -> int {
+    constexpr int D = decltype(d_tag)::value;
+    constexpr bool BF16 = decltype(bf16_tag)::value;
+    if (!profile) return fa_bwd_launch<D, BF16>(a, st);
+    *ms = profile_loop([&] { return fa_bwd_launch<D, BF16>(a, st); }, st);
+    return *ms < 0.f ? kErrCuda : kOk;
+  };
+  const bool bf16 = dtype == ATTN_B200_BF16;
+  if (d == 64) return bf16 ? run(std::integral_constant<int, 64>{}, std::true_type{}) : run(std::integral_constant<int, 64>{}, std::false_type{});
+  if (d == 128) return bf16 ? run(std::integral_constant<int, 128>{}, std::true_type{}) : run(std::integral_constant<int, 128>{}, std::false_type{});
+  return fail(kErrUnsupported, "fa_bwd: head dimension %d (q, k and v must share 64 or 128)", d);
 }
 
 // RetNet head-dim pairs built into this library (others: per-config libraries from the tuner).
@@ -123,6 +144,20 @@ float attn_b200_fa_fwd_profile(const void* q, const void* k, const void* v, void
                                void* stream) {
   float ms = -1.f;
   int rc = fa_fwd_common(q, k, v, o, lse, B, H, Lq, Lkv, dqk, dv, dtype, scale, causal, stream, true, &ms);
+  return rc == kOk ? ms : -1.f;
+}
+
+int attn_b200_fa_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                     void* dq, void* dk, void* dv, int B, int H, int Lq, int Lkv, int d, int dtype, float scale,
+                     int causal, void* stream) {
+  return fa_bwd_common(q, k, v, o, dout, lse, dq, dk, dv, B, H, Lq, Lkv, d, dtype, scale, causal, stream, false, nullptr);
+}
+
+float attn_b200_fa_bwd_profile(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                               const float* lse, void* dq, void* dk, void* dv, int B, int H, int Lq, int Lkv, int d,
+                               int dtype, float scale, int causal, void* stream) {
+  float ms = -1.f;
+  int rc = fa_bwd_common(q, k, v, o, dout, lse, dq, dk, dv, B, H, Lq, Lkv, d, dtype, scale, causal, stream, true, &ms);
   return rc == kOk ? ms : -1.f;
 }
 

@@ -62,6 +62,23 @@ float attn_b200_fa_fwd_profile(const void* q, const void* k, const void* v, void
                                void* stream);
 
 /*
+ * Flash-attention backward:  dQ, dK, dV of the forward above, given its output o, its log-sum-exp lse and dO.
+ * The reference declares this backward and leaves it empty (python/ops/attention_interface.py:38-39); this entry
+ * point is what that method would bind. Three kernels (dV, dK, dQ), each owning its output tile: no atomics and no
+ * workspace; P is recomputed from lse, delta = rowsum(dO .* O) is computed inside the kernels.
+ *   q, o, dout, dq [B,H,Lq,d]   k, v, dk, dv [B,H,Lkv,d]   (dtype)    lse [B,H,Lq] fp32 (from attn_b200_fa_fwd)
+ *   d in {64,128} for q, k and v alike. causal != 0 needs Lq == Lkv. scale as given to the forward.
+ */
+int attn_b200_fa_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                     void* dq, void* dk, void* dv, int B, int H, int Lq, int Lkv, int d, int dtype, float scale,
+                     int causal, void* stream);
+
+/* Same arguments; timing loop as attn_b200_fa_fwd_profile. Returns ms per backward (three launches), or -1. */
+float attn_b200_fa_bwd_profile(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                               const float* lse, void* dq, void* dk, void* dv, int B, int H, int Lq, int Lkv, int d,
+                               int dtype, float scale, int causal, void* stream);
+
+/*
  * RetNet parallel forward:  S~ = (Q K^T * scale) .* M,  r = max(sum_j |S~|, 1),  O = (S~ / r) V.
  * Replaces python/ops/retnet_interface.py:11-33 -> Runtime.apply -> kernel_entry -> ret_fwd_regfuse /
  * ret_fwd_smemfuse (csrc/kernels/retnet/regfuse/regfuse.h:47, csrc/kernels/retnet/smemfuse/smemfuse.h:62).

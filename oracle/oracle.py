@@ -85,6 +85,34 @@ def attention_fwd(q, k, v, scale: float = 0.125, causal: bool = False):
     return o, lse
 
 
+def attention_bwd(q, k, v, do, scale: float = 0.125, causal: bool = False):
+    """Closed-form gradients of attention_fwd (the derivative of python/utils/ref_op.py:2-6; the reference's own
+    backward is empty, python/ops/attention_interface.py:38-39). Returns (dq, dk, dv) in fp32.
+        P = softmax(S),  dV = P^T dO,  dP = dO V^T,  dS = P .* (dP - rowsum(dO .* O)) * scale,  dQ = dS K,  dK = dS^T Q"""
+    q, k, v, do = (t.to(torch.float32) for t in (q, k, v, do))
+    s = (q @ k.transpose(-1, -2)) * scale
+    if causal:
+        Lq, Lkv = s.shape[-2], s.shape[-1]
+        i = torch.arange(Lq)[:, None]
+        j = torch.arange(Lkv)[None, :]
+        s = s.masked_fill(j > i + (Lkv - Lq), float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    o = p @ v
+    dv = p.transpose(-1, -2) @ do
+    dp = do @ v.transpose(-1, -2)
+    delta = (do * o).sum(dim=-1, keepdim=True)
+    ds = p * (dp - delta) * scale
+    return ds @ k, ds.transpose(-1, -2) @ q, dv
+
+
+def attention_bwd_autograd(q, k, v, do, scale: float = 0.125, causal: bool = False):
+    """Same gradients through torch.autograd on attention_fwd."""
+    q, k, v = (t.to(torch.float32).clone().requires_grad_(True) for t in (q, k, v))
+    o, _ = attention_fwd(q, k, v, scale, causal)
+    o.backward(do.to(torch.float32))
+    return q.grad, k.grad, v.grad
+
+
 def retnet_fwd(q, k, v, mask, scale: float = 1.0):
     """o = ((q k^T * scale * mask) / r) v with r = clamp(sum_j |.|, min=1), fp32.
     python/utils/ref_op.py:8-13 (no scale there). mask is [H,Lq,Lkv] (or [Lq,Lkv] for one slice),
@@ -135,6 +163,11 @@ def pairs(Lq: int, Lkv: int, causal: bool) -> int:
 
 def flops_fwd(B, H, Lq, Lkv, dqk, dv, causal=False) -> int:
     return 2 * B * H * pairs(Lq, Lkv, causal) * (dqk + dv)
+
+
+def flops_attn_bwd(B, H, Lq, Lkv, d, causal=False) -> int:
+    """Five GEMMs over the (query, key) pairs that are not masked: S, dP, dV, dQ, dK."""
+    return 5 * 2 * B * H * pairs(Lq, Lkv, causal) * d
 
 
 def flops_ret_bwd(B, H, Lq, Lkv, dqk, dv, causal=False) -> int:

@@ -33,6 +33,21 @@ def attn_case(name, seed, B, H, Lq, Lkv, dqk, dv, kscale=1.0, vscale=1.0):
                         o=o.numpy())
 
 
+def attn_bwd_case(name, seed, B, H, Lq, Lkv, d):
+    """Gradients of the reference's attention formula by torch.autograd (the reference's own backward is empty,
+    python/ops/attention_interface.py:38-39)."""
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, H, Lq, d, generator=g).half()
+    k = torch.randn(B, H, Lkv, d, generator=g).half()
+    v = torch.randn(B, H, Lkv, d, generator=g).half()
+    do = torch.randn(B, H, Lq, d, generator=g).half()
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    o = attention_ref(qf, kf, vf)
+    o.backward(do.float())
+    np.savez_compressed(os.path.join(out_dir, name + ".npz"), q=q.numpy(), k=k.numpy(), v=v.numpy(), do=do.numpy(),
+                        o=o.detach().numpy(), dq=qf.grad.numpy(), dk=kf.grad.numpy(), dv=vf.grad.numpy())
+
+
 def ret_case(name, seed, B, H, Lq, Lkv, dqk, dv, qscale=1.0, kscale=1.0, vscale=1.0, mscale=1.0, decay=False):
     g = torch.Generator().manual_seed(seed)
     q = (qscale * torch.randn(B, H, Lq, dqk, generator=g)).half()
@@ -61,6 +76,8 @@ if __name__ == "__main__":
     attn_case("attn_d64", 11, 1, 2, 256, 256, 64, 64)
     attn_case("attn_d128_ragged", 12, 1, 2, 200, 333, 128, 128)
     attn_case("attn_d256_128_demo_scaling", 13, 1, 1, 256, 256, 256, 128, kscale=3.0, vscale=3.0)
+    attn_bwd_case("attn_bwd_d128_ragged", 14, 1, 2, 200, 333, 128)
+    attn_bwd_case("attn_bwd_d64", 15, 1, 2, 256, 256, 64)
     # retnet: general randn mask (as python/tests/test_runtime.py:103), demo scalings
     # (python/tests/attntuner_demo.py:45-48), and the decay mask of the benchmark configs
     ret_case("ret_randmask", 21, 1, 2, 256, 256, 64, 64)

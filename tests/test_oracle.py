@@ -34,6 +34,24 @@ def test_retnet_matches_reference_golden(golden, name):
             assert torch.allclose(got, ref, rtol=1e-4, atol=1e-4 * max(1.0, ref.abs().max().item())), key
 
 
+@pytest.mark.parametrize("name", ["attn_bwd_d128_ragged", "attn_bwd_d64"])
+def test_attention_backward_matches_reference_golden(golden, name):
+    """Closed-form gradients against autograd through the reference's attention formula (golden), and against
+    autograd through the oracle's own forward, with and without the causal mask."""
+    g = golden(name)
+    q, k, v, do = (T(g[x]) for x in ("q", "k", "v", "do"))
+    dq, dk, dv = oracle.attention_bwd(q, k, v, do, 0.125, False)
+    for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert (got - T(g[key])).abs().max().item() < 2e-5, key
+    Lmin = min(q.shape[2], k.shape[2])
+    qs, dos, ks, vs = q[:, :, :Lmin], do[:, :, :Lmin], k[:, :, :Lmin], v[:, :, :Lmin]
+    for causal, scale in ((True, 0.125), (False, 0.3)):
+        a = oracle.attention_bwd(qs, ks, vs, dos, scale, causal)
+        b = oracle.attention_bwd_autograd(qs, ks, vs, dos, scale, causal)
+        for x, y in zip(a, b):
+            assert (x - y).abs().max().item() < 2e-5
+
+
 def test_lse_and_scale_and_causal():
     g = torch.Generator().manual_seed(1)
     q, k, v = (torch.randn(2, 3, 40, 16, generator=g) for _ in range(3))
