@@ -13,14 +13,19 @@
 //   dQ      queries  Q   dO   K     V     K     P   .* (dP   - delta[query]) * scale
 //
 // with delta[i] = sum_d dO[i,d] * O[i,d], computed inside the kernels from the rows of dO and O (the dQ kernel: the
-// thread's own row, once per tile; the dK kernel: 128 rows per block, shared through a small table in shared memory).
+// thread's own row, once per tile; the dK kernel: 128 rows per block, by the helper warpgroup).
 // The reference has no attention backward (python/ops/attention_interface.py:38-39 is `pass`); the formulas are the
 // derivative of its forward (python/utils/ref_op.py:2-6) with the softmax recomputed from the forward's log-sum-exp.
 //
-// Roles as in chain_sm100.cuh: warps 0-3 element-wise (thread t owns TMEM lane t), warp 4 issues both GEMM1s, warp 5
-// GEMM2, warp 6 lane 0 is the TMA producer, warps 8-11 the epilogue. Every streamed tile is one ring item (two boxes
-// of 128 rows x 64 columns for D = 128), so the MMA warps wait on the ring barriers themselves. Tensor memory: Z1
-// double buffered at columns [0,256), Z2 single at [256,384), ACC at [384,384+D).
+// Roles: warps 0-3 and 8-11 are two element-wise warpgroups (two threads per row of the block: columns 0-63 and
+// 64-127), warp 4 issues both GEMM1s, warp 5 GEMM2, warp 6 lane 0 is the TMA producer, warps 12-15 are the helper
+// warpgroup: it writes the accumulator out when a tile is finished and, in the kernels whose columns are queries,
+// prepares the per-column terms (-lse * log2 e and -delta * scale) of the coming blocks in a small ring of tables in
+// shared memory, so that the element-wise threads never wait for global memory. Every streamed tile is one ring item
+// (two boxes of 128 rows x 64 columns for D = 128), so the MMA warps wait on the ring barriers themselves. Tensor
+// memory: Z1 double buffered at columns [0,256), Z2 single at [256,384), ACC at [384,384+D). W (16-bit) overlays Z1:
+// columns 0-63 of the block at [0,32), columns 64-127 at [64,96) of the buffer, each half written by the warpgroup
+// that read it.
 #pragma once
 
 #include "ptx.cuh"
@@ -47,7 +52,7 @@ struct FaBwdItem {
 
 enum FaBwdTag : int {
   kFbR = 31, kFbSlotFull = 32, kFbSlotEmpty = 33, kFbZFull = 34, kFbWFull = 35, kFbAccDone = 36, kFbAccFree = 37,
-  kFbRFree = 38, kFbZFree = 39, kFbZ2Full = 40, kFbZ2Free = 41, kFbDelta = 42
+  kFbRFree = 38, kFbZFree = 39, kFbZ2Full = 40, kFbZ2Free = 41, kFbTabFull = 42, kFbTabFree = 43
 };
 
 template <int D_, int WHICH_, bool BF16_>
@@ -63,11 +68,12 @@ struct FaBwdConfig {
   static constexpr int R_BYTES = 128 * D * 2;
   static constexpr int NR = DUAL ? 2 : 1;          // resident tiles
   static constexpr int NC = DUAL ? 2 : 1;          // C tiles per block
-  static constexpr int AUX_BYTES = 3072;           // delta table (2 x 128 floats), barriers, flags
+  static constexpr int NTAB = 4;                   // ring of per-block column tables (2 x 128 floats each)
+  static constexpr int AUX_BYTES = NTAB * 1024 + 1024;  // tables, barriers, flags
   static constexpr int NSLOT_FIT = (232448 - 1024 - AUX_BYTES - NR * R_BYTES) / ITEM_BYTES;
   static constexpr int NSLOT = NSLOT_FIT > 5 ? 5 : NSLOT_FIT;
   static constexpr int SMEM_BYTES = 1024 + NR * R_BYTES + NSLOT * ITEM_BYTES + AUX_BYTES;
-  static constexpr int NTHREADS = 384;
+  static constexpr int NTHREADS = 512;
   static constexpr int TMEM_COLS = 512;
   static_assert(D == 64 || D == 128, "head dimension");
   static_assert(NSLOT >= 4, "ring too small");
@@ -117,8 +123,9 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
   uint8_t* sR1 = smem;
   uint8_t* sR2 = smem + Cfg::R_BYTES;  // only with DUAL
   uint8_t* sRing = smem + Cfg::NR * Cfg::R_BYTES;
-  float* dtab = reinterpret_cast<float*>(sRing + NSLOT * ITEM);  // [2][128] delta of the block's queries (dK kernel)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(dtab + 256);
+  // [NTAB][256]: per block of 128 queries, -delta * scale at [0,128) and -lse * log2(e) at [128,256)
+  float* ctab = reinterpret_cast<float*>(sRing + NSLOT * ITEM);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ctab + Cfg::NTAB * 256);
   uint64_t* r_full = bars;                    // [1]
   uint64_t* slot_full = bars + 1;             // [NSLOT]
   uint64_t* slot_empty = slot_full + NSLOT;   // [NSLOT]
@@ -130,8 +137,9 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
   uint64_t* acc_done = z2_free + 1;           // [1]
   uint64_t* acc_free = acc_done + 1;          // [1]
   uint64_t* r_free = acc_free + 1;            // [1]
-  uint64_t* d_full = r_free + 1;              // [2] delta table of a block written (dK kernel, element-wise threads)
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(d_full + 2);
+  uint64_t* tab_full = r_free + 1;            // [NTAB] column table written            (helper -> element-wise)
+  uint64_t* tab_free = tab_full + Cfg::NTAB;  // [NTAB] column table read into registers (element-wise -> helper)
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tab_free + Cfg::NTAB);
   CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 2);
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
@@ -179,12 +187,15 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&z_full[i], 1);
-      mbar_init(&w_full[i], 128);
+      mbar_init(&w_full[i], 256);
       mbar_init(&z_free[i], 1);
-      mbar_init(&d_full[i], 128);
+    }
+    for (int i = 0; i < Cfg::NTAB; ++i) {
+      mbar_init(&tab_full[i], 128);
+      mbar_init(&tab_free[i], 256);
     }
     mbar_init(z2_full, 1);
-    mbar_init(z2_free, 128);
+    mbar_init(z2_free, 256);
     mbar_init(acc_done, 1);
     mbar_init(acc_free, 128);
     mbar_init(r_free, 1);
@@ -342,7 +353,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
             const uint32_t tw = tZ1 + (g & 1) * 128;
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)
-              umma_ts(tACC, tw + ks * 8, umma_smem_desc(a + ks * 2048, BOX, 1024), idesc_acc, (t > 0 || ks > 0) ? 1u : 0u);
+              umma_ts(tACC, tw + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8), umma_smem_desc(a + ks * 2048, BOX, 1024), idesc_acc, (t > 0 || ks > 0) ? 1u : 0u);
             tc_commit(&slot_empty[slot]);
             tc_commit(&z_free[g & 1]);
             if (t + 1 == n) tc_commit(acc_done);
@@ -354,12 +365,16 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
       g0 += n;
       ++kacc;
     }
-  } else if (warp < 4) {
-    // ------------------------------------------------------------------ element-wise warpgroup
-    const int tid = threadIdx.x;  // 0..127 = TMEM lane = row of the resident tile
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32);
+  } else if (warp < 4 || (warp >= 8 && warp < 12)) {
+    // ------------------------------------------------------------------ element-wise warpgroups
+    // Group 0 (warps 0-3) handles columns 0-63 of every block, group 1 (warps 8-11) columns 64-127; thread `tid` of
+    // either group owns TMEM lane (row) tid.
+    const int grp = warp >> 3;
+    const int tid = threadIdx.x & 127;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32);
     constexpr float kLog2e = 1.4426950408889634f;
-    const float sl2 = p.scale * kLog2e;
+    const uint64_t sl2 = f2_pack(p.scale * kLog2e, p.scale * kLog2e);
+    const uint64_t sc2 = f2_pack(p.scale, p.scale);
     bool ok = true;
     int g0 = 0;
     for (int u = 0; u < n_steps && ok; ++u) {
@@ -369,41 +384,35 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
       const int grow = row0 + tid;
       if (n_iter == 0) {
         // no block contributes to this tile: zeros
-        if (grow < rows_len) {
+        if (grp == 0 && grow < rows_len) {
           uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + (static_cast<size_t>(bh) * rows_len + grow) * D;
           for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
         }
         continue;
       }
-      // per-row terms of the dQ kernel (rows are queries)
-      float row_l2 = 0.f, row_d = 0.f;
+      // per-row terms of the dQ kernel (rows are queries): -lse * log2(e) and -delta * scale
+      float row_nl2 = 0.f, row_nds = 0.f;
       if (!ROWK && grow < p.Lq) {
-        row_l2 = p.lse[static_cast<size_t>(bh) * p.Lq + grow] * kLog2e;
-        row_d = fa_bwd_delta_row<D, BF16>(p.o, p.dout, static_cast<size_t>(bh) * p.Lq + grow);
+        row_nl2 = -p.lse[static_cast<size_t>(bh) * p.Lq + grow] * kLog2e;
+        row_nds = -fa_bwd_delta_row<D, BF16>(p.o, p.dout, static_cast<size_t>(bh) * p.Lq + grow) * p.scale;
       }
       for (int t = 0; t < n_iter; ++t) {
         const int g = g0 + t;
         const int col0 = (it.t_start + t) * 128;
-        // per-column terms of the dV / dK kernels (columns are queries): the value of column (chunk q, lane) sits in
-        // a register of that lane and travels by warp shuffle. Queries past the end get lse = +inf, i.e. P = 0.
-        float col_l2[4] = {0.f, 0.f, 0.f, 0.f}, col_d[4] = {0.f, 0.f, 0.f, 0.f};
+        // per-column terms of the dV / dK kernels (columns are queries), from the helper's table: the value of column
+        // (chunk q, lane) sits in a register of that lane and travels by warp shuffle
+        float col_nl2[2] = {0.f, 0.f}, col_nds[2] = {0.f, 0.f};
         if (ROWK) {
+          const int ts = g % Cfg::NTAB;
+          ok = mbar_wait_warp(&tab_full[ts], (g / Cfg::NTAB) & 1, ab, kFbTabFull);
+          if (!ok) break;
+          const float* tab = ctab + ts * 256;
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int qi = col0 + q * 32 + lane;
-            col_l2[q] = (qi < p.Lq) ? p.lse[static_cast<size_t>(bh) * p.Lq + qi] * kLog2e : __int_as_float(0x7f800000);
+          for (int q = 0; q < 2; ++q) {
+            col_nl2[q] = tab[128 + (2 * grp + q) * 32 + lane];
+            if (DUAL) col_nds[q] = tab[(2 * grp + q) * 32 + lane];
           }
-          if (DUAL) {
-            // delta of the block's 128 queries: warp w computes those of chunk w, the table hands them to all warps
-            const int qi = col0 + tid;
-            float* tab = dtab + (g & 1) * 128;
-            tab[tid] = (qi < p.Lq) ? fa_bwd_delta_row<D, BF16>(p.o, p.dout, static_cast<size_t>(bh) * p.Lq + qi) : 0.f;
-            mbar_arrive(&d_full[g & 1]);  // a bounded wait instead of a named barrier: an aborting warp cannot strand the others
-            ok = mbar_wait_warp(&d_full[g & 1], (g >> 1) & 1, ab, kFbDelta);
-            if (!ok) break;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) col_d[q] = tab[q * 32 + lane];
-          }
+          mbar_arrive(&tab_free[ts]);
         }
         const bool diag = p.causal && col0 == row0;  // the only block that straddles the diagonal (Lq == Lkv)
         ok = mbar_wait_warp(&z_full[g & 1], (g >> 1) & 1, ab, kFbZFull);
@@ -416,37 +425,41 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
         const uint32_t tz = tmem_addr(tZ1 + (g & 1) * 128, lane_base, 0);
         const uint32_t tz2 = tmem_addr(tZ2, lane_base, 0);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < 2; ++q) {
+          const int chunk = 2 * grp + q;  // 32-column chunk of the block
           uint32_t z1[32], z2[32];
-          tmem_ld32(tz + q * 32, z1);
-          if (DUAL) tmem_ld32(tz2 + q * 32, z2);
+          tmem_ld32(tz + chunk * 32, z1);
+          if (DUAL) tmem_ld32(tz2 + chunk * 32, z2);
           tc_wait_ld();
-          if (DUAL && q == 3) {
-            // Z2 is in registers: the second GEMM1 of the next block may overwrite it
+          if (DUAL && q == 1) {
+            // this thread's part of Z2 is in registers: the second GEMM1 of the next block may overwrite it
             tc_fence_before();
             mbar_arrive(z2_free);
           }
           uint32_t pk[16];
 #pragma unroll
           for (int c = 0; c < 32; c += 2) {
-            float w[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              float l2 = row_l2, dd = row_d;
-              if (ROWK) {
-                l2 = __shfl_sync(0xffffffffu, col_l2[q], c + e);
-                if (DUAL) dd = __shfl_sync(0xffffffffu, col_d[q], c + e);
-              }
-              float pr = ex2_approx(fmaf(__uint_as_float(z1[c + e]), sl2, -l2));
-              if (diag) {
-                const int cc = q * 32 + c + e;  // column inside the block; row inside the block is tid
-                if (ROWK ? (cc < tid) : (cc > tid)) pr = 0.f;
-              }
-              w[e] = DUAL ? pr * (__uint_as_float(z2[c + e]) - dd) * p.scale : pr;
+            uint64_t nl2 = f2_pack(row_nl2, row_nl2), nds = f2_pack(row_nds, row_nds);
+            if (ROWK) {
+              nl2 = f2_pack(__shfl_sync(0xffffffffu, col_nl2[q], c), __shfl_sync(0xffffffffu, col_nl2[q], c + 1));
+              if (DUAL) nds = f2_pack(__shfl_sync(0xffffffffu, col_nds[q], c), __shfl_sync(0xffffffffu, col_nds[q], c + 1));
             }
-            pk[c >> 1] = pack2<BF16>(w[0], w[1]);
+            float a0, a1;
+            f2_unpack(ffma2(f2_pack(__uint_as_float(z1[c]), __uint_as_float(z1[c + 1])), sl2, nl2), a0, a1);
+            float p0 = ex2_approx(a0), p1 = ex2_approx(a1);
+            if (diag) {
+              const int cc = chunk * 32 + c;  // column inside the block; the row inside the block is tid
+              if (ROWK ? (cc < tid) : (cc > tid)) p0 = 0.f;
+              if (ROWK ? (cc + 1 < tid) : (cc + 1 > tid)) p1 = 0.f;
+            }
+            if (DUAL) {
+              // dS = P .* (dP * scale - delta * scale)
+              const uint64_t t2 = ffma2(f2_pack(__uint_as_float(z2[c]), __uint_as_float(z2[c + 1])), sc2, nds);
+              f2_unpack(fmul2(f2_pack(p0, p1), t2), p0, p1);
+            }
+            pk[c >> 1] = pack2<BF16>(p0, p1);
           }
-          tmem_st16(tz + q * 16, pk);
+          tmem_st16(tz + grp * 64 + q * 16, pk);
         }
         tc_wait_st();
         tc_fence_before();
@@ -455,16 +468,58 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
       if (!ok) break;
       g0 += n_iter;
     }
-  } else if (warp >= 8) {
-    // ------------------------------------------------------------------ epilogue warpgroup
-    const int tid = threadIdx.x - 256;
+  } else if (warp >= 12) {
+    // ------------------------------------------------------------------ helper warpgroup: column tables and epilogue
+    const int tid = threadIdx.x - 384;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32);
+    constexpr float kLog2e = 1.4426950408889634f;
     bool ok = true;
     int kacc = 0;
+    // table cursor: runs ahead of the epilogue cursor by up to two blocks of the next work item
+    int pu = 0, pt = 0, gp = 0;
+    FaBwdItem pit;
+    bool pvalid = false;
+    auto p_next_item = [&]() {
+      pvalid = false;
+      while (pu < n_steps) {
+        const bool have = decode_step(pu, pit);
+        ++pu;
+        if (have && pit.n_iter > 0) {
+          pvalid = true;
+          pt = 0;
+          return;
+        }
+      }
+    };
+    auto produce_one = [&]() -> bool {  // one block's table; false when there is nothing left (or on abort)
+      if (!pvalid) return false;
+      const int ts = gp % Cfg::NTAB;
+      if (gp >= Cfg::NTAB) {
+        ok = mbar_wait_warp(&tab_free[ts], ((gp / Cfg::NTAB) - 1) & 1, ab, kFbTabFree);
+        if (!ok) return false;
+      }
+      const int qi = (pit.t_start + pt) * 128 + tid;
+      const size_t row = static_cast<size_t>(pit.bh) * p.Lq + qi;
+      float* tab = ctab + ts * 256;
+      // queries past the end: lse = +inf, i.e. P = 0
+      tab[128 + tid] = (qi < p.Lq) ? -p.lse[row] * kLog2e : __int_as_float(0xff800000);
+      if (DUAL) tab[tid] = (qi < p.Lq) ? -fa_bwd_delta_row<D, BF16>(p.o, p.dout, row) * p.scale : 0.f;
+      mbar_arrive(&tab_full[ts]);
+      ++gp;
+      if (++pt == pit.n_iter) p_next_item();
+      return true;
+    };
+    if (ROWK) p_next_item();
+    int g_end = 0;  // blocks of the work items up to and including the one whose epilogue comes next
     for (int u = 0; u < n_steps && ok; ++u) {
       FaBwdItem it;
       if (!decode_step(u, it)) continue;
       if (it.n_iter == 0) continue;
+      g_end += it.n_iter;
+      if (ROWK) {
+        while (ok && gp < g_end + 2 && produce_one()) {}
+        if (!ok) break;
+      }
       const int grow = it.row0 + tid;
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + (static_cast<size_t>(it.bh) * rows_len + grow) * D;
       ok = mbar_wait_warp(acc_done, kacc & 1, ab, kFbAccDone);
