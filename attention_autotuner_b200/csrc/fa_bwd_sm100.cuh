@@ -23,7 +23,8 @@
 // prepares the per-column terms (-lse * log2 e and -delta * scale) of the coming blocks in a small ring of tables in
 // shared memory, so that the element-wise threads never wait for global memory. Every streamed tile is one ring item
 // (two boxes of 128 rows x 64 columns for D = 128), so the MMA warps wait on the ring barriers themselves. Tensor
-// memory: Z1 double buffered at columns [0,256), Z2 single at [256,384), ACC at [384,384+D). W (16-bit) overlays Z1:
+// memory: Z1 double buffered at columns [0,256), Z2 single at [256,384) (dV kernel: a third Z1 buffer), ACC at
+// [384,384+D). W (16-bit) overlays Z1:
 // columns 0-63 of the block at [0,32), columns 64-127 at [64,96) of the buffer, each half written by the warpgroup
 // that read it.
 #pragma once
@@ -55,6 +56,18 @@ enum FaBwdTag : int {
   kFbRFree = 38, kFbZFree = 39, kFbZ2Full = 40, kFbZ2Free = 41, kFbTabFull = 42, kFbTabFree = 43
 };
 
+// Optional event trace (compile with -DAB200_TRACE): clock64 of CTA 0 at the hand-over points of the first blocks.
+#ifdef AB200_TRACE
+constexpr int kFaBwdTraceIters = 48;
+__device__ long long g_fa_bwd_trace[3][kFaBwdTraceIters][8];
+#define AB200_FBTR(who, j, ev)                                                                     \
+  do {                                                                                             \
+    if (blockIdx.x == 0 && (j) < kFaBwdTraceIters) g_fa_bwd_trace[who][j][ev] = clock64();         \
+  } while (0)
+#else
+#define AB200_FBTR(who, j, ev) do {} while (0)
+#endif
+
 template <int D_, int WHICH_, bool BF16_>
 struct FaBwdConfig {
   static constexpr int D = D_;  // head dimension of q, k, v (64 or 128)
@@ -69,7 +82,10 @@ struct FaBwdConfig {
   static constexpr int NR = DUAL ? 2 : 1;          // resident tiles
   static constexpr int NC = DUAL ? 2 : 1;          // C tiles per block
   static constexpr int NTAB = 4;                   // ring of per-block column tables (2 x 128 floats each)
-  static constexpr int AUX_BYTES = NTAB * 1024 + 1024;  // tables, barriers, flags
+  // dK kernel: -delta * scale of the first DCACHE_BLOCKS query blocks of the slice the helper worked on last; the two
+  // work items of a pair belong to the same slice, so the second one finds its values here
+  static constexpr int DCACHE_BLOCKS = (WHICH == kFaBwdDK) ? 32 : 0;
+  static constexpr int AUX_BYTES = NTAB * 1024 + 1024 + DCACHE_BLOCKS * 512;  // tables, barriers and flags, delta cache
   static constexpr int NSLOT_FIT = (232448 - 1024 - AUX_BYTES - NR * R_BYTES) / ITEM_BYTES;
   static constexpr int NSLOT = NSLOT_FIT > 5 ? 5 : NSLOT_FIT;
   static constexpr int SMEM_BYTES = 1024 + NR * R_BYTES + NSLOT * ITEM_BYTES + AUX_BYTES;
@@ -79,34 +95,71 @@ struct FaBwdConfig {
   static_assert(NSLOT >= 4, "ring too small");
 };
 
-// delta of one query row: sum_d dO[row,d] * O[row,d] (fp32 accumulation of 16-bit inputs)
+// delta[row] = sum_d dO[row,d] * O[row,d] (fp32 accumulation of 16-bit inputs) for the 32 consecutive query rows
+// row0 ... row0 + 31 of slice bh, computed by one converged warp with coalesced 16-byte loads (D / 8 lanes per row,
+// butterfly reduction); lane l returns the value of row row0 + l, 0 for rows past Lq.
 template <int D, bool BF16>
-__device__ __forceinline__ float fa_bwd_delta_row(const void* o, const void* dout, size_t row) {
-  const uint4* po = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(o) + row * D);
-  const uint4* pd = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(dout) + row * D);
-  float s0 = 0.f, s1 = 0.f;
-#pragma unroll 4
-  for (int i = 0; i < D / 8; ++i) {
-    const uint4 a = __ldg(po + i), b = __ldg(pd + i);
-    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+__device__ __forceinline__ float fa_bwd_delta_warp(const void* o, const void* dout, int bh, int row0, int Lq, int lane) {
+  constexpr int LPR = D / 8;     // lanes per row
+  constexpr int RPI = 32 / LPR;  // rows per iteration
+  const uint16_t* po = reinterpret_cast<const uint16_t*>(o);
+  const uint16_t* pd = reinterpret_cast<const uint16_t*>(dout);
+  float mine = 0.f;
+  // Eight iterations' loads (16 x 16 bytes per lane) are issued before the first use: the loop is bound by the
+  // latency of global memory, not by its bandwidth.
+  constexpr int NIT = 32 / RPI, BATCH = NIT < 8 ? NIT : 8;
+#pragma unroll 1
+  for (int it0 = 0; it0 < NIT; it0 += BATCH) {
+    uint4 a[BATCH], b[BATCH];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      float a0, a1, b0, b1;
-      if (BF16) {
-        a0 = __uint_as_float(aw[e] << 16);
-        a1 = __uint_as_float(aw[e] & 0xffff0000u);
-        b0 = __uint_as_float(bw[e] << 16);
-        b1 = __uint_as_float(bw[e] & 0xffff0000u);
-      } else {
-        const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&aw[e]));
-        const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&bw[e]));
-        a0 = fa.x; a1 = fa.y; b0 = fb.x; b1 = fb.y;
+    for (int i = 0; i < BATCH; ++i) {
+      const int row = row0 + (it0 + i) * RPI + lane / LPR;
+      a[i] = make_uint4(0, 0, 0, 0);
+      b[i] = make_uint4(0, 0, 0, 0);
+      if (row < Lq) {
+        const size_t off = (static_cast<size_t>(bh) * Lq + row) * D + (lane % LPR) * 8;
+        a[i] = __ldg(reinterpret_cast<const uint4*>(po + off));
+        b[i] = __ldg(reinterpret_cast<const uint4*>(pd + off));
       }
-      s0 = fmaf(a0, b0, s0);
-      s1 = fmaf(a1, b1, s1);
+    }
+#pragma unroll
+    for (int i = 0; i < BATCH; ++i) {
+      const uint32_t aw[4] = {a[i].x, a[i].y, a[i].z, a[i].w}, bw[4] = {b[i].x, b[i].y, b[i].z, b[i].w};
+      float s = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float a0, a1, b0, b1;
+        if (BF16) {
+          a0 = __uint_as_float(aw[e] << 16);
+          a1 = __uint_as_float(aw[e] & 0xffff0000u);
+          b0 = __uint_as_float(bw[e] << 16);
+          b1 = __uint_as_float(bw[e] & 0xffff0000u);
+        } else {
+          const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&aw[e]));
+          const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&bw[e]));
+          a0 = fa.x; a1 = fa.y; b0 = fb.x; b1 = fb.y;
+        }
+        s = fmaf(a0, b0, s);
+        s = fmaf(a1, b1, s);
+      }
+#pragma unroll
+      for (int m = LPR / 2; m >= 1; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+      // row row0 + it * RPI + j is complete in lanes [j * LPR, (j + 1) * LPR); lane l keeps row l
+      const float v = __shfl_sync(0xffffffffu, s, (lane % RPI) * LPR);
+      if (lane / RPI == it0 + i) mine = v;
     }
   }
-  return s0 + s1;
+  return mine;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint64_t fa_bwd_unpack2(uint32_t packed) {
+  if constexpr (BF16) {
+    return f2_pack(__uint_as_float(packed << 16), __uint_as_float(packed & 0xffff0000u));
+  } else {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&packed));
+    return f2_pack(f.x, f.y);
+  }
 }
 
 template <class Cfg>
@@ -116,6 +169,13 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
                     const __grid_constant__ CUtensorMap tmT, const FaBwdParams p) {
   constexpr int D = Cfg::D, DB = Cfg::DB, NSLOT = Cfg::NSLOT, NC = Cfg::NC, ITEM = Cfg::ITEM_BYTES, BOX = Cfg::BOX_BYTES;
   constexpr bool DUAL = Cfg::DUAL, ROWK = Cfg::ROWK, BF16 = Cfg::BF16;
+  // FUSED: the element-wise step computes P and dS in one pass over the two accumulators (the dK kernel: keeping P
+  // packed in registers next to the per-column terms made its first pass 2900 cycles per block against 1650 in dQ)
+#ifndef AB200_FA_BWD_FUSED_DK
+#define AB200_FA_BWD_FUSED_DK 1
+#endif
+  constexpr bool FUSED = ROWK && DUAL && (AB200_FA_BWD_FUSED_DK != 0);
+  constexpr int NZ = DUAL ? 2 : 3;   // Z1 buffers: the dV kernel has no Z2 and uses its columns for a third one
   constexpr int PER_BLOCK = NC + 1;  // ring items per 128-wide block: C1 (, C2), T
 
   extern __shared__ uint8_t smem_raw[];
@@ -129,10 +189,10 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
   uint64_t* r_full = bars;                    // [1]
   uint64_t* slot_full = bars + 1;             // [NSLOT]
   uint64_t* slot_empty = slot_full + NSLOT;   // [NSLOT]
-  uint64_t* z_full = slot_empty + NSLOT;      // [2] GEMM1 into Z1 buffer complete
-  uint64_t* w_full = z_full + 2;              // [2] W written over the Z1 buffer (element-wise -> GEMM2)
-  uint64_t* z_free = w_full + 2;              // [2] GEMM2 of a block complete: its Z1/W buffer may be rewritten
-  uint64_t* z2_full = z_free + 2;             // [1] second GEMM1 complete
+  uint64_t* z_full = slot_empty + NSLOT;      // [NZ] GEMM1 into Z1 buffer complete
+  uint64_t* w_full = z_full + 3;              // [NZ] W written over the Z1 buffer (element-wise -> GEMM2)
+  uint64_t* z_free = w_full + 3;              // [NZ] GEMM2 of a block complete: its Z1/W buffer may be rewritten
+  uint64_t* z2_full = z_free + 3;             // [1] second GEMM1 complete
   uint64_t* z2_free = z2_full + 1;            // [1] Z2 read into registers (element-wise -> GEMM1 warp)
   uint64_t* acc_done = z2_free + 1;           // [1]
   uint64_t* acc_free = acc_done + 1;          // [1]
@@ -141,6 +201,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
   uint64_t* tab_free = tab_full + Cfg::NTAB;  // [NTAB] column table read into registers (element-wise -> helper)
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tab_free + Cfg::NTAB);
   CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 2);
+  float* dcache = reinterpret_cast<float*>(sRing + NSLOT * ITEM + Cfg::NTAB * 1024 + 1024);  // [DCACHE_BLOCKS][128]
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
   const int lane = threadIdx.x & 31;
@@ -166,12 +227,19 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
     }
     return it;
   };
-  // Work list: pairs (k-th heaviest, k-th lightest row block of a slice) handed out round-robin, as in chain_sm100.cuh.
+  // Work list: pairs (k-th heaviest, k-th lightest row block of a slice), as in chain_sm100.cuh, handed out round-robin
+  // in runs of G consecutive pairs per CTA. G = 1 keeps all CTAs on neighbouring slices (operands shared in L2); the
+  // dK kernel takes G = 2, i.e. four tiles of one slice in a row, so that its helper finds three of four delta
+  // tables in its cache (computing one takes about 5300 cycles, against 3200 for the rest of a block).
+  constexpr int G = (Cfg::WHICH == kFaBwdDK) ? 2 : 1;
   const int npair = (p.nrb + 1) / 2;
   const int n_super = (p.total_items / p.nrb) * npair;
-  const int n_steps = static_cast<int>(blockIdx.x) < n_super ? 2 * ((n_super - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+  const int per_window = static_cast<int>(gridDim.x) * G;
+  const int n_steps = 2 * G * ((n_super + per_window - 1) / per_window);
   auto decode_step = [&](int u, FaBwdItem& it) -> bool {
-    const int sidx = blockIdx.x + gridDim.x * (u >> 1);
+    const int s = u >> 1;
+    const int sidx = ((s / G) * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x)) * G + (s % G);
+    if (sidx >= n_super) return false;
     const int j = sidx % npair;
     const int k = (u & 1) ? p.nrb - 1 - j : j;
     if ((u & 1) && k == j) return false;
@@ -185,7 +253,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
       mbar_init(&slot_full[i], 1);
       mbar_init(&slot_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 3; ++i) {
       mbar_init(&z_full[i], 1);
       mbar_init(&w_full[i], 256);
       mbar_init(&z_free[i], 1);
@@ -220,7 +288,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
   pdl_launch_dependents();
-  const uint32_t tZ1 = tmem_base;        // two buffers of 128 columns; W overlays the first 64 of each
+  const uint32_t tZ1 = tmem_base;        // NZ buffers of 128 columns; W overlays part of each
   const uint32_t tZ2 = tmem_base + 256;
   const uint32_t tACC = tmem_base + 384;
 
@@ -284,11 +352,12 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
         ok = mbar_wait_warp(r_full, kacc & 1, ab, kFbR);
         for (int t = 0; t < n && ok; ++t) {
           const int g = g0 + t;
-          if (g >= 2) {
-            ok = mbar_wait_warp(&z_free[g & 1], ((g - 2) >> 1) & 1, ab, kFbZFree);
+          if (g >= NZ) {
+            ok = mbar_wait_warp(&z_free[g % NZ], (g / NZ - 1) & 1, ab, kFbZFree);
             if (!ok) break;
           }
           const int pos = b0 + (t == 0 ? 0 : NC + (t - 1) * PER_BLOCK);
+          if (lane == 0) AB200_FBTR(1, g, 0);
           {
             const int slot = pos % NSLOT;
             ok = mbar_wait_warp(&slot_full[slot], (pos / NSLOT) & 1, ab, kFbSlotFull);
@@ -296,7 +365,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
             tc_fence_after();
             if (elect_one()) {
               const uint32_t a = ring_addr + slot * ITEM;
-              const uint32_t tz = tZ1 + (g & 1) * 128;
+              const uint32_t tz = tZ1 + (g % NZ) * 128;
 #pragma unroll
               for (int b = 0; b < DB; ++b)
 #pragma unroll
@@ -304,10 +373,11 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
                   umma_ss(tz, umma_smem_desc(r1_addr + b * BOX + ks * 32, 16, 1024),
                           umma_smem_desc(a + b * BOX + ks * 32, 16, 1024), idesc_z, (b > 0 || ks > 0) ? 1u : 0u);
               tc_commit(&slot_empty[slot]);
-              tc_commit(&z_full[g & 1]);
+              tc_commit(&z_full[g % NZ]);
               if (!DUAL && t + 1 == n) tc_commit(r_free);
             }
             __syncwarp();
+            if (lane == 0) AB200_FBTR(1, g, 1);
           }
           if (DUAL) {
             if (g >= 1) {
@@ -315,6 +385,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
               ok = mbar_wait_warp(z2_free, (g - 1) & 1, ab, kFbZ2Free);
               if (!ok) break;
             }
+            if (lane == 0) AB200_FBTR(1, g, 2);
             const int slot = (pos + 1) % NSLOT;
             ok = mbar_wait_warp(&slot_full[slot], ((pos + 1) / NSLOT) & 1, ab, kFbSlotFull);
             if (!ok) break;
@@ -332,6 +403,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
               if (t + 1 == n) tc_commit(r_free);
             }
             __syncwarp();
+            if (lane == 0) AB200_FBTR(1, g, 3);
           }
         }
       } else {
@@ -341,8 +413,9 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
             ok = mbar_wait_warp(acc_free, (kacc - 1) & 1, ab, kFbAccFree);
             if (!ok) break;
           }
-          ok = mbar_wait_warp(&w_full[g & 1], (g >> 1) & 1, ab, kFbWFull);
+          ok = mbar_wait_warp(&w_full[g % NZ], (g / NZ) & 1, ab, kFbWFull);
           if (!ok) break;
+          if (lane == 0) AB200_FBTR(1, g, 4);
           const int pos = b0 + NC + t * PER_BLOCK + (t + 1 < n ? NC : 0);
           const int slot = pos % NSLOT;
           ok = mbar_wait_warp(&slot_full[slot], (pos / NSLOT) & 1, ab, kFbSlotFull);
@@ -350,15 +423,16 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
           tc_fence_after();
           if (elect_one()) {
             const uint32_t a = ring_addr + slot * ITEM;
-            const uint32_t tw = tZ1 + (g & 1) * 128;
+            const uint32_t tw = tZ1 + (g % NZ) * 128;
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)
               umma_ts(tACC, tw + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8), umma_smem_desc(a + ks * 2048, BOX, 1024), idesc_acc, (t > 0 || ks > 0) ? 1u : 0u);
             tc_commit(&slot_empty[slot]);
-            tc_commit(&z_free[g & 1]);
+            tc_commit(&z_free[g % NZ]);
             if (t + 1 == n) tc_commit(acc_done);
           }
           __syncwarp();
+          if (lane == 0) AB200_FBTR(1, g, 5);
         }
       }
       b0 += n * PER_BLOCK;
@@ -392,9 +466,12 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
       }
       // per-row terms of the dQ kernel (rows are queries): -lse * log2(e) and -delta * scale
       float row_nl2 = 0.f, row_nds = 0.f;
-      if (!ROWK && grow < p.Lq) {
-        row_nl2 = -p.lse[static_cast<size_t>(bh) * p.Lq + grow] * kLog2e;
-        row_nds = -fa_bwd_delta_row<D, BF16>(p.o, p.dout, static_cast<size_t>(bh) * p.Lq + grow) * p.scale;
+      if (!ROWK) {
+        const float delta = fa_bwd_delta_warp<D, BF16>(p.o, p.dout, bh, grow - lane, p.Lq, lane);
+        if (grow < p.Lq) {
+          row_nl2 = -p.lse[static_cast<size_t>(bh) * p.Lq + grow] * kLog2e;
+          row_nds = -delta * p.scale;
+        }
       }
       for (int t = 0; t < n_iter; ++t) {
         const int g = g0 + t;
@@ -402,6 +479,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
         // per-column terms of the dV / dK kernels (columns are queries), from the helper's table: the value of column
         // (chunk q, lane) sits in a register of that lane and travels by warp shuffle
         float col_nl2[2] = {0.f, 0.f}, col_nds[2] = {0.f, 0.f};
+        if (threadIdx.x == 0) AB200_FBTR(0, g, 0);
         if (ROWK) {
           const int ts = g % Cfg::NTAB;
           ok = mbar_wait_warp(&tab_full[ts], (g / Cfg::NTAB) & 1, ab, kFbTabFull);
@@ -415,55 +493,98 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
           mbar_arrive(&tab_free[ts]);
         }
         const bool diag = p.causal && col0 == row0;  // the only block that straddles the diagonal (Lq == Lkv)
-        ok = mbar_wait_warp(&z_full[g & 1], (g >> 1) & 1, ab, kFbZFull);
+        if (threadIdx.x == 0) AB200_FBTR(0, g, 1);
+        ok = mbar_wait_warp(&z_full[g % NZ], (g / NZ) & 1, ab, kFbZFull);
         if (!ok) break;
+        if (threadIdx.x == 0) AB200_FBTR(0, g, 2);
+        tc_fence_after();
+        const uint32_t tz = tmem_addr(tZ1 + (g % NZ) * 128, lane_base, 0);
+        const uint32_t tz2 = tmem_addr(tZ2, lane_base, 0);
+        // Step 1, P = exp2(Z1 * scale * log2 e - lse * log2 e) for this thread's 64 columns, packed to 16 bits. The dV
+        // kernel stores it as W; the others keep it in registers: this part runs while the second GEMM1 is still
+        // in flight, and Z2 (single buffered) is then held only for a short multiply.
+        auto prob2 = [&](uint32_t za, uint32_t zb, int q, int c, float& p0, float& p1) {
+          const int chunk = 2 * grp + q;
+          uint64_t nl2 = f2_pack(row_nl2, row_nl2);
+          if (ROWK) nl2 = f2_pack(__shfl_sync(0xffffffffu, col_nl2[q], c), __shfl_sync(0xffffffffu, col_nl2[q], c + 1));
+          float a0, a1;
+          f2_unpack(ffma2(f2_pack(__uint_as_float(za), __uint_as_float(zb)), sl2, nl2), a0, a1);
+          // every other pair on the FMA pipes: the special-function unit (16 exp2 per clock and SM) would otherwise
+          // bound the step
+          if ((c >> 1) & 1) {
+            exp2_poly2(f2_pack(a0, a1), p0, p1);
+          } else {
+            p0 = ex2_approx(a0);
+            p1 = ex2_approx(a1);
+          }
+          if (diag) {
+            const int cc = chunk * 32 + c;  // column inside the block; the row inside the block is tid
+            if (ROWK ? (cc < tid) : (cc > tid)) p0 = 0.f;
+            if (ROWK ? (cc + 1 < tid) : (cc + 1 > tid)) p1 = 0.f;
+          }
+        };
+        uint32_t pp[FUSED ? 1 : 32];
+        if constexpr (!FUSED) {
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int chunk = 2 * grp + q;  // 32-column chunk of the block
+            uint32_t z1[32];
+            tmem_ld32(tz + chunk * 32, z1);
+            tc_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+              float p0, p1;
+              prob2(z1[c], z1[c + 1], q, c, p0, p1);
+              pp[q * 16 + (c >> 1)] = pack2<BF16>(p0, p1);
+            }
+            if (!DUAL) tmem_st16(tz + grp * 64 + q * 16, &pp[q * 16]);
+          }
+        }
         if (DUAL) {
+          // Step 2, dS = P .* (dP * scale - delta * scale)
+          if (threadIdx.x == 0) AB200_FBTR(0, g, 3);
           ok = mbar_wait_warp(z2_full, g & 1, ab, kFbZ2Full);
           if (!ok) break;
-        }
-        tc_fence_after();
-        const uint32_t tz = tmem_addr(tZ1 + (g & 1) * 128, lane_base, 0);
-        const uint32_t tz2 = tmem_addr(tZ2, lane_base, 0);
+          if (threadIdx.x == 0) AB200_FBTR(0, g, 4);
+          tc_fence_after();
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const int chunk = 2 * grp + q;  // 32-column chunk of the block
-          uint32_t z1[32], z2[32];
-          tmem_ld32(tz + chunk * 32, z1);
-          if (DUAL) tmem_ld32(tz2 + chunk * 32, z2);
-          tc_wait_ld();
-          if (DUAL && q == 1) {
-            // this thread's part of Z2 is in registers: the second GEMM1 of the next block may overwrite it
-            tc_fence_before();
-            mbar_arrive(z2_free);
-          }
-          uint32_t pk[16];
+          for (int q = 0; q < 2; ++q) {
+            const int chunk = 2 * grp + q;
+            uint32_t z2[32], z1[FUSED ? 32 : 1];
+            tmem_ld32(tz2 + chunk * 32, z2);
+            if constexpr (FUSED) tmem_ld32(tz + chunk * 32, z1);
+            tc_wait_ld();
+            if (q == 1) {
+              // this thread's part of Z2 is in registers: the second GEMM1 of the next block may overwrite it
+              tc_fence_before();
+              mbar_arrive(z2_free);
+              if (threadIdx.x == 0) AB200_FBTR(0, g, 5);
+            }
+            uint32_t pk[16];
 #pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            uint64_t nl2 = f2_pack(row_nl2, row_nl2), nds = f2_pack(row_nds, row_nds);
-            if (ROWK) {
-              nl2 = f2_pack(__shfl_sync(0xffffffffu, col_nl2[q], c), __shfl_sync(0xffffffffu, col_nl2[q], c + 1));
-              if (DUAL) nds = f2_pack(__shfl_sync(0xffffffffu, col_nds[q], c), __shfl_sync(0xffffffffu, col_nds[q], c + 1));
-            }
-            float a0, a1;
-            f2_unpack(ffma2(f2_pack(__uint_as_float(z1[c]), __uint_as_float(z1[c + 1])), sl2, nl2), a0, a1);
-            float p0 = ex2_approx(a0), p1 = ex2_approx(a1);
-            if (diag) {
-              const int cc = chunk * 32 + c;  // column inside the block; the row inside the block is tid
-              if (ROWK ? (cc < tid) : (cc > tid)) p0 = 0.f;
-              if (ROWK ? (cc + 1 < tid) : (cc + 1 > tid)) p1 = 0.f;
-            }
-            if (DUAL) {
-              // dS = P .* (dP * scale - delta * scale)
+            for (int c = 0; c < 32; c += 2) {
+              uint64_t nds = f2_pack(row_nds, row_nds);
+              if (ROWK) nds = f2_pack(__shfl_sync(0xffffffffu, col_nds[q], c), __shfl_sync(0xffffffffu, col_nds[q], c + 1));
               const uint64_t t2 = ffma2(f2_pack(__uint_as_float(z2[c]), __uint_as_float(z2[c + 1])), sc2, nds);
-              f2_unpack(fmul2(f2_pack(p0, p1), t2), p0, p1);
+              uint64_t pr2;
+              if constexpr (FUSED) {
+                float p0, p1;
+                prob2(z1[c], z1[c + 1], q, c, p0, p1);
+                pr2 = f2_pack(p0, p1);
+              } else {
+                pr2 = fa_bwd_unpack2<BF16>(pp[q * 16 + (c >> 1)]);
+              }
+              float w0, w1;
+              f2_unpack(fmul2(pr2, t2), w0, w1);
+              pk[c >> 1] = pack2<BF16>(w0, w1);
             }
-            pk[c >> 1] = pack2<BF16>(p0, p1);
+            tmem_st16(tz + grp * 64 + q * 16, pk);
           }
-          tmem_st16(tz + grp * 64 + q * 16, pk);
         }
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(&w_full[g & 1]);
+        mbar_arrive(&w_full[g % NZ]);
+        if (threadIdx.x == 0) AB200_FBTR(0, g, 6);
       }
       if (!ok) break;
       g0 += n_iter;
@@ -479,6 +600,8 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
     int pu = 0, pt = 0, gp = 0;
     FaBwdItem pit;
     bool pvalid = false;
+    int cache_bh = -1;
+    uint32_t cache_valid = 0;  // bit b: block b of slice cache_bh is in dcache (each thread reads back only what it wrote)
     auto p_next_item = [&]() {
       pvalid = false;
       while (pu < n_steps) {
@@ -498,13 +621,32 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
         ok = mbar_wait_warp(&tab_free[ts], ((gp / Cfg::NTAB) - 1) & 1, ab, kFbTabFree);
         if (!ok) return false;
       }
+      if (tid == 0) AB200_FBTR(2, gp, 0);
       const int qi = (pit.t_start + pt) * 128 + tid;
       const size_t row = static_cast<size_t>(pit.bh) * p.Lq + qi;
       float* tab = ctab + ts * 256;
       // queries past the end: lse = +inf, i.e. P = 0
       tab[128 + tid] = (qi < p.Lq) ? -p.lse[row] * kLog2e : __int_as_float(0xff800000);
-      if (DUAL) tab[tid] = (qi < p.Lq) ? -fa_bwd_delta_row<D, BF16>(p.o, p.dout, row) * p.scale : 0.f;
+      if (DUAL) {
+        const int qb = pit.t_start + pt;
+        if (pit.bh != cache_bh) {
+          cache_bh = pit.bh;
+          cache_valid = 0;
+        }
+        float nds;
+        if (qb < Cfg::DCACHE_BLOCKS && ((cache_valid >> qb) & 1u)) {
+          nds = dcache[qb * 128 + tid];
+        } else {
+          nds = -fa_bwd_delta_warp<D, BF16>(p.o, p.dout, pit.bh, qi - lane, p.Lq, lane) * p.scale;
+          if (qb < Cfg::DCACHE_BLOCKS) {
+            dcache[qb * 128 + tid] = nds;
+            cache_valid |= 1u << qb;
+          }
+        }
+        tab[tid] = nds;
+      }
       mbar_arrive(&tab_full[ts]);
+      if (tid == 0) AB200_FBTR(2, gp, 1);
       ++gp;
       if (++pt == pit.n_iter) p_next_item();
       return true;
