@@ -174,7 +174,13 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
 #ifndef AB200_FA_BWD_FUSED_DK
 #define AB200_FA_BWD_FUSED_DK 1
 #endif
-  constexpr bool FUSED = ROWK && DUAL && (AB200_FA_BWD_FUSED_DK != 0);
+#ifndef AB200_FA_BWD_FUSED_DQ
+#define AB200_FA_BWD_FUSED_DQ 0
+#endif
+#ifndef AB200_FA_BWD_POLY
+#define AB200_FA_BWD_POLY 0
+#endif
+  constexpr bool FUSED = DUAL && (ROWK ? (AB200_FA_BWD_FUSED_DK != 0) : (AB200_FA_BWD_FUSED_DQ != 0));
   constexpr int NZ = DUAL ? 2 : 3;   // Z1 buffers: the dV kernel has no Z2 and uses its columns for a third one
   constexpr int PER_BLOCK = NC + 1;  // ring items per 128-wide block: C1 (, C2), T
 
@@ -509,9 +515,10 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
           if (ROWK) nl2 = f2_pack(__shfl_sync(0xffffffffu, col_nl2[q], c), __shfl_sync(0xffffffffu, col_nl2[q], c + 1));
           float a0, a1;
           f2_unpack(ffma2(f2_pack(__uint_as_float(za), __uint_as_float(zb)), sl2, nl2), a0, a1);
-          // every other pair on the FMA pipes: the special-function unit (16 exp2 per clock and SM) would otherwise
-          // bound the step
-          if ((c >> 1) & 1) {
+          // AB200_FA_BWD_POLY=1 puts every other pair on the FMA pipes; measured at B=8 H=16 L=4096 d=128: 5.3-5.7 ms
+          // per backward against 5.1-5.3 ms with all of them on the special-function unit (the step is bound by
+          // instruction issue, not by that unit)
+          if (AB200_FA_BWD_POLY && ((c >> 1) & 1)) {
             exp2_poly2(f2_pack(a0, a1), p0, p1);
           } else {
             p0 = ex2_approx(a0);
@@ -525,16 +532,17 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
         };
         uint32_t pp[FUSED ? 1 : 32];
         if constexpr (!FUSED) {
+          // both 32-column loads are issued before the wait: one exposed TMEM latency per block instead of two
+          uint32_t z1[2][32];
+          tmem_ld32(tz + (2 * grp) * 32, z1[0]);
+          tmem_ld32(tz + (2 * grp + 1) * 32, z1[1]);
+          tc_wait_ld();
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
-            const int chunk = 2 * grp + q;  // 32-column chunk of the block
-            uint32_t z1[32];
-            tmem_ld32(tz + chunk * 32, z1);
-            tc_wait_ld();
 #pragma unroll
             for (int c = 0; c < 32; c += 2) {
               float p0, p1;
-              prob2(z1[c], z1[c + 1], q, c, p0, p1);
+              prob2(z1[q][c], z1[q][c + 1], q, c, p0, p1);
               pp[q * 16 + (c >> 1)] = pack2<BF16>(p0, p1);
             }
             if (!DUAL) tmem_st16(tz + grp * 64 + q * 16, &pp[q * 16]);
