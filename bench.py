@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Headline benchmark: flash-attention forward TFLOPS on B200 (and the CPU reference beside it).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload C2|C2causal|C2bf16|C1|C3|C4|C5sq|C5dec]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload C2|C2causal|C2bf16|C2bwd|C1|C3|C4|C5sq|C5dec]
     python bench.py --impl reference ...          # the reference's CPU formula on the host cores
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
@@ -42,6 +42,9 @@ WORKLOADS = {
     "C2": (8, 16, 4096, 4096, 128, 128, "fp16", False),
     "C2causal": (8, 16, 4096, 4096, 128, 128, "fp16", True),
     "C2bf16": (8, 16, 4096, 4096, 128, 128, "bf16", False),
+    # flash-attention forward + backward (device timing only: 1 + 3 launches per step; 2 + 5 GEMMs counted)
+    "C2bwd": (8, 16, 4096, 4096, 128, 128, "fp16", False),
+    "C2bwdcausal": (8, 16, 4096, 4096, 128, 128, "fp16", True),
     "C2bf16causal": (8, 16, 4096, 4096, 128, 128, "bf16", True),
     "C5sq": (16, 32, 16384, 16384, 128, 128, "bf16", False),
     "C5sqcausal": (16, 32, 16384, 16384, 128, 128, "bf16", True),
@@ -49,6 +52,7 @@ WORKLOADS = {
 }
 METRIC = "attn fwd TFLOPS at B=8,H=16,L=4096,d=128 fp16"
 UNIT = "TFLOP/s"
+ATTN_BWD = ("C2bwd", "C2bwdcausal")
 RETNET = {"C3": "fwd", "C4": "fwd+bwd", "C3mask": "fwd", "C4mask": "fwd+bwd"}
 # dram__bytes_read.sum + dram__bytes_write.sum per step from the ncu captures summarised under profiles/
 # (fa_fwd_sm100_kernel_C2_fp16.md, chain_pair_sm100_kernel_C4_retnet_fp16.md); None where no capture was taken
@@ -62,6 +66,8 @@ def metric_name(workload):
     if workload == "C2":
         return METRIC
     B, H, Lq, Lkv, dqk, dv, dtype, causal = WORKLOADS[workload]
+    if workload in ATTN_BWD:
+        return "attn fwd+bwd TFLOPS at B=%d,H=%d,L=%d,d=%d %s%s" % (B, H, Lq, dqk, dtype, " causal" if causal else "")
     return "attn fwd TFLOPS at B=%d,H=%d,Lq=%d,Lkv=%d,d=%d %s%s" % (B, H, Lq, Lkv, dqk, dtype, " causal" if causal else "")
 
 
@@ -70,6 +76,8 @@ def flops_of(workload):
     f = flops_fwd(B, H, Lq, Lkv, dqk, dv, causal)
     if RETNET.get(workload) == "fwd+bwd":
         f += f / (dqk + dv) * (3 * dqk + 2 * dv)
+    if workload in ATTN_BWD:
+        f += f / 2 * 5  # S, dP, dV, dQ, dK
     return f
 
 
@@ -153,19 +161,21 @@ def cpu_reference_run(workload, steps, warmup, budget_s=20.0):
     masks = oracle.decay_mask(H, Lq, Lkv) if ret else None
 
     def run_slice(i, sl):
-        if not ret:
+        if workload in ATTN_BWD:
+            oracle.attention_bwd_autograd(sl[0], sl[1], sl[2], sl[3], scale, causal)
+        elif not ret:
             oracle.attention_fwd(sl[0], sl[1], sl[2], scale, causal)
         elif ret == "fwd":
             oracle.retnet_fwd(sl[0], sl[1], sl[2], masks[i % H], scale)
         else:  # the reference's own way: autograd through the formula with r detached (ref_op.py:8-13)
             oracle.retnet_bwd_autograd(sl[0], sl[1], sl[2], masks[i % H], sl[3], scale)
 
-    first = oracle.slice_inputs(workload, 0, 0, H, Lq, Lkv, dqk, dv, dt, with_do=bool(ret))
+    first = oracle.slice_inputs(workload, 0, 0, H, Lq, Lkv, dqk, dv, dt, with_do=bool(ret) or workload in ATTN_BWD)
     t0 = time.perf_counter()
     run_slice(0, first)
     per_slice = time.perf_counter() - t0
     n_slices = max(1, min(B * H, int(budget_s / max(per_slice, 1e-6) / max(1, steps + warmup))))
-    slices = [oracle.slice_inputs(workload, (i // H) % B, i % H, H, Lq, Lkv, dqk, dv, dt, with_do=bool(ret))
+    slices = [oracle.slice_inputs(workload, (i // H) % B, i % H, H, Lq, Lkv, dqk, dv, dt, with_do=bool(ret) or workload in ATTN_BWD)
               for i in range(n_slices)]
     fl = flops_of(workload) * n_slices / (B * H)
 
@@ -199,7 +209,8 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     B, H, Lq, Lkv, dqk, dv, dtype, causal = WORKLOADS[args.workload]
-    opname = "RetNet parallel " + RETNET[args.workload] + " (decay mask)" if args.workload in RETNET else "flash-attention forward"
+    opname = "RetNet parallel " + RETNET[args.workload] + " (decay mask)" if args.workload in RETNET else (
+        "flash-attention forward + backward" if args.workload in ATTN_BWD else "flash-attention forward")
     config = {"workload": f"{args.workload}: {opname} B={B} H={H} Lq={Lq} Lkv={Lkv} dqk={dqk} dv={dv} "
                           f"{dtype} causal={causal} scale=1/sqrt(dqk), per GPU",
               "slices_per_gpu": B * H, "sharding": "(batch, head) slices, no collective",
@@ -268,6 +279,18 @@ def main():
             if ret != "fwd":
                 _lib.check(lib.attn_b200_ret_bwd(P(q), P(k), P(v), P(maskd), P(do), P(r), P(dq), P(dk), P(dvo), None, B, H,
                                                  Lq, Lkv, dqk, dv, code, scale, P(dec), 1, sp))
+    elif args.workload in ATTN_BWD:
+        lse = torch.empty(B, H, Lq, device=dev, dtype=torch.float32)
+        do = torch.randn(B, H, Lq, dv, device=dev, generator=g).to(tdt)
+        dq, dk, dvo = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        launches_per_step = 4
+        sp = ctypes.c_void_p(stream.cuda_stream)
+        args.no_e2e = True
+
+        def step():
+            _lib.check(lib.attn_b200_fa_fwd(P(q), P(k), P(v), P(o), P(lse), B, H, Lq, Lkv, dqk, dv, code, scale, int(causal), sp))
+            _lib.check(lib.attn_b200_fa_bwd(P(q), P(k), P(v), P(o), P(do), P(lse), P(dq), P(dk), P(dvo), B, H, Lq, Lkv, dqk,
+                                            code, scale, int(causal), sp))
     else:
         def step():
             _lib.check(lib.attn_b200_fa_fwd(P(q), P(k), P(v), P(o), None, B, H, Lq, Lkv, dqk, dv, code, scale,
@@ -355,7 +378,8 @@ def main():
                          "peak_source": f"{peak_src} (cuBLAS bf16 burst; the timed region is a burst of a few tens of ms)",
                          "peak_sustained": peak_sus, "frac_of_sustained": (achieved / peak_sus if peak_sus else None),
                          "flops_per_step": fl_gpu, "launches_per_step": launches_per_step,
-                         "kernel": "chain_pair_sm100_kernel" if ret else "fa_fwd_sm100_kernel"},
+                         "kernel": ("chain_pair_sm100_kernel" if ret else
+                                    "fa_bwd_sm100_kernel" if args.workload in ATTN_BWD else "fa_fwd_sm100_kernel")},
             "clocks": clocks,
             # launches inside the two timed regions; the end-to-end leg launches once per batch entry (the host-buffer
             # operators cut the batch into B pieces)
