@@ -93,6 +93,12 @@ def test_many_slices_deterministic_and_linear_in_dout(lib):
         assert oracle.within(oracle.error_stats(got[:1, :4], want), "fp16", scale_by_peak=True)
 
 
+def test_more_query_blocks_than_the_delta_cache_holds(lib):
+    """The dK kernel caches delta for the first 32 query blocks of a slice; 33 blocks exercise both paths."""
+    q, k, v, do = rand_case(17, 1, 2, 4224, 256, 64, torch.float16)
+    check(run_fwd_bwd(lib, q, k, v, do, 0.125, False), q, k, v, do, 0.125, False, "fp16")
+
+
 def test_argument_errors(lib):
     q, k, v, do = (t.cuda() for t in rand_case(9, 1, 1, 128, 256, 128, torch.float16))
     o = torch.empty_like(q)
