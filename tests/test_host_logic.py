@@ -125,6 +125,13 @@ def test_argument_validation_without_gpu(lib):
     assert lib.attn_b200_fa_fwd(p, p, p, p, None, 1, 1, 128, 128, 128, 128, 7, 0.1, 0, None) == 1  # dtype
     assert lib.attn_b200_fa_fwd(p, p, p, p, None, 0, 1, 128, 128, 128, 128, 0, 0.1, 0, None) == 1  # B
     assert lib.attn_b200_fa_fwd(p, p, p, p, None, 1, 1, 128, 128, 128, 128, 0, -1.0, 0, None) == 1  # scale
+    # attention backward: (q,k,v,o,do,lse,dq,dk,dv, B,H,Lq,Lkv,d, dtype, scale, causal, stream)
+    rc = lib.attn_b200_fa_bwd(p, p, p, None, p, p, p, p, p, 1, 1, 128, 128, 128, 0, 0.1, 0, None)
+    assert rc == 1 and b"null" in lib.attn_b200_last_error()
+    assert lib.attn_b200_fa_bwd(p, p, p, p, p, p, p, p, p, 1, 1, 128, 128, 96, 0, 0.1, 0, None) == 2    # head dimension
+    assert lib.attn_b200_fa_bwd(p, p, p, p, p, p, p, p, p, 1, 1, 128, 256, 128, 0, 0.1, 1, None) == 2   # causal, Lq != Lkv
+    assert lib.attn_b200_fa_bwd(p, p, p, p, p, p, p, p, p, 1, 1, 128, 128, 128, 3, 0.1, 0, None) == 1   # dtype
+    assert lib.attn_b200_fa_bwd(p, p, p, p, p, p, p, p, p, 1, 0, 128, 128, 128, 0, 0.1, 0, None) == 1   # H
 
 
 def test_per_config_library_builds_and_exports_reference_symbols(tmp_path):
