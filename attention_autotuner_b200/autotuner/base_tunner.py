@@ -197,7 +197,7 @@ class BaseTunner:
 
         os.makedirs(self.cache_path, exist_ok=True)
         with open(self._cache_file(), "w") as f:
-            json.dump(best_config.__dict__, f)
+            json.dump(best_config.to_dict(), f)
         return best_config
 
     # ------------------------------------------------------------------ cache

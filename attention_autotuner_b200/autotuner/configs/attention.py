@@ -42,7 +42,6 @@ class AttnConfig(BaseConfig):
         self.Bc = 128
         self.Nthreads = 128 * self.q_tiles * self.softmax_split + 128
         self.operation = "attn"
-        self.template_dir = os.path.join(CSRC_DIR, "kernels", "attention")
 
     # ---- resources (bytes / columns), used by the tuner's feasibility check
     def smem_bytes(self) -> int:

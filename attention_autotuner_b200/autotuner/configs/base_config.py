@@ -9,6 +9,11 @@ accepted so that code constructing configs the old way keeps working; the fields
 anything are stored and otherwise ignored (listed in LEGACY_FIELDS).
 """
 
+import os
+
+CSRC_DIR = os.path.normpath(os.path.join(os.path.dirname(__file__), "..", "..", "csrc"))
+TEMPLATE_SUBDIR = {"attn": ("attention",), "ret": ("retnet",), "ret_bwd": ("retnet", "bwd")}
+
 LEGACY_FIELDS = ("BlockKSmem", "BlockKSmem2", "num_stages_qk", "num_stages_v", "num_stages_mask", "unrollLastIter",
                  "warps_mma1_n", "warps_mma_n", "mmawarpsN", "mmawarpsN_dv", "mmawarpsN_dk", "mmawarpsN_dq",
                  "num_stages_dv", "num_stages_ds", "num_stages_dq")
@@ -59,11 +64,21 @@ class BaseConfig:
         self.dtype = dtype        # "fp16" | "bf16"
         self.fuse_type = "tmem"   # the reference's "register"/"shared" styles both map onto tensor memory
         self.operation = None
-        self.template_dir = None
 
     def set_fuse_type(self, fuse_type):
         """Accepted for compatibility ("register", "shared"); accumulators always live in tensor memory."""
         self.fuse_type = "tmem"
+
+    @property
+    def template_dir(self) -> str:
+        """Directory of this operation's launch-shim template (profile_code.py). Always derived from ``operation``
+        and the location of the installed package; never stored, so cache files written on one machine load on
+        any other (the reference stores an absolute path, python/autotuner/configs/attention.py:25)."""
+        return os.path.join(CSRC_DIR, "kernels", *TEMPLATE_SUBDIR[self.operation])
+
+    def to_dict(self) -> dict:
+        """JSON-serialisable fields of the record: what the tuner writes to its cache file."""
+        return {k: v for k, v in self.__dict__.items() if k != "template_dir"}
 
     @property
     def bf16(self) -> int:
@@ -84,7 +99,8 @@ class BaseConfig:
     @classmethod
     def from_dict(cls, dd: dict):
         cc = cls.__new__(cls)
-        cc.__dict__.update(dd)
+        # a path read from a file must never decide which template gets executed: drop it, template_dir is derived
+        cc.__dict__.update({k: v for k, v in dd.items() if k != "template_dir"})
         cc.__dict__.setdefault("dtype", "fp16")
         cc.__dict__.setdefault("fuse_type", "tmem")
         if cc.__dict__.get("operation") == "attn":

@@ -45,7 +45,6 @@ class RetConfig(BaseConfig):
         self.Bc = 128
         self.Nthreads = 384
         self.operation = "ret"
-        self.template_dir = os.path.join(CSRC_DIR, "kernels", "retnet")
 
     def smem_bytes(self) -> int:
         return _chain_smem(self.Kd)[0]

@@ -32,7 +32,6 @@ class RetBwdConfig(BaseConfig):
         self.Bc = 128
         self.Nthreads = 384
         self.operation = "ret_bwd"
-        self.template_dir = os.path.join(CSRC_DIR, "kernels", "retnet", "bwd")
 
     def smem_bytes(self) -> int:
         return max(_chain_smem(self.Kd)[0], _chain_smem(self.D)[0])

@@ -28,11 +28,32 @@ def _sources():
     return out
 
 
+def source_hash() -> str:
+    """Hash of every source the library is compiled from (file names and contents)."""
+    import hashlib
+    h = hashlib.sha1()
+    for path in _sources():
+        if os.path.exists(path):
+            with open(path, "rb") as f:
+                h.update(os.path.basename(path).encode() + b"\0" + f.read() + b"\0")
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _stamp_path() -> str:
+    return LIB_PATH + ".srchash"
+
+
 def is_stale() -> bool:
+    """True when the library is missing or was built from other sources than the ones present now. Decided by a
+    hash of the sources stored beside the library, not by file times (a fresh checkout has arbitrary ones)."""
     if not os.path.exists(LIB_PATH):
         return True
-    t = os.path.getmtime(LIB_PATH)
-    return any(os.path.exists(s) and os.path.getmtime(s) > t for s in _sources())
+    try:
+        with open(_stamp_path()) as f:
+            return f.read().strip() != source_hash()
+    except OSError:
+        return True
 
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
@@ -47,6 +68,8 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
         raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
     if verbose:
         print(res.stderr)
+    with open(_stamp_path(), "w") as f:
+        f.write(source_hash() + "\n")
     return LIB_PATH
 
 

@@ -212,4 +212,8 @@ int attn_b200_selftest_pair(const void* a, const void* b, const void* t, float* 
   return selftest_pair(a, b, t, z, d, K, N2, dtype, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int attn_b200_selftest_wait(int limit_us, int whole_warp, void* stream) {
+  return selftest_wait(limit_us, whole_warp, reinterpret_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

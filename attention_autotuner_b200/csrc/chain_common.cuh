@@ -48,6 +48,21 @@ enum ChainTag : int {
   kCtR = 11, kCtSlotFull = 12, kCtSlotEmpty = 13, kCtZFull = 14, kCtWFull = 15, kCtAccDone = 16, kCtAccFree = 17, kCtRFree = 18, kCtZFree = 19
 };
 
+// The forward keeps W = S~ UNNORMALISED in 16 bits (the division by r happens once, in the epilogue), whereas the
+// reference divides by the running r before the fp16 cast (csrc/kernels/retnet/regfuse/regfuse.h:306-316) and can
+// never leave the fp16 range. cvt.rn.satfinite clamps |S~| > 65504 silently, which would make the output wrong, so a
+// clamp is detected and reported (status 2, read by the host like a timeout). No element can exceed 65504 unless the
+// running sum of |W| over the thread's columns does, so the common case costs one comparison per 32 columns; only
+// then are the packed values inspected.
+__device__ __forceinline__ void chain_check_saturation(float abs_sum_so_far, const uint32_t (&pk)[16]) {
+  if (abs_sum_so_far > 65504.0f) {
+    bool sat = false;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) sat |= half2_has_maxnorm(pk[i]);
+    if (sat) report_saturation();
+  }
+}
+
 // Element-wise step of one block, W = Z .* mask .* scale (./ r), for the thread that owns TMEM lane (row) `tz >> 16`:
 // it reads fp32 values of its row of Z at `tz`, applies the row factor and the mask (decay factors built in
 // registers, or a general 16-bit mask tensor) and writes packed 16-bit pairs of W over the first columns of the same
@@ -127,6 +142,7 @@ __device__ __forceinline__ void chain_ew_decay2(uint32_t tz, float rowf, float l
       pk[2 * c4] = pack2<BF16>(w0, w1);
       pk[2 * c4 + 1] = pack2<BF16>(w2, w3);
     }
+    if constexpr (MODE == kChainFwd && !BF16) chain_check_saturation((s0 + s1) + (s2 + s3), pk);
     tmem_st16(tz + (SPLITW ? (QD0 >> 1) * 64 + q * 16 : (QD0 + q) * 16), pk);
   }
   if (MODE == kChainFwd) rsum += (s0 + s1) + (s2 + s3);
@@ -260,6 +276,7 @@ __device__ __forceinline__ void chain_ew_mask2(uint32_t tz, const uint32_t (&mk)
       pk[2 * c4] = pack2<BF16>(w0, w1);
       pk[2 * c4 + 1] = pack2<BF16>(w2, w3);
     }
+    if constexpr (MODE == kChainFwd && !BF16) chain_check_saturation((s0 + s1) + (s2 + s3), pk);
     tmem_st16(tz + (SPLITW ? (QD0 >> 1) * 64 + q * 16 : (QD0 + q) * 16), pk);
   }
   if (MODE == kChainFwd) rsum += (s0 + s1) + (s2 + s3);

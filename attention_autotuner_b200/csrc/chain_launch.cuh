@@ -44,7 +44,7 @@ inline int ret_check_common(const RetArgs& a, const char* what) {
   if (!isfinite(a.scale) || a.scale == 0.f) return fail(kErrInvalidArgument, "%s: scale must be finite and non-zero", what);
   if (!aligned16(a.q) || !aligned16(a.k) || !aligned16(a.v) || (a.mask && !aligned16(a.mask)))
     return fail(kErrInvalidArgument, "%s: tensors must be 16-byte aligned", what);
-  return kOk;
+  return check_prior_status(what);
 }
 
 // CTAs of the persistent grid: one per SM (a CTA uses all of shared and tensor memory). The kernels hand out

@@ -63,6 +63,7 @@ int fa_bwd_launch(const FaBwdArgs& a, cudaStream_t stream) {
   const void* ptrs[] = {a.q, a.k, a.v, a.o, a.dout, a.dq, a.dk, a.dv};
   for (const void* ptr : ptrs)
     if (!aligned32(ptr)) return fail(kErrInvalidArgument, "fa_bwd: tensors must be 32-byte aligned");
+  if (int prior = check_prior_status("fa_bwd")) return prior;
   FaBwdParams p{};
   p.lse = a.lse;
   p.o = a.o;

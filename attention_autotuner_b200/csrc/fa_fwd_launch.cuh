@@ -34,6 +34,7 @@ int fa_fwd_launch(const FaFwdArgs& a, cudaStream_t stream) {
 
   CUtensorMap tq, tk, tv;
   int rc;
+  if ((rc = check_prior_status("fa_fwd"))) return rc;
   if ((rc = bind_device_of(a.q, "fa_fwd"))) return rc;
   if ((rc = make_tmap_3d(&tq, a.q, Cfg::BF16, Cfg::DQK, a.Lq, a.BH, 64, Cfg::BM))) return rc;
   if ((rc = make_tmap_3d(&tk, a.k, Cfg::BF16, Cfg::DQK, a.Lkv, a.BH, 64, Cfg::BN))) return rc;
@@ -70,6 +71,7 @@ int fa_fwd_pair_launch(const FaFwdArgs& a, cudaStream_t stream) {
 
   CUtensorMap tq, tk, tv;
   int rc;
+  if ((rc = check_prior_status("fa_fwd"))) return rc;
   if ((rc = bind_device_of(a.q, "fa_fwd"))) return rc;
   if ((rc = make_tmap_3d(&tq, a.q, Cfg::BF16, Cfg::DQK, a.Lq, a.BH, 64, Cfg::BM))) return rc;
   if ((rc = make_tmap_3d(&tk, a.k, Cfg::BF16, Cfg::DQK, a.Lkv, a.BH, 64, Cfg::BN / 2))) return rc;  // half of the keys

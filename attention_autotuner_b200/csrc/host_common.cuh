@@ -10,6 +10,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "ptx.cuh"
 
 namespace ab200 {
@@ -71,24 +73,93 @@ inline int check_launch(const char* what) {
   return kOk;
 }
 
+// Host-visible mirror of the device status words of THIS library on the calling thread's current device: four ints in
+// mapped pinned host memory ([0] status, [1] detail, [2] numeric flag) that report_timeout() / report_saturation() write
+// next to the device-side words.
+// Created on the first call per device (a few bytes of pinned host memory that live until the process exits; one
+// synchronous copy of the pointer into the device symbol). Returns nullptr, with the error text set, if that fails.
+// Internal linkage on purpose: the table pairs with THIS library's g_status_mirror symbol, and the local statics of an
+// inline function would be shared by every library of the process that contains the same function.
+static volatile int* status_mirror() {
+  constexpr int kMaxDevices = 64;
+  static volatile int* table[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    fail(kErrCuda, "status mirror: no usable current device");
+    return nullptr;
+  }
+  if (table[dev] != nullptr) return table[dev];
+  std::lock_guard<std::mutex> lock(mu);
+  if (table[dev] != nullptr) return table[dev];
+  int* host = nullptr;
+  int* devptr = nullptr;
+  cudaError_t e = cudaHostAlloc(reinterpret_cast<void**>(&host), 4 * sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable);
+  if (e == cudaSuccess) {
+    host[0] = host[1] = host[2] = host[3] = 0;
+    e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&devptr), host, 0);
+  }
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_status_mirror, &devptr, sizeof(devptr));
+  if (e != cudaSuccess) {
+    fail(kErrCuda, "status mirror set-up: %s", cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  table[dev] = host;
+  return host;
+}
+
+// Called by every launcher before it launches: refuses to run while the sticky status word of an earlier kernel is
+// still set (every bounded wait would give up at once and the outputs would be garbage). No synchronisation: the
+// word is read from the host-mapped mirror.
+static int check_prior_status(const char* what) {
+  volatile int* m = status_mirror();
+  if (m == nullptr) return kErrCuda;
+  if (m[0] != 0) {
+    const int det = m[1];
+    return fail(kErrDevice,
+                "%s: an earlier kernel of this library gave up on a bounded wait (status %d, tag %d, block %d); results "
+                "since then are invalid. Read and clear the status (device_status(1)) before launching again",
+                what, m[0], det >> 16, det & 0xffff);
+  }
+  if (m[2] != 0)
+    return fail(kErrDevice,
+                "%s: an earlier RetNet forward of this library clamped unnormalised scores to the fp16 range (status 2); its "
+                "output is not trustworthy. Use bf16 or smaller inputs; read and clear the status (device_status(1)) before "
+                "launching again", what);
+  return kOk;
+}
+
 // Synchronises the device and returns the sticky device status word (0 = ok); clears it when asked.
 inline int read_device_status(int clear, int* detail) {
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail(kErrCuda, "cudaDeviceSynchronize: %s", cudaGetErrorString(e)), -1;
-  int st = 0, det = 0;
+  int st = 0, det = 0, num = 0;
   if (cudaMemcpyFromSymbol(&st, g_device_status, sizeof(int)) != cudaSuccess ||
-      cudaMemcpyFromSymbol(&det, g_device_status_detail, sizeof(int)) != cudaSuccess) {
+      cudaMemcpyFromSymbol(&det, g_device_status_detail, sizeof(int)) != cudaSuccess ||
+      cudaMemcpyFromSymbol(&num, g_numeric_status, sizeof(int)) != cudaSuccess) {
     fail(kErrCuda, "cudaMemcpyFromSymbol(device status): %s", cudaGetErrorString(cudaGetLastError()));
     return -1;
   }
   if (detail) *detail = det;
-  if (clear && st != 0) {
+  if (clear && (st != 0 || num != 0)) {
     int zero = 0;
     cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
     cudaMemcpyToSymbol(g_device_status_detail, &zero, sizeof(int));
+    cudaMemcpyToSymbol(g_numeric_status, &zero, sizeof(int));
+    volatile int* m = status_mirror();
+    if (m != nullptr) m[0] = m[1] = m[2] = 0;
   }
-  if (st != 0) fail(kErrDevice, "device status %d (tag %d, block %d)", st, det >> 16, det & 0xffff);
-  return st;
+  if (st != 0) {
+    fail(kErrDevice, "device status %d (tag %d, block %d)", st, det >> 16, det & 0xffff);
+    return st;
+  }
+  if (num != 0) {
+    fail(kErrDevice, "device status %d: a RetNet forward clamped unnormalised scores to the fp16 range (|q k^T * scale * mask| "
+                     "above 65504); its output is not trustworthy. Use bf16 or smaller inputs", (int)kStatusSaturated);
+    return kStatusSaturated;
+  }
+  return 0;
 }
 
 // The tensor maps are encoded through the driver API, which needs a context current on the calling

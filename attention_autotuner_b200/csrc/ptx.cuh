@@ -21,10 +21,19 @@ namespace ab200 {
 enum DeviceStatus : int {
   kStatusOk = 0,
   kStatusWaitTimeout = 1,  // a bounded mbarrier wait expired
+  kStatusSaturated = 2,    // a 16-bit intermediate hit the largest finite fp16 value: the result is not trustworthy
 };
 
 __device__ int g_device_status = 0;
 __device__ int g_device_status_detail = 0;  // (barrier tag << 16) | blockIdx.x, first failure only
+// Numeric flag, kept apart from g_device_status so that it never makes a wait give up: set when the RetNet forward had to
+// clamp an unnormalised score to the fp16 range (see chain_common.cuh). Reported by the host as status 2.
+__device__ int g_numeric_status = 0;
+// Host-visible copy of the words above: mapped pinned host memory, set up once per device by the host side
+// (status_mirror() in host_common.cuh). [0] = status, [1] = detail, [2] = numeric flag. The launchers read it without a
+// synchronisation before every launch, so a kernel that gave up is noticed by the next call instead of silently
+// poisoning everything after it. nullptr until the first launch on the device.
+__device__ volatile int* g_status_mirror = nullptr;
 
 #ifndef AB200_WAIT_LIMIT_NS
 #define AB200_WAIT_LIMIT_NS 1000000000ull  // 1 s per wait
@@ -95,8 +104,29 @@ struct CtaAbort {
 __device__ __noinline__ void report_timeout(CtaAbort* ab, int tag) {
   ab->flag = 1;
   if (atomicCAS(&g_device_status, kStatusOk, kStatusWaitTimeout) == kStatusOk) {
-    g_device_status_detail = (tag << 16) | (blockIdx.x & 0xffff);
+    const int detail = (tag << 16) | (blockIdx.x & 0xffff);
+    g_device_status_detail = detail;
+    volatile int* mirror = g_status_mirror;
+    if (mirror != nullptr) {
+      mirror[1] = detail;
+      __threadfence_system();
+      mirror[0] = kStatusWaitTimeout;
+    }
   }
+}
+
+__device__ __noinline__ void report_saturation() {
+  if (atomicExch(&g_numeric_status, 1) == 0) {
+    volatile int* mirror = g_status_mirror;
+    if (mirror != nullptr) mirror[2] = 1;
+  }
+}
+
+// True when one of the two fp16 halves of `packed` is the largest finite magnitude (0x7bff), which is what
+// cvt.rn.satfinite produces for every input beyond the fp16 range.
+__device__ __forceinline__ bool half2_has_maxnorm(uint32_t packed) {
+  const uint32_t m = packed & 0x7fff7fffu;
+  return (m & 0xffffu) == 0x7bffu || (m >> 16) == 0x7bffu;
 }
 
 // Once any CTA of any launch has reported a failure the status word stays non-zero until the host clears
@@ -104,7 +134,8 @@ __device__ __noinline__ void report_timeout(CtaAbort* ab, int tag) {
 // than one per CTA.
 // Bounded wait for one thread (the single-thread producer / MMA roles). Returns false on expiry or
 // when another role of the CTA already aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, CtaAbort* ab, int tag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, CtaAbort* ab, int tag,
+                                          uint64_t limit_ns = AB200_WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
@@ -113,7 +144,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, CtaAbo
       if (ab->flag || *reinterpret_cast<volatile int*>(&g_device_status) != 0) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > AB200_WAIT_LIMIT_NS) {
+      if (now - t0 > limit_ns) {
         report_timeout(ab, tag);
         return false;
       }
@@ -132,7 +163,8 @@ __device__ __forceinline__ void mbar_wait_drain(uint64_t* bar, uint32_t parity, 
 
 // Bounded wait for a whole, converged warp. The result is warp-uniform, so the callers can keep
 // issuing .sync.aligned tcgen05 instructions afterwards without divergence.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, CtaAbort* ab, int tag) {
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, CtaAbort* ab, int tag,
+                                               uint64_t limit_ns = AB200_WAIT_LIMIT_NS) {
   uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {
     bool ok = mbar_try_wait(bar, parity);
@@ -145,7 +177,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, C
         } else {
           uint64_t now = globaltimer_ns();
           if (t0 == 0) t0 = now;
-          if (now - t0 > AB200_WAIT_LIMIT_NS) {
+          if (now - t0 > limit_ns) {
             report_timeout(ab, tag);
             give_up = 1;
           }

@@ -181,4 +181,32 @@ inline int selftest_gemm_ts(const void* p, const void* v, float* d, int N, int b
   return check_launch("selftest_gemm_ts");
 }
 
+// The bounded wait in miniature: one warp waits on an mbarrier that nobody ever arrives at, with a wait limit of
+// limit_ns instead of the kernels' one second. The wait runs out, report_timeout() sets the status words and the kernel
+// returns normally: no TMA, no tensor memory, no cluster, nothing in flight. whole_warp selects mbar_wait_warp
+// (the converged-warp form the MMA and softmax roles use) or mbar_wait (the single-thread form of the producers).
+constexpr int kTagSelftestWait = 99;
+__global__ void __launch_bounds__(32, 1) selftest_wait_kernel(unsigned long long limit_ns, int whole_warp) {
+  __shared__ uint64_t bar;
+  __shared__ CtaAbort ab;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    ab.flag = 0;
+    fence_mbar_init();
+  }
+  __syncwarp();
+  if (whole_warp) {
+    (void)mbar_wait_warp(&bar, 0, &ab, kTagSelftestWait, limit_ns);
+  } else if (threadIdx.x == 0) {
+    (void)mbar_wait(&bar, 0, &ab, kTagSelftestWait, limit_ns);
+  }
+}
+
+inline int selftest_wait(int limit_us, int whole_warp, cudaStream_t stream) {
+  if (limit_us <= 0 || limit_us > 100000) return fail(kErrInvalidArgument, "selftest_wait: limit_us must be in [1, 100000]");
+  if (int prior = check_prior_status("selftest_wait")) return prior;
+  selftest_wait_kernel<<<1, 32, 0, stream>>>(static_cast<unsigned long long>(limit_us) * 1000ull, whole_warp ? 1 : 0);
+  return check_launch("selftest_wait");
+}
+
 }  // namespace ab200

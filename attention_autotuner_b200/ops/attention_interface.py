@@ -14,6 +14,7 @@ import ctypes
 import torch
 
 from .. import _lib
+from ._checks import check_like, check_qkv
 from ..arch import Arch
 from ..autotuner.runtime import Runtime
 from ..autotuner.tunner import AttnTunner
@@ -23,12 +24,10 @@ class MultiHeadAttnFunc(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, device_type: Arch, causal=False, softmax_scale=None, return_lse=False):
+        check_qkv("flash_attn_func", q, k, v)
         q, k, v = [x.contiguous() for x in [q, k, v]]
         batch_size, nheads, seqlen_q, key_dim = q.shape
         head_dim = v.shape[-1]
-        assert q.dtype in (torch.float16, torch.bfloat16) and k.dtype == q.dtype and v.dtype == q.dtype
-        assert head_dim % 64 == 0 and head_dim <= 512
-        assert key_dim % 64 == 0 and key_dim <= 256
 
         o = torch.empty(batch_size, nheads, seqlen_q, head_dim, device=q.device, dtype=q.dtype)
         needs_grad = any(ctx.needs_input_grad[:3])
@@ -59,6 +58,7 @@ class MultiHeadAttnFunc(torch.autograd.Function):
                                       f"(got {d}, {k.shape[3]}, {v.shape[3]})")
         if ctx.causal and Lq != Lkv:
             raise NotImplementedError("causal attention backward needs Lq == Lkv")
+        check_like("flash_attn_func backward", "dO", do, o.shape, o.dtype, o.device)
         do = do.contiguous()
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         P = lambda t: ctypes.c_void_p(t.data_ptr())

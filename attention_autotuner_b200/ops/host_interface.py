@@ -75,10 +75,37 @@ def _host_like(shape, dtype):
     return torch.empty(shape, dtype=dtype).pin_memory()
 
 
-def flash_attn_host(q, k, v, device_type, causal=False, softmax_scale=None, *, out=None, device=None, chunks=None):
+def _finish(s_out, cur, wait):
+    """The results are written by asynchronous device -> host copies on s_out. With wait=True (the default) the
+    calling thread blocks until the last of them has landed, so the returned host tensors can be read at once.
+    With wait=False the event that marks the last copy is returned instead and the caller must synchronise on
+    it (or on the device) before touching the results."""
+    done = s_out.record_event()
+    cur.wait_stream(s_out)
+    if wait:
+        done.synchronize()
+        return None
+    return done
+
+
+def _check_host_shapes(op, q, k, v):
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError(f"{op}: q, k, v must be 4-d [batch, heads, length, head_dim]")
+    if tuple(k.shape[:2]) != tuple(q.shape[:2]) or tuple(v.shape[:2]) != tuple(q.shape[:2]):
+        raise ValueError(f"{op}: k / v batch and heads {tuple(k.shape[:2])} / {tuple(v.shape[:2])} differ from q's "
+                         f"{tuple(q.shape[:2])}")
+    if k.shape[3] != q.shape[3] or v.shape[2] != k.shape[2] or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError(f"{op}: inconsistent shapes or dtypes: q {tuple(q.shape)} {q.dtype}, k {tuple(k.shape)} {k.dtype}, "
+                         f"v {tuple(v.shape)} {v.dtype}")
+
+
+def flash_attn_host(q, k, v, device_type, causal=False, softmax_scale=None, *, out=None, device=None, chunks=None,
+                    wait=True):
     """q [B,H,Lq,dqk], k [B,H,Lkv,dqk], v [B,H,Lkv,dv] on the host; returns o [B,H,Lq,dv] on the host (``out`` if
     given). ``softmax_scale=None`` keeps the reference's 0.125. ``chunks``: number of pieces the [batch, heads]
-    grid is cut into (default: one per batch entry)."""
+    grid is cut into (default: one per batch entry). The call returns once ``o`` is complete; with ``wait=False``
+    it returns ``(o, event)`` without blocking and ``o`` may only be read after ``event.synchronize()``."""
+    _check_host_shapes("flash_attn_host", q, k, v)
     _check_host(q, k, v, out)
     dev = _device(device)
     B = q.shape[0]
@@ -102,15 +129,18 @@ def flash_attn_host(q, k, v, device_type, causal=False, softmax_scale=None, *, o
             s_out.wait_event(ev_op)
             out[b0:b1, h0:h1].copy_(od, non_blocking=True)
             od.record_stream(s_out)
-    cur.wait_stream(s_out)
-    return out
+    done = _finish(s_out, cur, wait)
+    return out if wait else (out, done)
 
 
 def retnet_host(q, k, v, device_type, *, mask=None, decay=None, causal=False, scale=None, dout=None, outs=None,
-                device=None, chunks=None):
+                device=None, chunks=None, wait=True):
     """RetNet parallel forward (``dout=None``; returns o) or forward + backward (returns o, dq, dk, dv) on host
     tensors. ``mask`` [H,Lq,Lkv] (host or device; uploaded once) or ``decay`` (H gammas), as RetNetAttnFunc.
-    ``outs``: optional host tensors to receive the results, in the order they are returned."""
+    ``outs``: optional host tensors to receive the results, in the order they are returned. The call returns once
+    the results are complete; with ``wait=False`` it returns ``(results, event)`` without blocking and the results
+    may only be read after ``event.synchronize()``."""
+    _check_host_shapes("retnet_host", q, k, v)
     _check_host(q, k, v, dout)
     dev = _device(device)
     B = q.shape[0]
@@ -147,5 +177,6 @@ def retnet_host(q, k, v, device_type, *, mask=None, decay=None, causal=False, sc
             for dst, src in zip(outs, res):
                 dst[b0:b1, h0:h1].copy_(src, non_blocking=True)
                 src.record_stream(s_out)
-    cur.wait_stream(s_out)
-    return tuple(outs) if backward else outs[0]
+    done = _finish(s_out, cur, wait)
+    res_host = tuple(outs) if backward else outs[0]
+    return res_host if wait else (res_host, done)

@@ -11,6 +11,7 @@ tensor, ``causal=True`` declares it lower triangular so the kernels skip the blo
 import torch
 
 from ..arch import Arch
+from ._checks import check_like, check_mask_decay, check_qkv
 from ..autotuner.runtime import Runtime
 from ..autotuner.tunner import RetBwdTunner, RetTunner
 
@@ -18,21 +19,17 @@ from ..autotuner.tunner import RetBwdTunner, RetTunner
 def retnet_forward(q, k, v, mask, device_type: Arch, causal=False, scale=None, decay=None):
     """The forward launch without autograd: returns (o, r, mask, decay) with mask / decay as the kernels took them
     (contiguous, decay as fp32 on the device). r = max(sum_j |S~|, 1) per row is what the backward needs."""
-    assert q.dtype in (torch.float16, torch.bfloat16) and k.dtype == q.dtype and v.dtype == q.dtype
-    assert (mask is None) != (decay is None), "give either a mask tensor or per-head decay"
+    check_qkv("RetNetAttnFunc", q, k, v)
+    check_mask_decay("RetNetAttnFunc", q, k, mask, decay)
     q, k, v = [x.contiguous() for x in [q, k, v]]
     batch_size, nheads, seqlen_q, key_dim = q.shape
     head_dim = v.shape[-1]
-    assert head_dim % 64 == 0 and head_dim <= 512
-    assert key_dim % 64 == 0 and key_dim <= 256
     maskr = None
     if mask is not None:
-        assert mask.dtype == q.dtype
         maskr = mask.detach().contiguous()
     decayr = None
     if decay is not None:
-        decayr = decay.detach().to(device=q.device, dtype=torch.float32).contiguous()
-        assert decayr.numel() == nheads
+        decayr = decay.detach().to(device=q.device, dtype=torch.float32).contiguous().reshape(-1)
     o = torch.empty(batch_size, nheads, seqlen_q, head_dim, device=q.device, dtype=q.dtype)
     r = torch.empty(batch_size, nheads, seqlen_q, device=q.device, dtype=torch.float32)
     arr = [q, k, v, maskr, o, r]
@@ -44,6 +41,10 @@ def retnet_forward(q, k, v, mask, device_type: Arch, causal=False, scale=None, d
 def retnet_backward(q, k, v, mask, do, r, device_type: Arch, causal=False, scale=None, decay=None):
     """The backward launches without autograd: (dq, dk, dv) from the tensors of retnet_forward. r is a constant
     (python/utils/ref_op.py:11 detaches it)."""
+    check_qkv("RetNetAttnFunc backward", q, k, v)
+    check_mask_decay("RetNetAttnFunc backward", q, k, mask, decay)
+    check_like("RetNetAttnFunc backward", "dO", do, (*q.shape[:3], v.shape[3]), q.dtype, q.device)
+    check_like("RetNetAttnFunc backward", "r", r, q.shape[:3], torch.float32, q.device)
     do = do.contiguous()
     dq = torch.empty_like(q)
     dk = torch.empty_like(k)

@@ -2,7 +2,11 @@
  * C ABI of libattn_b200.so: fused attention / RetNet kernels for NVIDIA B200 (sm_100a).
  *
  * Plain pointers and sizes only; every tensor pointer is a DEVICE pointer owned by the caller, dense and
- * row-major in the layouts given below, 16-byte aligned. The library allocates no device memory.
+ * row-major in the layouts given below. Alignment: inputs of the forward entry points (q, k, v, mask) 16 bytes,
+ * every 16-bit OUTPUT tensor (o, dq, dk, dv) 32 bytes (they are written with 256-bit stores), and all eight 16-bit
+ * tensors of attn_b200_fa_bwd 32 bytes; fp32 vectors (lse, r, decay) 4 bytes. A misaligned pointer is rejected with
+ * ATTN_B200_ERR_INVALID_ARGUMENT. The library allocates no device memory (on its first launch per device it pins two
+ * ints of host memory for the status word described at attn_b200_device_status).
  * Kernels are launched asynchronously on `stream` (a cudaStream_t passed as void*, NULL = default
  * stream). Every function returns 0 on success and one of ATTN_B200_ERR_* otherwise; the text of the
  * last error of the calling thread is available from attn_b200_last_error().
@@ -12,8 +16,9 @@
  *     int   kernel_entry(ptrs..., int B, int H, int Seq_k, int Seq_q);
  *     float profile     (ptrs..., int B, int H, int Seq_q, int Seq_k);
  * The per-configuration libraries built by attention_autotuner_b200.autotuner keep exactly those two
- * symbols (second half of this header). libattn_b200.so itself exports the general entry points
- * below, which take the head dimensions, dtype, scale and stream explicitly.
+ * symbols; their signatures, which differ per operation, are given as function-pointer types in the second
+ * half of this header. libattn_b200.so itself exports the general entry points below, which take the head
+ * dimensions, dtype, scale and stream explicitly.
  */
 #ifndef ATTN_B200_H_
 #define ATTN_B200_H_
@@ -35,7 +40,10 @@ extern "C" {
 const char* attn_b200_last_error(void);
 
 /* Synchronises the current device and returns the sticky device status word written by the kernels
- * (0 = ok, 1 = a bounded barrier wait expired). `clear` != 0 resets it. Returns -1 if the read failed. */
+ * (0 = ok, 1 = a bounded barrier wait expired). `clear` != 0 resets it. Returns -1 if the read failed.
+ * While the word is set, every launching entry point returns ATTN_B200_ERR_DEVICE without launching (it reads a
+ * host-mapped copy of the word, no synchronisation), so a kernel that gave up cannot silently poison later results:
+ * read and clear the status, then launch again. */
 int attn_b200_device_status(int clear);
 
 /* ABI version of this header (bumped on incompatible changes). */
@@ -133,6 +141,63 @@ int attn_b200_selftest_gemm_ts(const void* p, const void* v, float* d, int N, in
  */
 int attn_b200_selftest_pair(const void* a, const void* b, const void* t, float* z, float* d, int K, int N2, int dtype,
                             void* stream);
+
+/*
+ * The bounded wait in miniature: launches one warp that waits on a barrier nobody arrives at, with a limit of
+ * limit_us microseconds (1..100000) instead of the kernels' one second. The wait runs out, the kernel sets the status
+ * word and returns normally (no copy, no tensor memory, nothing in flight). Afterwards attn_b200_device_status(0)
+ * returns 1 with tag 99 in attn_b200_last_error(), and every launching entry point refuses with ATTN_B200_ERR_DEVICE
+ * until the status is cleared. whole_warp != 0 exercises the converged-warp form of the wait, 0 the single-thread
+ * form. No counterpart in the reference (its kernels have no bounded waits).
+ */
+int attn_b200_selftest_wait(int limit_us, int whole_warp, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Second half: symbols of the per-configuration libraries (one tile configuration of one operation each, built by
+ * attention_autotuner_b200.autotuner.Runtime.compile from csrc/kernels/<operation>/profile_code.py). Every such library
+ * exports the same six names; the argument lists depend on the operation, so they are given as function-pointer
+ * types for dlsym / ctypes users. The two legacy symbols have exactly the reference's argument orders (fp16, the
+ * reference's constants, default stream; note Seq_k before Seq_q in kernel_entry and Seq_q before Seq_k in profile);
+ * the _ex forms add what the reference hard-codes. dtype and head dimensions are fixed per library.
+ *     kernel_entry, kernel_entry_ex : return ATTN_B200_OK or an ATTN_B200_ERR_* code
+ *     profile, profile_ex           : return ms per launch, -1 on error
+ *     const char* last_error(void); int device_status(int clear);    as attn_b200_last_error / attn_b200_device_status
+ * ------------------------------------------------------------------------------------------------------------------ */
+
+/* operation "attn" (reference: csrc/kernels/attention/regfuse/profile_code.py:30 profile, :68 kernel_entry) */
+typedef int (*attn_b200_attn_kernel_entry_t)(void* q, void* k, void* v, void* o, int B, int H, int Seq_k, int Seq_q);
+typedef float (*attn_b200_attn_profile_t)(void* q, void* k, void* v, void* o, int B, int H, int Seq_q, int Seq_k);
+typedef int (*attn_b200_attn_kernel_entry_ex_t)(const void* q, const void* k, const void* v, void* o, float* lse, int B,
+                                                int H, int Seq_k, int Seq_q, float scale, int causal, void* stream);
+typedef float (*attn_b200_attn_profile_ex_t)(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H,
+                                             int Seq_q, int Seq_k, float scale, int causal, void* stream);
+
+/* operation "ret" (reference: csrc/kernels/retnet/regfuse/profile_code.py:30 profile, :72 kernel_entry) */
+typedef int (*attn_b200_ret_kernel_entry_t)(void* q, void* k, void* v, void* mask, void* o, float* r, int B, int H, int Seq_k,
+                                            int Seq_q);
+typedef float (*attn_b200_ret_profile_t)(void* q, void* k, void* v, void* mask, void* o, float* r, int B, int H, int Seq_q,
+                                         int Seq_k);
+typedef int (*attn_b200_ret_kernel_entry_ex_t)(const void* q, const void* k, const void* v, const void* mask, void* o,
+                                               float* r, int B, int H, int Seq_k, int Seq_q, float scale,
+                                               const float* decay, int causal, void* stream);
+typedef float (*attn_b200_ret_profile_ex_t)(const void* q, const void* k, const void* v, const void* mask, void* o, float* r,
+                                            int B, int H, int Seq_q, int Seq_k, float scale, const float* decay, int causal,
+                                            void* stream);
+
+/* operation "ret_bwd" (reference: csrc/kernels/retnet/bwd/profile_code.py:50 profile, :98 kernel_entry); dqaccum is
+ * accepted and ignored, may be NULL */
+typedef int (*attn_b200_ret_bwd_kernel_entry_t)(void* q, void* k, void* v, void* mask, void* dout, float* r, void* dq,
+                                                void* dk, void* dv, float* dqaccum, int B, int H, int Seq_k, int Seq_q);
+typedef float (*attn_b200_ret_bwd_profile_t)(void* q, void* k, void* v, void* mask, void* dout, float* r, void* dq, void* dk,
+                                             void* dv, float* dqaccum, int B, int H, int Seq_q, int Seq_k);
+typedef int (*attn_b200_ret_bwd_kernel_entry_ex_t)(const void* q, const void* k, const void* v, const void* mask,
+                                                   const void* dout, const float* r, void* dq, void* dk, void* dv,
+                                                   float* dqaccum, int B, int H, int Seq_k, int Seq_q, float scale,
+                                                   const float* decay, int causal, void* stream);
+typedef float (*attn_b200_ret_bwd_profile_ex_t)(const void* q, const void* k, const void* v, const void* mask,
+                                                const void* dout, const float* r, void* dq, void* dk, void* dv,
+                                                float* dqaccum, int B, int H, int Seq_q, int Seq_k, float scale,
+                                                const float* decay, int causal, void* stream);
 
 #ifdef __cplusplus
 }

@@ -15,6 +15,7 @@ as arguments whose defaults reproduce the reference.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -178,7 +179,7 @@ def flops_ret_bwd(B, H, Lq, Lkv, dqk, dv, causal=False) -> int:
 # Tolerances (absolute, against this fp32 oracle)
 # ------------------------------------------------------------------------------------------------
 TOL = {
-    # fp16 outputs: BASELINE north_star's bound
+    # fp16 outputs
     "fp16": dict(max_abs=2e-3, mean_abs=2e-4),
     # bf16 has 3 fewer mantissa bits: 8x
     "bf16": dict(max_abs=1.6e-2, mean_abs=1.6e-3),
@@ -190,6 +191,24 @@ def error_stats(x: torch.Tensor, ref: torch.Tensor) -> dict:
     denom = ref.abs().max().clamp(min=1e-30)
     return dict(max_abs=d.max().item(), mean_abs=d.mean().item(), max_rel_to_peak=(d.max() / denom).item(),
                 ref_peak=denom.item())
+
+
+def report(name: str, stats: dict, dtype_name: str = "fp16", scale_by_peak: bool = False) -> bool:
+    """Prints one line with the error figures of a compared tensor (max-abs, mean-abs, max-abs relative to the
+    reference's peak, the peak, and which bound gates it), appends the record to the JSON-lines file named by the
+    environment variable ATTN_B200_PARITY_LOG when it is set, and returns within(...)."""
+    ok = within(stats, dtype_name, scale_by_peak)
+    gate = "peak-scaled" if (scale_by_peak and stats["ref_peak"] > 1.0) else "absolute"
+    t = TOL[dtype_name]
+    print(f"[parity] {name}: max_abs={stats['max_abs']:.3e} mean_abs={stats['mean_abs']:.3e} "
+          f"max_rel_to_peak={stats['max_rel_to_peak']:.3e} ref_peak={stats['ref_peak']:.3e} "
+          f"bound={gate} ({t['max_abs']:.1e}/{t['mean_abs']:.1e} {dtype_name}) {'ok' if ok else 'FAIL'}")
+    path = os.environ.get("ATTN_B200_PARITY_LOG")
+    if path:
+        import json
+        with open(path, "a") as f:
+            f.write(json.dumps(dict(name=name, dtype=dtype_name, gate=gate, ok=ok, **stats)) + "\n")
+    return ok
 
 
 def within(stats: dict, dtype_name: str, scale_by_peak: bool = False) -> bool:

@@ -172,6 +172,35 @@ def test_config2_full_size_properties(lib):
     assert _lib.device_status() == 0
 
 
+@pytest.mark.parametrize("dtype_name,causal,nbatch", [("fp16", False, 8), ("fp16", True, 8), ("bf16", False, 1), ("bf16", True, 1)])
+def test_config2_every_slice_against_the_oracle(lib, dtype_name, causal, nbatch):
+    """B=8 H=16 L=4096 d=128 with the per-slice seeded inputs: fp16 checks all 128 (batch, head) slices, bf16 the 16
+    heads of the first batch entry, each slice over all rows against the fp32 oracle. Prints the error figures."""
+    c = oracle.CONFIGS["C2"]
+    B, H, L, d = c["B"], c["H"], c["Lq"], c["dqk"]
+    dt, code = DT[dtype_name]
+    scale = d ** -0.5
+    q, k, v = (torch.empty(B, H, L, d, dtype=dt) for _ in range(3))
+    for b in range(B):
+        for h in range(H):
+            q[b, h], k[b, h], v[b, h] = oracle.slice_inputs("C2", b, h, H, L, L, d, d, dt)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    o = torch.full((B, H, L, d), float("nan"), device="cuda", dtype=dt)
+    _lib.check(lib.attn_b200_fa_fwd(P(qd), P(kd), P(vd), P(o), None, B, H, L, L, d, d, code, scale, int(causal), None))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    oc = o.cpu()
+    worst = dict(max_abs=0.0, mean_abs=0.0, max_rel_to_peak=0.0, ref_peak=0.0)
+    for b in range(nbatch):
+        oref, _ = oracle.attention_fwd(q[b], k[b], v[b], scale, causal)     # the 16 heads of one batch entry at once
+        for h in range(H):
+            st = oracle.error_stats(oc[b, h], oref[h])
+            assert oracle.within(st, dtype_name), (b, h, st)
+            worst = {key: max(worst[key], st[key]) for key in worst}
+    assert oracle.report(f"C2 {dtype_name}{' causal' if causal else ''} worst of {nbatch * H} slices", worst, dtype_name)
+    assert not torch.isnan(oc).any()
+
+
 def test_python_operator_matches_capi(lib):
     from attention_autotuner_b200.ops.attention_interface import flash_attn_func
     q, k, v = rand_qkv(19, 2, 2, 512, 768, 128, 128, torch.float16)
@@ -181,8 +210,10 @@ def test_python_operator_matches_capi(lib):
     assert torch.equal(o.cpu(), oc)
     o2, lse = flash_attn_func(qd, kd, vd, B200(), True, 0.07, True)
     check(o2.cpu(), lse.cpu(), q, k, v, 0.07, True, "fp16")
-    with pytest.raises(AssertionError):
-        flash_attn_func(qd[..., :96], kd[..., :96], vd, B200())   # key_dim % 64 != 0, as the reference asserts
+    with pytest.raises(ValueError):
+        flash_attn_func(qd[..., :96], kd[..., :96], vd, B200())   # key_dim % 64 != 0 (the reference asserts the same)
+    with pytest.raises(ValueError, match="batch/heads"):
+        flash_attn_func(qd, kd[:, :1], vd[:, :1], B200())          # fewer k/v heads: rejected, not read out of bounds
 
 
 def test_legacy_kernel_entry_symbol():

@@ -206,3 +206,119 @@ def test_cta_pair_knob_in_configs_and_search_space():
         ", true>" in _create_entry_code(RetBwdConfig(128, 128, 256, 512))
     # a decay mask is lower triangular whatever `causal` says: one cache entry
     assert RetTunner(B200(), [z, z, zv, None, zv, None], causal=True, decay=torch.ones(1))._cache_file() == rt._cache_file()
+
+
+def test_committed_cache_files_load_on_any_checkout(tmp_path):
+    """Every committed best-config file must be usable wherever the package is installed: no absolute path inside,
+    the launch-shim source renders from it, and Runtime gets as far as the nvcc command line in an empty directory.
+    (The reference stores template_dir in the file, python/autotuner/base_tunner.py:197-208.)"""
+    import glob
+    from attention_autotuner_b200.autotuner import runtime as rtm
+    cache_dir = os.path.join(ROOT, "attention_autotuner_b200", "cache")
+    files = sorted(glob.glob(os.path.join(cache_dir, "*.json")))
+    assert len(files) >= 5
+    for path in files:
+        with open(path) as f:
+            d = json.load(f)
+        for key, val in d.items():
+            assert not (isinstance(val, str) and (val.startswith("/") or ":\\" in val)), (path, key, val)
+        assert "template_dir" not in d
+        cfg = supported_configs[d["operation"]].from_dict(d)
+        assert os.path.isfile(os.path.join(cfg.template_dir, "profile_code.py"))
+        assert cfg.template_dir.startswith(os.path.join(ROOT, "attention_autotuner_b200", "csrc"))
+        src = rtm._create_entry_code(cfg)
+        assert 'extern "C" int kernel_entry(' in src and 'extern "C" float profile(' in src
+        rt = Runtime(B200(), cfg, tmp_dir=str(tmp_path), libname="pending")  # "pending": do not compile in the constructor
+        cmd = nvcc_command(B200(), os.path.join(rt.tmp_dir, str(cfg) + ".cu"), os.path.join(rt.tmp_dir, str(cfg) + ".so"))
+        assert cmd[0].endswith("nvcc") and any(a.startswith("-I") and a.endswith("csrc") for a in cmd)
+        assert "template_dir" not in cfg.to_dict() and json.dumps(cfg.to_dict())
+    # a path smuggled into a cache file never decides which template is executed
+    poisoned = dict(d, template_dir="/nonexistent/elsewhere")
+    cfg = supported_configs[d["operation"]].from_dict(poisoned)
+    assert "/nonexistent" not in cfg.template_dir and rtm._create_entry_code(cfg)
+
+
+def test_tuner_cache_writer_stores_no_path(tmp_path, monkeypatch):
+    monkeypatch.setenv("ATTN_B200_CACHE_DIR", str(tmp_path))
+    cfg = AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=5)
+    assert "template_dir" not in cfg.to_dict() and "template_dir" not in cfg.__dict__
+    assert cfg.template_dir.endswith(os.path.join("csrc", "kernels", "attention"))
+
+
+def test_library_staleness_is_decided_by_a_source_hash(tmp_path, monkeypatch):
+    from attention_autotuner_b200 import build
+    fake = tmp_path / "libattn_b200.so"
+    monkeypatch.setattr(build, "LIB_PATH", str(fake))
+    assert build.is_stale()                       # no library
+    fake.write_bytes(b"x")
+    assert build.is_stale()                       # library without a stamp
+    (tmp_path / "libattn_b200.so.srchash").write_text(build.source_hash() + "\n")
+    assert not build.is_stale()
+    os.utime(fake, (1, 1))                        # file times do not matter (a fresh checkout has arbitrary ones)
+    assert not build.is_stale()
+    (tmp_path / "libattn_b200.so.srchash").write_text("0" * 40 + "\n")
+    assert build.is_stale()                       # built from other sources
+
+
+def test_operator_argument_checks_raise_before_any_launch():
+    """Mismatched tensors must raise ValueError instead of reaching a kernel that indexes raw pointers."""
+    from attention_autotuner_b200.ops import _checks
+    from attention_autotuner_b200.ops.attention_interface import flash_attn_func
+    from attention_autotuner_b200.ops.retnet_interface import RetNetAttnFunc
+    h = torch.float16
+    q = torch.zeros(2, 4, 128, 128, dtype=h)
+    k = torch.zeros(2, 4, 256, 128, dtype=h)
+    v = torch.zeros(2, 4, 256, 128, dtype=h)
+    bad = [
+        (q, k[:, :2], v, "batch/heads"),                          # fewer k heads (grouped-query layout)
+        (q, k, v[:, :2], "batch/heads"),
+        (q, k[..., :64], v, "head dimension"),                    # k head dim differs from q
+        (q, k, v[:, :, :128], "keys"),                            # v shorter than k
+        (q, k.to(torch.bfloat16), v, "dtype"),
+        (q.float(), k.float(), v.float(), "float16 or bfloat16"),
+        (q[0], k[0], v[0], "4-d"),
+        (q[..., :96], k[..., :96], v, "CUDA device" if not torch.cuda.is_available() else "multiple of 64"),
+    ]
+    for qq, kk, vv, msg in bad:
+        with pytest.raises(ValueError, match=msg):
+            flash_attn_func(qq, kk, vv, B200())
+        with pytest.raises(ValueError, match=msg):
+            RetNetAttnFunc(qq, kk, vv, None, B200(), decay=torch.ones(4))
+    if not torch.cuda.is_available():
+        with pytest.raises(ValueError, match="CUDA device"):
+            flash_attn_func(q, k, v, B200())
+    # mask / decay forms
+    with pytest.raises(ValueError, match="either a mask"):
+        _checks.check_mask_decay("op", q, k, None, None)
+    with pytest.raises(ValueError, match="either a mask"):
+        _checks.check_mask_decay("op", q, k, torch.zeros(4, 128, 256, dtype=h), torch.ones(4))
+    with pytest.raises(ValueError, match="mask has shape"):
+        _checks.check_mask_decay("op", q, k, torch.zeros(4, 128, 128, dtype=h), None)
+    with pytest.raises(ValueError, match="mask has dtype"):
+        _checks.check_mask_decay("op", q, k, torch.zeros(4, 128, 256), None)
+    with pytest.raises(ValueError, match="per-head"):
+        _checks.check_mask_decay("op", q, k, None, torch.ones(3))
+    _checks.check_mask_decay("op", q, k, torch.zeros(4, 128, 256, dtype=h), None)
+    with pytest.raises(ValueError, match="dO has shape"):
+        _checks.check_like("op", "dO", torch.zeros(2, 4, 128, 64, dtype=h), (2, 4, 128, 128), h, q.device)
+
+
+def test_timing_statistics():
+    from attention_autotuner_b200.utils import timing
+    s = timing.summarize([5.0, 1.0, 3.0, 2.0, 4.0])
+    assert s["median_ms"] == 3.0 and s["min_ms"] == 1.0 and s["reps"] == 5
+    assert abs(s["p20_ms"] - 1.8) < 1e-9 and abs(s["p80_ms"] - 4.2) < 1e-9
+    assert timing.percentile([7.0], 0.8) == 7.0
+    with pytest.raises(ValueError):
+        timing.percentile([], 0.5)
+
+
+def test_bench_flop_model_and_workload_table():
+    import bench
+    assert abs(bench.flops_of("C2") - 1.0995e12) / 1.0995e12 < 1e-3
+    assert abs(bench.flops_of("C5sq") - 70.37e12) / 70.37e12 < 1e-3
+    assert abs(bench.flops_of("C5dec") - 4.398e12) / 4.398e12 < 1e-3
+    assert abs(bench.flops_of("C5sq", 64) * 8 - bench.flops_of("C5sq")) < 1.0     # 64 of 512 slices on each of 8 ranks
+    assert bench.flops_of("C2bwd") == bench.flops_of("C2") * 3.5
+    for name in bench.EXTRA_SHORT + bench.STRONG + bench.SUSTAINED:
+        assert name in bench.WORKLOADS
