@@ -121,15 +121,26 @@ class BaseTunner:
         return 0.0
 
     # ------------------------------------------------------------------ tune
-    def tune(self, log_path=None, *, search=None):
-        """Returns the best configuration: from the JSON cache if present; otherwise by searching
+    def problem(self) -> dict:
+        """Problem description the cost model works on."""
+        t = self.torch_array
+        B, H, Lq, dqk = (int(x) for x in t[0].shape)
+        return dict(B=B, H=H, Lq=Lq, Lkv=int(t[1].shape[2]), dqk=dqk, dv=int(t[2].shape[3]), causal=self._cost_model_causal())
+
+    def _cost_model_causal(self) -> bool:
+        return self.causal
+
+    def tune(self, log_path=None, *, search=None, top_k=None, force=False):
+        """Returns the best configuration: from the JSON cache if present (unless ``force``); otherwise by searching
         (default, as in the reference) or, when ``search`` is False / ATTN_B200_AUTOTUNE=0 / nvcc is missing,
-        the built-in default."""
+        the built-in default. ``top_k`` (or ATTN_B200_TUNE_TOPK) prunes the search with the cost model
+        (autotuner/cost_model.py): only the k candidates it predicts fastest are compiled and timed. Without
+        pruning the log records what pruning to five candidates would have picked and at what regret."""
         st = time.time()
         dim_qk = self.problem_key["dim_qk"]
         dim_v = self.problem_key["dim_v"]
 
-        best_config = self.check_cache()
+        best_config = None if force else self.check_cache()
         if best_config is not None:
             return best_config
         if search is None:
@@ -138,11 +149,27 @@ class BaseTunner:
             return self.default_config()
 
         configs = self.get_tuned_configs()
+        n_candidates = len(configs)
+        if top_k is None and os.environ.get("ATTN_B200_TUNE_TOPK"):
+            top_k = int(os.environ["ATTN_B200_TUNE_TOPK"])
+        predicted = {}
+        try:
+            from . import cost_model
+            op = configs[0].operation if configs else None
+            prob = self.problem()
+            predicted = {c: cost_model.predict_ms(op, c.__dict__, prob) for c in configs}
+            if top_k is not None and 0 < top_k < len(configs):
+                configs = cost_model.rank(op, configs, prob)[:top_k]
+        except (OSError, KeyError, ValueError) as e:  # no weights file, or no weights for this operation: search everything
+            print("cost model unavailable (%s): exhaustive search" % e)
+            predicted = {}
         print("Configs to be tuned: ")
         for config in configs:
             pprint.pprint(config)
 
+        t_compile = time.time()
         cresults = self.compile_parallel(configs, DEFAULT_JIT_DIR, timeout=300)
+        t_compile = time.time() - t_compile
         profile_dict = {}
         latency = 1e8
         best_config = None
@@ -191,14 +218,34 @@ class BaseTunner:
                 "dtype": self.dtype, "causal": self.causal, "flops": fl, "peak_tflops": peak,
                 "results": [{"config": repr(c), "ms": ms,
                              "tflops": (fl / ms / 1e9 if ms < 1e8 else 0.0),
-                             "frac_of_peak": (fl / ms / 1e9 / peak if ms < 1e8 and peak else 0.0)}
+                             "frac_of_peak": (fl / ms / 1e9 / peak if ms < 1e8 and peak else 0.0),
+                             "predicted_ms": predicted.get(c)}
                             for c, ms in profile_dict.items()],
-                "best": repr(best_config), "best_ms": latency, "search_time_s": end - st}, f, indent=1)
+                "best": repr(best_config), "best_ms": latency, "search_time_s": end - st,
+                "compile_time_s": t_compile,
+                "cost_model": self._cost_model_record(profile_dict, predicted, n_candidates, top_k, t_compile, end - st)},
+                f, indent=1)
 
         os.makedirs(self.cache_path, exist_ok=True)
         with open(self._cache_file(), "w") as f:
             json.dump(best_config.to_dict(), f)
         return best_config
+
+    @staticmethod
+    def _cost_model_record(profile_dict, predicted, n_candidates, top_k, t_compile, t_search, k_report=5):
+        """What the cost model did (pruned search) or would have done (exhaustive search) for this problem."""
+        rec = {"candidates": n_candidates, "timed": len(profile_dict), "pruned_to_top_k": top_k}
+        timed = [(c, ms) for c, ms in profile_dict.items() if ms < 1e8 and predicted.get(c) is not None]
+        if len(timed) >= 2 and (top_k is None or top_k >= n_candidates):
+            order = sorted(timed, key=lambda t: predicted[t[0]])
+            k = min(k_report, len(order))
+            best_all = min(ms for _c, ms in timed)
+            best_k = min(ms for _c, ms in order[:k])
+            rec.update({"what_if_top_k": k, "what_if_best_ms": best_k, "what_if_regret": best_k / best_all - 1.0,
+                        "rank_of_measured_best": 1 + [ms for _c, ms in order].index(best_all),
+                        # compilation dominates the search and is spread over the cores: k of n candidates cost about k/n
+                        "what_if_search_time_s": t_search - t_compile * (1.0 - k / len(order))})
+        return rec
 
     # ------------------------------------------------------------------ cache
     def _key_suffix(self) -> str:

@@ -15,6 +15,8 @@ class AttnConfig(BaseConfig):
       softmax_split  softmax warpgroups per query tile (1, or 2: two threads share a score row; needs q_tiles == 2)
       mma_warps  MMA-issuing warps: 1, or 2 taking strict turns, one per query tile (needs q_tiles == 2)
       exp_emu    of every 8 pairs of scores, how many use the FMA-pipe exp2 polynomial instead of MUFU (0..8)
+      exp_h2     of every 4 groups of 8 scores, how many use the packed fp16 exponential (two results per MUFU
+                 operation; fp16 only, needs softmax_split == 1 and exp_emu == 0; the rescale threshold drops to 2^4)
       cta_pair   1: clusters of two CTAs with cta_group::2 MMAs (512 query rows per pair, each CTA streams half of K and V);
                  needs q_tiles == 2, dv_chunk == 128 and the other second-order knobs at their defaults;
                  kv_stages then counts full K/V tiles as before (the ring holds twice as many half tiles)
@@ -23,7 +25,7 @@ class AttnConfig(BaseConfig):
     def __init__(self, Br, Bc, Kd, D, BlockKSmem=256, BlockKSmem2=64, num_stages_qk=1, num_stages_v=1,
                  Nthreads=256, unrollLastIter: bool = True, warps_mma1_n=None, warps_mma_n=None, *,
                  q_tiles=None, kv_stages=None, dv_chunk=None, softmax_split=1, exp_emu=0, mma_warps=1, cta_pair=0,
-                 dtype: str = "fp16") -> None:
+                 exp_h2=0, dtype: str = "fp16") -> None:
         super().__init__(Br, Bc, Kd, D, BlockKSmem, num_stages_qk, Nthreads, unrollLastIter, dtype=dtype)
         self.BlockKSmem2 = BlockKSmem2
         self.num_stages_v = num_stages_v
@@ -37,6 +39,7 @@ class AttnConfig(BaseConfig):
         self.softmax_split = softmax_split
         self.exp_emu = exp_emu
         self.mma_warps = mma_warps
+        self.exp_h2 = int(exp_h2)
         self.cta_pair = int(cta_pair)
         self.Br = 128 * self.q_tiles
         self.Bc = 128
@@ -60,18 +63,19 @@ class AttnConfig(BaseConfig):
             d["cfg_type"] = "FaPairConfig<{}, {}, {}>".format(self.Kd, 2 * self.kv_stages, d["bf16"])
             d["launcher"] = "fa_fwd_pair_launch"
         else:
-            d["cfg_type"] = "FaFwdConfig<{}, {}, {}, {}, {}, {}, {}, {}>".format(
+            d["cfg_type"] = "FaFwdConfig<{}, {}, {}, {}, {}, {}, {}, {}, {}>".format(
                 self.Kd, self.dv_chunk, self.q_tiles, self.kv_stages, d["bf16"], self.exp_emu, self.softmax_split,
-                self.mma_warps)
+                self.mma_warps, self.exp_h2)
             d["launcher"] = "fa_fwd_launch"
         return d
 
     def __repr__(self) -> str:
         return ("Config(fuse_type={}, Br={}, Bc={}, Kd={}, D={}, q_tiles={}, kv_stages={}, dv_chunk={}, softmax_split={}, "
-                "exp_emu={}, mma_warps={}, cta_pair={}, dtype={})".format(
+                "exp_emu={}, mma_warps={}, cta_pair={}, exp_h2={}, dtype={})".format(
                     self.fuse_type, self.Br, self.Bc, self.Kd, self.D, self.q_tiles, self.kv_stages, self.dv_chunk,
-                    self.softmax_split, self.exp_emu, self.mma_warps, self.cta_pair, self.dtype))
+                    self.softmax_split, self.exp_emu, self.mma_warps, self.cta_pair, self.exp_h2, self.dtype))
 
     def __str__(self) -> str:
         return (f"attn_{self.fuse_type}_{self.Br}_{self.Bc}_{self.Kd}_{self.D}_{self.q_tiles}_{self.kv_stages}_{self.dv_chunk}_"
-                f"{self.softmax_split}_{self.exp_emu}_{self.mma_warps}_{self.cta_pair}_{self.dtype}")
+                f"{self.softmax_split}_{self.exp_emu}_{self.mma_warps}_{self.cta_pair}_"
+                + (f"h{self.exp_h2}_" if self.exp_h2 else "") + f"{self.dtype}")

@@ -16,6 +16,8 @@ def main():
     ap.add_argument("--log-dir", default=None)
     ap.add_argument("--cache-dir", default=None)
     ap.add_argument("--quick", action="store_true", help="small batch (same head dims and sequence lengths)")
+    ap.add_argument("--force", action="store_true", help="search even where a cache entry exists, and overwrite it")
+    ap.add_argument("--top-k", type=int, default=None, help="prune every search to the cost model's k best candidates")
     args = ap.parse_args()
     if args.cache_dir:
         os.environ["ATTN_B200_CACHE_DIR"] = args.cache_dir
@@ -38,7 +40,7 @@ def main():
             B = 2
         q, k, v = rnd(B, H, L, d, dt=dt), rnd(B, H, L, d, dt=dt), rnd(B, H, L, d, dt=dt)
         o = torch.empty_like(q)
-        cfg = AttnTunner(arch, [q, k, v, o], scale=d ** -0.5, causal=causal).tune(args.log_dir)
+        cfg = AttnTunner(arch, [q, k, v, o], scale=d ** -0.5, causal=causal).tune(args.log_dir, force=args.force, top_k=args.top_k)
         print("attention", d, dt, causal, "->", repr(cfg), flush=True)
         del q, k, v, o
 
@@ -47,12 +49,12 @@ def main():
     q, k, v, do = rnd(B, H, L, dqk), rnd(B, H, L, dqk), rnd(B, H, L, dv), rnd(B, H, L, dv)
     o, r = torch.empty_like(v), torch.empty(B, H, L, device=dev)
     gam = (1.0 - torch.pow(2.0, -5.0 - torch.arange(H, dtype=torch.float64))).float().to(dev)
-    cfg = RetTunner(arch, [q, k, v, None, o, r], scale=dqk ** -0.5, decay=gam).tune(args.log_dir)
+    cfg = RetTunner(arch, [q, k, v, None, o, r], scale=dqk ** -0.5, decay=gam).tune(args.log_dir, force=args.force, top_k=args.top_k)
     print("retnet fwd ->", repr(cfg), flush=True)
     from .runtime import Runtime
     Runtime(arch, cfg).apply([q, k, v, None, o, r], scale=dqk ** -0.5, decay=gam)   # a valid r for the backward
     dq, dk, dvo = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    cfg = RetBwdTunner(arch, [q, k, v, None, do, r, dq, dk, dvo, None], scale=dqk ** -0.5, decay=gam).tune(args.log_dir)
+    cfg = RetBwdTunner(arch, [q, k, v, None, do, r, dq, dk, dvo, None], scale=dqk ** -0.5, decay=gam).tune(args.log_dir, force=args.force, top_k=args.top_k)
     print("retnet bwd ->", repr(cfg), flush=True)
 
 

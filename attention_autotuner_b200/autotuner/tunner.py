@@ -38,6 +38,9 @@ class AttnTunner(BaseTunner):
             return False
         if config.mma_warps == 2 and config.q_tiles != 2:
             return False
+        if getattr(config, "exp_h2", 0) and (config.dtype != "fp16" or config.softmax_split != 1 or config.exp_emu != 0
+                                              or config.cta_pair or not 0 < config.exp_h2 <= 4):
+            return False
         if config.cta_pair and (config.q_tiles != 2 or config.dv_chunk != 128 or config.softmax_split != 1
                                 or config.exp_emu != 0 or config.mma_warps != 1):
             return False
@@ -57,6 +60,12 @@ class AttnTunner(BaseTunner):
                 for split, emu, mw in ((2, 0, 1), (2, 2, 1), (1, 2, 1), (1, 0, 2), (2, 0, 2)):
                     configs.append(AttnConfig(Br, Bc, dim_qk, dim_v, q_tiles=2, kv_stages=4, dv_chunk=dv_chunk,
                                               softmax_split=split, exp_emu=emu, mma_warps=mw, dtype=self.dtype))
+                # packed half-precision exponentials (two per MUFU operation) for a quarter / half / all of the scores
+                if self.dtype == "fp16":
+                    for h2 in (1, 2, 3, 4):
+                        for stages in (4, 5):
+                            configs.append(AttnConfig(Br, Bc, dim_qk, dim_v, q_tiles=2, kv_stages=stages, dv_chunk=dv_chunk,
+                                                      exp_h2=h2, dtype=self.dtype))
                 # CTA pairs (cta_group::2): 512 query rows per cluster
                 for stages in (3, 4):
                     configs.append(AttnConfig(Br, Bc, dim_qk, dim_v, q_tiles=2, kv_stages=stages, dv_chunk=dv_chunk,
@@ -112,6 +121,9 @@ class _RetBase(BaseTunner):
 
     def _pairs_causal(self):
         return self.causal or self.decay is not None
+
+    def _cost_model_causal(self) -> bool:
+        return self._pairs_causal()
 
 
 class RetTunner(_RetBase):

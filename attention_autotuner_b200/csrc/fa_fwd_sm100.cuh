@@ -35,8 +35,21 @@ struct FaFwdParams {
   float scale_log2;    // scale * log2(e)
 };
 
-template <int DQK_, int DV_, int NQ_, int NSTAGE_, bool BF16_, int EXP_EMU_ = 0, int SPLIT_ = 1, int NMMA_ = 1>
+template <int DQK_, int DV_, int NQ_, int NSTAGE_, bool BF16_, int EXP_EMU_ = 0, int SPLIT_ = 1, int NMMA_ = 1, int EXP_H2_ = 0>
 struct FaFwdConfig {
+  // of every 4 groups of 8 scores, how many take the packed half-precision exponential (ex2.approx.f16x2: two
+  // results per MUFU operation, already in P's storage type). fp16 only; 0 = every exponential in fp32. MUFU is
+  // as scarce as the tensor pipe at head dimension 128 (one ex2 per 256 tensor FLOP, 16 per clock and SM), so this
+  // halves the longest phase of the softmax. The argument of the exponential is rounded to fp16 first, whose
+  // precision falls with |x|: configurations that use it keep the lazy-rescale threshold at 2^4 instead of 2^8, so
+  // that the entries that dominate a row have |x| < 4 (relative error below 6.8e-4, against 4.9e-4 for rounding P
+  // itself to fp16). Row sums of these groups are added in fp16 over four pairs (values below 2^5) and
+  // accumulated in fp32.
+  static constexpr int EXP_H2 = EXP_H2_;
+  static_assert(EXP_H2_ >= 0 && EXP_H2_ <= 4, "EXP_H2 counts groups out of 4");
+  static_assert(EXP_H2_ == 0 || (!BF16_ && SPLIT_ == 1 && EXP_EMU_ == 0), "EXP_H2 needs fp16, one softmax warpgroup per tile, no FMA-pipe emulation");
+  // log2 of the growth of the running maximum that triggers a rescale of O
+  static constexpr float RESCALE_LOG2 = EXP_H2_ > 0 ? 4.0f : 8.0f;
   // MMA-issuing warps: 1, or 2 taking strict turns, one per query tile (see fa_fwd_mma_pair.cuh)
   static constexpr int NMMA = NMMA_;
   static_assert(NMMA_ == 1 || (NMMA_ == 2 && NQ_ == 2), "NMMA");
@@ -399,7 +412,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (threadIdx.x % 128 == 0) AB200_TR(s, j, 3);
 
       // Lazy rescale: keep the old reference unless the maximum grew by more than 2^8 in the exp2 domain.
-      bool need = (j == 0) || ((m_blk - m_ref) * p.scale_log2 > 8.0f);
+      bool need = (j == 0) || ((m_blk - m_ref) * p.scale_log2 > Cfg::RESCALE_LOG2);
       if (m_blk == -INFINITY) need = false;
       if (__any_sync(0xffffffffu, need)) {
         float alpha = 1.0f;
@@ -429,6 +442,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const uint64_t sl2 = f2_pack(p.scale_log2, p.scale_log2);
       const uint64_t nm2 = f2_pack(neg_m, neg_m);
       uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
+      uint32_t hsum = 0;  // fp16 pair: sum of up to four packed exponentials of a group (EXP_H2)
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t pk[BN / 4];
@@ -436,6 +450,19 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int c = 0; c < BN / 2; c += 2) {
           const int cc = h * (BN / 2) + c;
           const uint64_t x2 = ffma2(f2_pack(sv[cc], sv[cc + 1]), sl2, nm2);
+          if constexpr (Cfg::EXP_H2 > 0) {
+            // groups of four pairs (8 scores): EXP_H2 of every 4 groups use the packed fp16 exponential
+            if (((c >> 3) & 3) < Cfg::EXP_H2) {
+              float x0, x1;
+              f2_unpack(x2, x0, x1);
+              const uint32_t ph = ex2_approx_h2(pack2<false>(x0, x1));
+              pk[c >> 1] = ph;
+              if (((c >> 1) & 3) == 0) hsum = ph;
+              else hsum = hadd2_u32(hsum, ph);
+              if (((c >> 1) & 3) == 3) acc[(c >> 3) & 3] = fadd2(acc[(c >> 3) & 3], h2_to_f2(hsum));
+              continue;
+            }
+          }
           float e0, e1;
           if (((c >> 1) & 7) < Cfg::EXP_EMU) {
             exp2_poly2(x2, e0, e1);  // FMA-pipe exponential for EXP_EMU of every 8 pairs

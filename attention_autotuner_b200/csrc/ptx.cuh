@@ -375,6 +375,34 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Two exponentials per MUFU operation: 2^x for a pair of fp16 values, results in fp16 (subnormal results are kept).
+// The input pair is what cvt.rn.f16x2 makes of x, so the relative error of a result is about ln2 * ulp_fp16(x) / 2:
+// 3.4e-4 for 1 <= |x| < 2, 6.8e-4 for 2 <= |x| < 4, doubling per binade of |x|.
+__device__ __forceinline__ uint32_t ex2_approx_h2(uint32_t xh2) {
+  uint32_t y;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(xh2));
+  return y;
+}
+__device__ __forceinline__ uint32_t hadd2_u32(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+// The two fp16 halves of a register as a packed fp32 pair (low half first).
+__device__ __forceinline__ uint64_t h2_to_f2(uint32_t h2) {
+  float lo, hi;
+  asm("{\n\t"
+      ".reg .b16 l, h;\n\t"
+      "mov.b32 {l, h}, %2;\n\t"
+      "cvt.f32.f16 %0, l;\n\t"
+      "cvt.f32.f16 %1, h;\n\t"
+      "}\n"
+      : "=f"(lo), "=f"(hi)
+      : "r"(h2));
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
 // Three-input maximum and packed two-wide fp32 arithmetic (sm_100): halve the instruction count of the
 // element-wise phases.
 __device__ __forceinline__ float fmax3(float a, float b, float c) {

@@ -209,9 +209,10 @@ def test_linearity_and_determinism_at_config3_size(lib):
 def test_config4_every_slice_against_the_oracle(lib, form):
     """B=8 H=8 L=2048 dqk=256 dv=512 fp16, scale 1/16, the decay mask given as per-head gammas and as the reference's
     materialised [H, L, L] fp16 mask tensor (its own call form): O, r, dQ, dK, dV of all 64 (batch, head) slices
-    against the fp32 oracle (r detached in the backward, as python/utils/ref_op.py:11). O is bounded by max |V| / r
-    and stays below 1 here, so its bound is the ABSOLUTE 2e-3 / 2e-4; the gradients sum thousands of terms and are
-    gated relative to their peak. The worst figures over the slices are printed for every tensor."""
+    against the fp32 oracle (r detached in the backward, as python/utils/ref_op.py:11). O is a convex-like combination
+    of rows of V (sum_j |S~_ij| / r <= 1), so |O| <= max |V| (about 4 for N(0,1) values) and it is held to the ABSOLUTE
+    2e-3 / 2e-4 bound; the gradients sum thousands of terms (peaks of 7 to 16) and are gated relative to their peak.
+    The worst figures over the slices are printed for every tensor."""
     c = oracle.CONFIGS["C4"]
     B, H, L, dqk, dv = c["B"], c["H"], c["Lq"], c["dqk"], c["dv"]
     scale = 1 / 16
@@ -243,8 +244,8 @@ def test_config4_every_slice_against_the_oracle(lib, form):
                 worst[n] = {key: max(worst[n][key], st[key]) for key in st}
     for n in names:
         assert oracle.report(f"C4 ({form}) worst of 64 slices {n}", worst[n], "fp16", scale_by_peak=True)
-    # O never exceeds 1 in magnitude here, so the bound that gated it was the absolute one
-    assert worst["o"]["ref_peak"] <= 1.0 and oracle.within(worst["o"], "fp16", scale_by_peak=False)
+    # O meets the absolute bound (no scaling by its peak)
+    assert oracle.within(worst["o"], "fp16", scale_by_peak=False), worst["o"]
 
 
 def test_python_operator_forward_backward(lib):

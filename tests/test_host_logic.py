@@ -322,3 +322,41 @@ def test_bench_flop_model_and_workload_table():
     assert bench.flops_of("C2bwd") == bench.flops_of("C2") * 3.5
     for name in bench.EXTRA_SHORT + bench.STRONG + bench.SUSTAINED:
         assert name in bench.WORKLOADS
+
+
+def test_cost_model_ranks_the_measured_best_near_the_top():
+    """The cost model is fitted on the committed search logs. Held-out check: fit on all logs but one, rank the
+    held-out log's candidates; timing only the five predicted fastest must find a configuration within 3 % of the
+    exhaustive search's best, for every committed log."""
+    from attention_autotuner_b200.autotuner import cost_model as cm
+    logs = cm.load_logs()
+    assert len(logs) >= 5
+    recs = cm.pruning_report(top_k=5, logs=logs)
+    assert {r["operation"] for r in recs} == {"attn", "ret", "ret_bwd"}
+    for r in recs:
+        assert r["regret"] <= 0.03, r
+    # the committed weights are the fit of the committed logs, and predictions are in the right range
+    w = cm.load_weights()
+    refit = cm.fit(logs)
+    for op in refit:
+        for name, val in refit[op].items():
+            assert abs(w[op][name] - val) <= 1e-6 + 1e-6 * abs(val), (op, name)
+    name, op, problem, rows = logs[0]
+    for cfg, ms in rows:
+        assert 0.5 * ms < cm.predict_ms(op, cfg, problem) < 2.0 * ms
+
+
+def test_cost_model_prunes_the_search_space_without_a_gpu():
+    from attention_autotuner_b200.autotuner import cost_model as cm
+    t = AttnTunner(B200(), [torch.zeros(8, 16, 4096, 128, dtype=torch.float16)] * 4)
+    cfgs = t.get_tuned_configs()
+    ranked = cm.rank("attn", cfgs, t.problem())
+    assert len(ranked) == len(cfgs) and set(map(str, ranked)) == set(map(str, cfgs))
+    # two ping-ponging query tiles beat one, full-width V chunks beat half-width ones
+    assert ranked[0].q_tiles == 2 and ranked[0].dv_chunk == 128
+    assert ranked[-1].dv_chunk == 64
+    assert cm.parse_config_repr("Config(fuse_type=tmem, Br=128, q_tiles=2, dtype=fp16)") == {
+        "fuse_type": "tmem", "Br": 128, "q_tiles": 2, "dtype": "fp16"}
+    rec = t._cost_model_record({cfgs[0]: 1.0, cfgs[1]: 2.0, cfgs[2]: 0.5}, {cfgs[0]: 1.1, cfgs[1]: 1.9, cfgs[2]: 0.6}, 30, None,
+                               10.0, 12.0, k_report=1)
+    assert rec["what_if_regret"] == 0.0 and rec["rank_of_measured_best"] == 1 and rec["what_if_search_time_s"] < 12.0
