@@ -229,6 +229,14 @@ class BaseTunner:
         os.makedirs(self.cache_path, exist_ok=True)
         with open(self._cache_file(), "w") as f:
             json.dump(best_config.to_dict(), f)
+        if os.environ.get("ATTN_B200_REFERENCE_FILES", "0") == "1":
+            # the reference's own file names (python/autotuner/base_tunner.py:178-193): one log and one cache entry per
+            # (operation, dqk, dv), whatever the dtype or mask form; same text format, so old and new logs diff
+            import shutil
+            shutil.copyfile(os.path.join(log_path, stem + ".txt"),
+                            os.path.join(log_path, "profile_result_{}_{}_{}.txt".format(best_config.operation, dim_qk, dim_v)))
+            with open(os.path.join(self.cache_path, "best_config_{}_{}_{}.json".format(self.op_name, dim_qk, dim_v)), "w") as f:
+                json.dump(best_config.to_dict(), f)
         return best_config
 
     @staticmethod
