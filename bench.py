@@ -56,6 +56,10 @@ WORKLOADS = {
     "C2bwd": (8, 16, 4096, 4096, 128, 128, "fp16", False),
     "C2bwdcausal": (8, 16, 4096, 4096, 128, 128, "fp16", True),
     "C2bf16causal": (8, 16, 4096, 4096, 128, 128, "bf16", True),
+    # reduced batches of the same shapes for profiler captures (inputs still larger than the L2)
+    "C2small": (2, 16, 4096, 4096, 128, 128, "fp16", False),
+    "C2bwdsmall": (2, 16, 4096, 4096, 128, 128, "fp16", False),
+    "C4small": (2, 8, 2048, 2048, 256, 512, "fp16", True),
     # long sequences, bf16, 512 (batch, head) slices split over the ranks
     "C5sq": (16, 32, 16384, 16384, 128, 128, "bf16", False),
     "C5sqcausal": (16, 32, 16384, 16384, 128, 128, "bf16", True),
@@ -63,8 +67,8 @@ WORKLOADS = {
 }
 METRIC = "attn fwd TFLOPS at B=8,H=16,L=4096,d=128 fp16"
 UNIT = "TFLOP/s"
-ATTN_BWD = ("C2bwd", "C2bwdcausal")
-RETNET = {"C3": "fwd", "C4": "fwd+bwd", "C3mask": "fwd", "C4mask": "fwd+bwd"}
+ATTN_BWD = ("C2bwd", "C2bwdcausal", "C2bwdsmall")
+RETNET = {"C3": "fwd", "C4": "fwd+bwd", "C3mask": "fwd", "C4mask": "fwd+bwd", "C4small": "fwd+bwd"}
 STRONG = ("C5sq", "C5sqcausal", "C5dec")
 EXTRA_SHORT = ("C2causal", "C2bf16", "C2bf16causal", "C3", "C3mask", "C4", "C4mask", "C2bwd")
 SUSTAINED = ("C2", "C4")
@@ -76,8 +80,8 @@ NCU_TRAFFIC_BYTES = {"C2": 515.2e6, "C3": 383.6e6, "C4": 1725.3e6}
 
 def metric_name(workload):
     if workload in RETNET:
-        return "RetNet %s TFLOPS at B=8,H=8,L=2048,dqk=256,dv=512 fp16 (decay mask%s, unmasked pairs counted)" % (
-            RETNET[workload], " as a mask tensor" if workload.endswith("mask") else "")
+        return "RetNet %s TFLOPS at B=%d,H=8,L=2048,dqk=256,dv=512 fp16 (decay mask%s, unmasked pairs counted)" % (
+            RETNET[workload], WORKLOADS[workload][0], " as a mask tensor" if workload.endswith("mask") else "")
     if workload == "C2":
         return METRIC
     B, H, Lq, Lkv, dqk, dv, dtype, causal = WORKLOADS[workload]
