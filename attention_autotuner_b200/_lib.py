@@ -54,6 +54,8 @@ def _declare(lib):
     lib.attn_b200_selftest_gemm_ts.argtypes = [vp, vp, vp, ci, ci, vp]
     lib.attn_b200_selftest_pair.restype = ci
     lib.attn_b200_selftest_pair.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, vp]
+    lib.attn_b200_ret_chunk_fwd.restype = ci
+    lib.attn_b200_ret_chunk_fwd.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, cf, vp]
     lib.attn_b200_selftest_wait.restype = ci
     lib.attn_b200_selftest_wait.argtypes = [ci, ci, vp]
     for name, sig in _OPTIONAL.items():

@@ -7,6 +7,7 @@
 #include "chain_launch.cuh"
 #include "fa_bwd_launch.cuh"
 #include "fa_fwd_launch.cuh"
+#include "ret_chunk_launch.cuh"
 #include "selftest.cuh"
 #include "selftest_pair.cuh"
 
@@ -198,6 +199,15 @@ float attn_b200_ret_bwd_profile(const void* q, const void* k, const void* v, con
   int rc = ret_common(true, ret_args(q, k, v, mask, decay, nullptr, const_cast<float*>(r), dout, dq, dk, dv_out, B, H,
                                      Lq, Lkv, dqk, dv, scale, causal), dtype, stream, true, &ms);
   return rc == kOk ? ms : -1.f;
+}
+
+int attn_b200_ret_chunk_fwd(const void* q, const void* k, const void* v, const float* decay, void* o, int B, int H, int L,
+                            int dqk, int dv, int dtype, float scale, void* stream) {
+  if (B <= 0 || H <= 0) return fail(kErrInvalidArgument, "ret_chunk_fwd: B and H must be positive");
+  if (dtype != ATTN_B200_F16 && dtype != ATTN_B200_BF16) return fail(kErrInvalidArgument, "ret_chunk_fwd: dtype %d", dtype);
+  RetChunkArgs a{q, k, v, decay, o, B * H, H, L, dqk, dv, scale};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return dtype == ATTN_B200_BF16 ? ret_chunk_dispatch<true>(a, st) : ret_chunk_dispatch<false>(a, st);
 }
 
 int attn_b200_selftest_gemm_ss(const void* a, const void* b, float* d, int N, int K, int dtype, void* stream) {

@@ -1,0 +1,405 @@
+// Chunkwise (recurrent-state) RetNet forward for sm_100a: the unnormalised retention
+//
+//     O[i] = scale * sum_{j <= i} gamma^(i-j) (q_i . k_j) v_j
+//
+// computed in chunks of 128 positions with a running state instead of over all (i, j) pairs, so the work grows
+// with L, not L^2. It is the function the reference's recurrent kernel computes with an fp32 CUB scan
+// (csrc/kernels/retnet/recurrent/recurrent.h:110-114 scan operator, :132-395 scan_fwd_kernel, C entry
+// retnet_recurrent_fwd :427-463: state_t = decay_t * state_{t-1} + k_t v_t^T, out_t = q_t . state_t) for a per-head
+// constant decay, and the "chunkwise retnet" its README lists as to do (README.md:103). Here the state lives in
+// tensor memory and every product runs on the tcgen05 tensor cores.
+//
+// One CTA owns one (batch, head) slice and DVC columns of V / O and walks the sequence chunk by chunk. With
+// S = state after the previous chunk [dqk x DVC] and g = gamma^128:
+//
+//     Z   = Q_c K_c^T                             [128 x 128]   both operands K-major in shared memory
+//     ACC = Q_c S                                 [128 x DVC]   S as 16-bit copy in shared memory (MN-major B operand)
+//     ACC[i] *= gamma^(i+1)                       in tensor memory, by the thread that owns row i
+//     W   = Z .* gamma^(i-j) for j <= i, else 0   fp32 in registers, 16-bit written over Z in tensor memory
+//     ACC += W V_c                                W from tensor memory
+//     O_c = scale * ACC
+//     V_c[j] *= gamma^(127-j)                     in place in shared memory, once W V_c has read the plain tile
+//     S   = g S + K_c^T V_c                       fp32 in tensor memory; K_c^T is the MN-major A operand
+//
+// Every decay factor is applied where its value is at most 1 and in fp32 or on a term whose weight it is: W carries
+// gamma^(i-j) computed in fp32 registers, the carried term is scaled in the fp32 accumulator, and the scaled V rows
+// only feed the state update, where a row that underflows in 16 bits is a contribution that small. So no
+// intermediate exceeds the magnitudes of Q K^T and V whatever gamma in (0, 1] is, and no scratch memory is needed.
+//
+// Roles: warps 0-3 element-wise warpgroup (thread t owns TMEM lane t: a row of Z / ACC, or a row of the state, and
+// row t of the V tile), warp 4 issues every MMA (converged warp, one elected lane; a single issuer keeps all
+// tensor-memory hazards in program order), warp 5 lane 0 is the TMA producer. Tensor memory: Z at [0,128), ACC at
+// [128,128+DVC), the state halves (dqk rows 0-127, 128-255) at [256,256+DVC) and [384,384+DVC).
+#pragma once
+
+#include "chain_common.cuh"
+
+namespace ab200 {
+
+struct RetChunkParams {
+  void* o;               // [BH, L, dv] 16-bit
+  const float* decay;    // [H] gammas
+  int H, L, dv;
+  float scale;
+};
+
+template <int DQK_, int DVC_, bool BF16_>
+struct RetChunkConfig {
+  static constexpr int DQK = DQK_;    // head dimension of q, k: 128 or 256 (the state tile has 128 rows per MMA)
+  static constexpr int DVC = DVC_;    // columns of V / O per CTA: 64 or 128
+  static constexpr bool BF16 = BF16_;
+  static constexpr int C = 128;       // chunk length
+  static constexpr int NH = DQK / 128;       // state halves
+  static constexpr int KB = DQK / 64;        // boxes per Q / K tile
+  static constexpr int VB = DVC / 64;        // boxes per V tile
+  static constexpr int BOX_BYTES = 128 * 128;
+  static constexpr int QK_BYTES = KB * BOX_BYTES;
+  static constexpr int V_BYTES = VB * BOX_BYTES;
+  static constexpr int SB_HALF_BYTES = VB * BOX_BYTES;  // 128 state rows x DVC columns, 16-bit
+  static constexpr int SMEM_TILES = 2 * QK_BYTES + V_BYTES + NH * SB_HALF_BYTES;
+  static constexpr int SMEM_BYTES = 1024 + SMEM_TILES + 512;
+  static constexpr int NTHREADS = 192;
+  static constexpr int TMEM_COLS = 512;
+  static_assert(DQK == 128 || DQK == 256, "dqk");
+  static_assert(DVC == 64 || DVC == 128, "dv chunk");
+  static_assert(SMEM_BYTES <= 232448, "shared memory");
+};
+
+enum RetChunkTag : int {
+  kRcQ = 51, kRcK = 52, kRcV = 53, kRcQFree = 54, kRcKVFree = 55, kRcZ = 56, kRcW = 57, kRcAcc = 58, kRcAccFree = 59,
+  kRcU = 60, kRcState = 61, kRcY = 62, kRcVScaled = 63
+};
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::NTHREADS, 1)
+ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, const RetChunkParams p) {
+  constexpr int DQK = Cfg::DQK, DVC = Cfg::DVC, NH = Cfg::NH, KB = Cfg::KB, VB = Cfg::VB, BOX = Cfg::BOX_BYTES;
+  constexpr bool BF16 = Cfg::BF16;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + Cfg::QK_BYTES;
+  uint8_t* sV = sK + Cfg::QK_BYTES;
+  uint8_t* sSb = sV + Cfg::V_BYTES;  // NH halves of [128 state rows][DVC] 16-bit, laid out like a V tile
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::SMEM_TILES);
+  uint64_t* q_full = bars + 0;     // Q chunk landed                                   (TMA -> MMA)
+  uint64_t* k_full = bars + 1;     // K chunk landed
+  uint64_t* v_full = bars + 2;     // V chunk landed
+  uint64_t* q_free = bars + 3;     // Z and Q S of the chunk complete                   (MMA -> TMA)
+  uint64_t* kv_free = bars + 4;    // state update of the chunk complete: K and V free  (MMA -> TMA)
+  uint64_t* z_full = bars + 5;     // Z complete                                        (MMA -> element-wise)
+  uint64_t* w_full = bars + 6;     // W written over Z and the carried term scaled       (element-wise -> MMA), 128 arrivals
+  uint64_t* acc_done = bars + 7;   // ACC of the chunk complete                         (MMA -> element-wise)
+  uint64_t* acc_free = bars + 8;   // ACC read into registers                           (element-wise -> MMA), 128 arrivals
+  uint64_t* u_done = bars + 9;     // state update of the chunk complete                (MMA -> element-wise)
+  uint64_t* s_ready = bars + 10;   // decayed state in TMEM and its 16-bit copy in smem (element-wise -> MMA), 128 arrivals
+  uint64_t* y_done = bars + 11;    // Q S complete                                      (MMA -> element-wise)
+  uint64_t* v_scaled = bars + 12;  // rows of the V tile scaled in place                (element-wise -> MMA), 128 arrivals
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 1);
+
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
+  const int lane = threadIdx.x & 31;
+  const int bh = blockIdx.y;
+  const int n_off = blockIdx.x * DVC;
+  const int nchunk = (p.L + 127) / 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(k_full, 1);
+    mbar_init(v_full, 1);
+    mbar_init(q_free, 1);
+    mbar_init(kv_free, 1);
+    mbar_init(z_full, 1);
+    mbar_init(w_full, 128);
+    mbar_init(acc_done, 1);
+    mbar_init(acc_free, 128);
+    mbar_init(u_done, 1);
+    mbar_init(s_ready, 128);
+    mbar_init(y_done, 1);
+    mbar_init(v_scaled, 128);
+    ab->flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(tmem_base_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 5 && lane == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  const uint32_t tZ = tmem_base;
+  const uint32_t tACC = tmem_base + 128;
+  const uint32_t tS = tmem_base + 256;  // half h at tS + 128 * h
+
+  if (warp == 5) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      bool ok = true;
+      int nq = 0, nkv = 0;  // chunks whose Q / K and V' loads have been issued
+      for (int c = 0; c < nchunk && ok; ++c) {
+        if (c > 0) ok = mbar_wait(q_free, (c - 1) & 1, ab, kRcQFree);
+        if (!ok) break;
+        mbar_expect_tx(q_full, Cfg::QK_BYTES);
+#pragma unroll
+        for (int b = 0; b < KB; ++b) tma_load_3d(sQ + b * BOX, &tmQ, q_full, b * 64, c * 128, bh);
+        ++nq;
+        if (c > 0) ok = mbar_wait(kv_free, (c - 1) & 1, ab, kRcKVFree);
+        if (!ok) break;
+        mbar_expect_tx(k_full, Cfg::QK_BYTES);
+#pragma unroll
+        for (int b = 0; b < KB; ++b) tma_load_3d(sK + b * BOX, &tmK, k_full, b * 64, c * 128, bh);
+        mbar_expect_tx(v_full, Cfg::V_BYTES);
+#pragma unroll
+        for (int b = 0; b < VB; ++b) tma_load_3d(sV + b * BOX, &tmV, v_full, n_off + b * 64, c * 128, bh);
+        ++nkv;
+      }
+      if (!ok) {
+        // abort path: let the copies already issued land before this CTA's shared memory is released
+        if (nq > 0) mbar_wait_drain(q_full, (nq - 1) & 1, 2000000ull);
+        if (nkv > 0) {
+          mbar_wait_drain(k_full, (nkv - 1) & 1, 2000000ull);
+          mbar_wait_drain(v_full, (nkv - 1) & 1, 2000000ull);
+        }
+      }
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------ MMA issuer (converged warp, one elected lane)
+    constexpr uint32_t idesc_z = umma_idesc(128, 128, BF16, false, false);   // Q K^T: both K-major
+    constexpr uint32_t idesc_y = umma_idesc(128, DVC, BF16, false, true);    // Q S, W V: B MN-major
+    constexpr uint32_t idesc_u = umma_idesc(128, DVC, BF16, true, true);     // K^T V: A and B MN-major
+    const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV), sb_addr = smem_u32(sSb);
+    bool ok = true;
+    for (int c = 0; c < nchunk && ok; ++c) {
+      const uint32_t ph = c & 1;
+      ok = mbar_wait_warp(q_full, ph, ab, kRcQ);
+      if (ok) ok = mbar_wait_warp(k_full, ph, ab, kRcK);
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
+#pragma unroll
+        for (int ks = 0; ks < DQK / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * BOX + (ks & 3) * 32;
+          umma_ss(tZ, umma_smem_desc(q_addr + off, 16, 1024), umma_smem_desc(k_addr + off, 16, 1024), idesc_z, ks > 0 ? 1u : 0u);
+        }
+        tc_commit(z_full);
+      }
+      __syncwarp();
+      if (c > 0) {
+        // the carried state: its 16-bit copy is in shared memory and ACC of the previous chunk has been read
+        ok = mbar_wait_warp(s_ready, (c - 1) & 1, ab, kRcState);
+        if (ok) ok = mbar_wait_warp(acc_free, (c - 1) & 1, ab, kRcAccFree);
+        if (!ok) break;
+        tc_fence_after();
+        if (elect_one()) {
+#pragma unroll
+          for (int ks = 0; ks < DQK / 16; ++ks) {
+            const uint32_t qoff = (ks >> 2) * BOX + (ks & 3) * 32;
+            const uint32_t soff = (ks >> 3) * Cfg::SB_HALF_BYTES + (ks & 7) * 2048;
+            umma_ss(tACC, umma_smem_desc(q_addr + qoff, 16, 1024), umma_smem_desc(sb_addr + soff, BOX, 1024), idesc_y,
+                    ks > 0 ? 1u : 0u);
+          }
+          tc_commit(y_done);
+        }
+        __syncwarp();
+      }
+      if (elect_one()) tc_commit(q_free);  // Z and Q S are the only readers of the Q chunk
+      __syncwarp();
+      ok = mbar_wait_warp(v_full, ph, ab, kRcV);
+      if (ok) ok = mbar_wait_warp(w_full, ph, ab, kRcW);
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts(tACC, tZ + ks * 8, umma_smem_desc(v_addr + ks * 2048, BOX, 1024), idesc_y, (c > 0 || ks > 0) ? 1u : 0u);
+        tc_commit(acc_done);
+      }
+      __syncwarp();
+      // state update once the rows of the V tile carry gamma^(127-j): S_h (already multiplied by g) += K_c[:, half h]^T V_c
+      ok = mbar_wait_warp(v_scaled, ph, ab, kRcVScaled);
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_ss(tS + h * 128, umma_smem_desc(k_addr + (2 * h) * BOX + ks * 2048, BOX, 1024),
+                    umma_smem_desc(v_addr + ks * 2048, BOX, 1024), idesc_u, (c > 0 || ks > 0) ? 1u : 0u);
+        }
+        tc_commit(u_done);
+        tc_commit(kv_free);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ element-wise warpgroup
+    const int tid = threadIdx.x;  // 0..127 = TMEM lane = row of the chunk
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32);
+    const int h = bh % p.H;
+    const float lg = log2f(p.decay[h]);
+    const float row_decay = exp2f(tid * lg);                 // gamma^i, row factor of W (columns bring gamma^-j)
+    const float carry = exp2f((tid + 1) * lg);               // gamma^(i+1): the carried state seen from row i
+    const float vrow = exp2f((127 - tid) * lg);              // gamma^(127-j) for row j = tid of the V tile
+    const float g128 = exp2f(128.0f * lg);
+    const uint64_t g2 = f2_pack(g128, g128);
+    const uint64_t carry2 = f2_pack(carry, carry);
+    const uint64_t sc2 = f2_pack(p.scale, p.scale);
+    const uint32_t tz = tmem_addr(tZ, lane_base, 0);
+    const uint32_t ta = tmem_addr(tACC, lane_base, 0);
+    bool ok = true;
+    for (int c = 0; c < nchunk && ok; ++c) {
+      const uint32_t ph = c & 1;
+      // ---- W = Z .* gamma^(i-j), keys after the row's own position removed (the forward flavour of the chain kernels'
+      //      element-wise step: row factor gamma^i, running column factor gamma^-j, triangular predicate)
+      ok = mbar_wait_warp(z_full, ph, ab, kRcZ);
+      if (!ok) break;
+      tc_fence_after();
+      {
+        float unused_sum = 0.f;
+        chain_ew_decay2<kChainFwd, BF16, 0, false>(tz, row_decay, lg, 0.f, 0.f, true, tid, unused_sum);
+        chain_ew_decay2<kChainFwd, BF16, 2, false>(tz, row_decay, lg, 0.f, 0.f, true, tid, unused_sum);
+      }
+      // ---- the carried term Q S, now in ACC, seen from row i: times gamma^(i+1)
+      if (c > 0) {
+        ok = mbar_wait_warp(y_done, (c - 1) & 1, ab, kRcY);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < DVC; c0 += 32) {
+          uint32_t rr[32];
+          tmem_ld32(ta + c0, rr);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float x0, x1;
+            f2_unpack(fmul2(f2_pack(__uint_as_float(rr[i]), __uint_as_float(rr[i + 1])), carry2), x0, x1);
+            rr[i] = __float_as_uint(x0);
+            rr[i + 1] = __float_as_uint(x1);
+          }
+          tmem_st32(ta + c0, rr);
+        }
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(w_full);
+
+      // ---- W V_c has read the plain V tile: scale its rows in place for the state update (row j = tid)
+      ok = mbar_wait_warp(acc_done, ph, ab, kRcAcc);
+      if (ok) ok = mbar_wait_warp(v_full, ph, ab, kRcV);  // long complete; makes the TMA's writes visible to this thread
+      if (!ok) break;
+      tc_fence_after();
+      {
+        const uint64_t vr2 = f2_pack(vrow, vrow);
+#pragma unroll
+        for (int b = 0; b < VB; ++b) {
+          uint4* line = reinterpret_cast<uint4*>(sV + b * BOX + tid * 128);  // the row's 128-byte line of box b
+#pragma unroll
+          for (int q8 = 0; q8 < 8; ++q8) {
+            uint4 u = line[q8];
+            uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float lo, hi;
+              f2_unpack(fmul2(chain_unpack_pair<BF16>(w[e]), vr2), lo, hi);
+              w[e] = pack2<BF16>(lo, hi);
+            }
+            line[q8] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(v_scaled);
+      }
+
+      // ---- O_c = scale * ACC
+      {
+        const int row = c * 128 + tid;
+        uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (static_cast<size_t>(bh) * p.L + row) * p.dv + n_off;
+#pragma unroll
+        for (int c0 = 0; c0 < DVC; c0 += 32) {
+          uint32_t rr[32];
+          tmem_ld32(ta + c0, rr);
+          tc_wait_ld();
+          if (c0 + 32 >= DVC) {
+            tc_fence_before();
+            mbar_arrive(acc_free);
+          }
+          if (row < p.L) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 16) {
+              uint32_t v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                float x0, x1;
+                f2_unpack(fmul2(f2_pack(__uint_as_float(rr[i + 2 * e]), __uint_as_float(rr[i + 2 * e + 1])), sc2), x0, x1);
+                v[e] = pack2<BF16>(x0, x1);
+              }
+              st_global_v8(orow + c0 + i, v);
+            }
+          }
+        }
+      }
+
+      // ---- carried state for the next chunk: 16-bit copy of S into shared memory, S <- g S in tensor memory
+      if (c + 1 < nchunk) {
+        ok = mbar_wait_warp(u_done, ph, ab, kRcU);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int hh = 0; hh < NH; ++hh) {
+          const uint32_t ts = tmem_addr(tS + hh * 128, lane_base, 0);
+          uint8_t* srow = sSb + hh * Cfg::SB_HALF_BYTES + tid * 128;  // row `tid` of every 64-column box
+#pragma unroll
+          for (int c0 = 0; c0 < DVC; c0 += 32) {
+            uint32_t rr[32];
+            tmem_ld32(ts + c0, rr);
+            tc_wait_ld();
+            // 32 columns = four 16-byte groups of the row's 128-byte line in box c0 / 64 (128-byte swizzle)
+            uint8_t* box = srow + (c0 >> 6) * BOX;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 v;
+              v.x = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 0]), __uint_as_float(rr[q4 * 8 + 1]));
+              v.y = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 2]), __uint_as_float(rr[q4 * 8 + 3]));
+              v.z = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 4]), __uint_as_float(rr[q4 * 8 + 5]));
+              v.w = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 6]), __uint_as_float(rr[q4 * 8 + 7]));
+              const int chunk16 = ((c0 & 63) >> 3) + q4;
+              *reinterpret_cast<uint4*>(box + ((chunk16 ^ (tid & 7)) << 4)) = v;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float x0, x1;
+              f2_unpack(fmul2(f2_pack(__uint_as_float(rr[i]), __uint_as_float(rr[i + 1])), g2), x0, x1);
+              rr[i] = __float_as_uint(x0);
+              rr[i + 1] = __float_as_uint(x1);
+            }
+            tmem_st32(ts + c0, rr);
+          }
+        }
+        tc_wait_st();
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(s_ready);
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace ab200

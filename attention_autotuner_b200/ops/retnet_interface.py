@@ -78,6 +78,35 @@ class RetNetAttn(torch.autograd.Function):
         return (dq, dk, dv, None, None) + (None,) * ctx.n_extra
 
 
+def retnet_chunkwise(q, k, v, decay, device_type: Arch = None, scale=None):
+    """Chunkwise (recurrent-state) RetNet forward: o[i] = scale * sum_{j <= i} decay_h^(i-j) (q_i . k_j) v_j, the
+    unnormalised retention of the reference's recurrent kernel (csrc/kernels/retnet/recurrent/recurrent.h:427-463),
+    evaluated chunk by chunk with the state in tensor memory: the cost grows with L, not L^2. Forward only.
+    q, k [B,H,L,dqk] (dqk 128 or 256), v [B,H,L,dv], fp16 or bf16 on one CUDA device; ``decay``: H per-head gammas."""
+    import ctypes
+
+    from .. import _lib
+    check_qkv("retnet_chunkwise", q, k, v)
+    check_mask_decay("retnet_chunkwise", q, k, None, decay)
+    if k.shape[2] != q.shape[2]:
+        raise ValueError(f"retnet_chunkwise: q and k must have the same length, got {q.shape[2]} and {k.shape[2]}")
+    if q.shape[3] not in (128, 256):
+        raise ValueError(f"retnet_chunkwise: head dimension of q/k must be 128 or 256, got {q.shape[3]}")
+    q, k, v = [x.contiguous() for x in [q, k, v]]
+    B, H, L, dqk = q.shape
+    dv = v.shape[3]
+    lib = _lib.load()
+    decayd = decay.detach().to(device=q.device, dtype=torch.float32).contiguous().reshape(-1)
+    o = torch.empty(B, H, L, dv, device=q.device, dtype=q.dtype)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    with torch.cuda.device(q.device):
+        stream = ctypes.c_void_p(torch.cuda.current_stream(q.device).cuda_stream)
+        _lib.check(lib.attn_b200_ret_chunk_fwd(P(q), P(k), P(v), P(decayd), P(o), B, H, L, dqk, dv,
+                                               0 if q.dtype == torch.float16 else 1, 1.0 if scale is None else float(scale),
+                                               stream))
+    return o
+
+
 def RetNetAttnFunc(q, k, v, mask, device_type, causal=False, scale=None, decay=None):
     if scale is None and decay is None:
         if causal is False:

@@ -125,6 +125,20 @@ float attn_b200_ret_bwd_profile(const void* q, const void* k, const void* v, con
                                 void* stream);
 
 /*
+ * Chunkwise (recurrent-state) RetNet forward: the unnormalised retention
+ *     O[i] = scale * sum_{j <= i} gamma_h^(i-j) (q_i . k_j) v_j
+ * evaluated chunk by chunk with a running state, so the work grows with L instead of L^2. Replaces the reference's
+ * retnet_recurrent_fwd (csrc/kernels/retnet/recurrent/recurrent.h:427-463: fp32 tensors laid out [bh, dim, L], a CUB
+ * scan per (k, v) dimension pair, reached from benchmarks/retnet/retnet.cu:175-215) for a per-head constant decay, and
+ * is the "chunkwise retnet" of its to-do list (README.md:103). Tensors use this library's layout and types:
+ *   q, k [B,H,L,dqk]  v, o [B,H,L,dv]  (dtype)   decay: H floats gamma_h in (0, 1] (device)
+ *   dqk in {128, 256}; dv a multiple of 64 up to 512. No normalisation, no r (that is the parallel form's).
+ *   No scratch memory: every decay factor is applied in registers, in tensor memory or in place in shared memory.
+ */
+int attn_b200_ret_chunk_fwd(const void* q, const void* k, const void* v, const float* decay, void* o, int B, int H, int L,
+                            int dqk, int dv, int dtype, float scale, void* stream);
+
+/*
  * Building-block self tests (single CTA, used by the test-suite to pin the tcgen05 / TMA descriptors):
  *   ss: d[128,N] = a[128,K] * b[N,K]^T       K in {64,128,192,256}, N multiple of 32, N*K <= 32768
  *   ts: d[128,N] = p[128,128] * v[128,N]     N in {64,128,192,256}

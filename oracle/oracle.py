@@ -152,6 +152,42 @@ def retnet_bwd_autograd(q, k, v, mask, do, scale: float = 1.0):
     return q.grad, k.grad, v.grad
 
 
+def retnet_recurrent(q, k, v, gammas, scale: float = 1.0):
+    """The recurrent form, position by position, in fp32: state_t = gamma * state_{t-1} + k_t^T v_t (a [dqk, dv] matrix
+    per slice), o_t = scale * q_t state_t. Restates the reference's scan (csrc/kernels/retnet/recurrent/recurrent.h:
+    110-114 combines (decay, k*v) pairs as state = decay * state + k*v; :262-275 multiply the scanned state by q and
+    sum over the k dimension) for a per-head constant decay. No normalisation, no r. q, k [B,H,L,dqk], v [B,H,L,dv],
+    gammas [H]. Parity status of THIS function: unpinned - the reference's kernel cannot be built here and its Python
+    package has no formula for the recurrent form; it is pinned only against retnet_retention below (same
+    function, evaluated over all pairs)."""
+    q, k, v = (t.to(torch.float32) for t in (q, k, v))
+    B, H, L, dqk = q.shape
+    dv = v.shape[-1]
+    g = gammas.to(torch.float32).view(1, H, 1, 1)
+    state = torch.zeros(B, H, dqk, dv)
+    out = torch.empty(B, H, L, dv)
+    for t in range(L):
+        state = g * state + k[:, :, t, :, None] * v[:, :, t, None, :]
+        out[:, :, t] = torch.einsum("bhk,bhkv->bhv", q[:, :, t], state) * scale
+    return out
+
+
+def retnet_retention(q, k, v, gammas, scale: float = 1.0):
+    """The same function over all (i, j) pairs: o = ((q k^T * scale) .* D) v with D[h,i,j] = gamma_h^(i-j) for i >= j.
+    This is retnet_fwd without the division by r (python/utils/ref_op.py:9-12 minus line 11)."""
+    q, k, v = (t.to(torch.float32) for t in (q, k, v))
+    H, L = q.shape[1], q.shape[2]
+    d = decay_mask(H, L, L, gammas)
+    return ((q @ k.transpose(-1, -2)) * scale * d) @ v
+
+
+def flops_ret_chunk(B, H, L, dqk, dv) -> int:
+    """Chunkwise algorithm, chunks of 128: per chunk Q K^T, W V, Q S and K^T V."""
+    nchunk = (L + 127) // 128
+    per_chunk = 2 * 128 * 128 * dqk + 2 * 128 * 128 * dv + 2 * 2 * 128 * dqk * dv
+    return B * H * nchunk * per_chunk
+
+
 # ------------------------------------------------------------------------------------------------
 # FLOP model (algorithmic; recomputation forced by tiling is not counted)
 # ------------------------------------------------------------------------------------------------

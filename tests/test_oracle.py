@@ -102,3 +102,21 @@ def test_slice_inputs_reproducible():
     c = oracle.slice_inputs("C1", 1, 3, 4, 64, 64, 16, 16, torch.float16)
     assert all(torch.equal(x, y) for x, y in zip(a, b))
     assert not torch.equal(a[0], c[0])
+
+
+def test_recurrent_form_equals_the_all_pairs_form():
+    """The position-by-position recurrence (the reference's scan operator, csrc/kernels/retnet/recurrent/recurrent.h:
+    110-114) and the all-pairs evaluation with the decay mask are the same function; where r = 1 it is also what
+    retnet_fwd (pinned to the reference's retnet_ref) returns."""
+    g = torch.Generator().manual_seed(3)
+    B, H, L, dqk, dv = 2, 3, 70, 16, 24
+    q, k, v = (torch.randn(B, H, L, d, generator=g) for d in (dqk, dqk, dv))
+    gam = oracle.decay_gammas(H)
+    a = oracle.retnet_recurrent(q, k, v, gam, 0.3)
+    b = oracle.retnet_retention(q, k, v, gam, 0.3)
+    assert torch.allclose(a, b, atol=1e-4, rtol=1e-5)
+    tiny = 1e-5
+    c, r = oracle.retnet_fwd(q, k, v, oracle.decay_mask(H, L, L, gam), tiny)
+    assert (r == 1).all()
+    assert torch.allclose(c, oracle.retnet_retention(q, k, v, gam, tiny), atol=1e-9, rtol=1e-5)
+    assert oracle.flops_ret_chunk(1, 1, 128, 256, 512) == 2 * 128 * 128 * 256 + 2 * 128 * 128 * 512 + 4 * 128 * 256 * 512
