@@ -61,11 +61,13 @@ int ret_chunk_launch(const RetChunkArgs& a, cudaStream_t stream) {
   return check_launch("ret_chunk_fwd launch");
 }
 
-// Tile choice by head dimensions: 128 columns of V per CTA where dv allows it.
+// Tile choice: 128 columns of V per CTA where dv allows it, 64 when that would leave most SMs without a CTA (a CTA walks
+// its slice sequentially, so the grid BH * dv / DVC is all the parallelism there is).
 template <bool BF16>
 int ret_chunk_dispatch(const RetChunkArgs& a, cudaStream_t stream) {
-  if (a.dqk == 128) return (a.dv % 128 == 0) ? ret_chunk_launch<128, 128, BF16>(a, stream) : ret_chunk_launch<128, 64, BF16>(a, stream);
-  if (a.dqk == 256) return (a.dv % 128 == 0) ? ret_chunk_launch<256, 128, BF16>(a, stream) : ret_chunk_launch<256, 64, BF16>(a, stream);
+  const bool wide = (a.dv % 128 == 0) && (static_cast<long long>(a.BH) * (a.dv / 128) >= 100);
+  if (a.dqk == 128) return wide ? ret_chunk_launch<128, 128, BF16>(a, stream) : ret_chunk_launch<128, 64, BF16>(a, stream);
+  if (a.dqk == 256) return wide ? ret_chunk_launch<256, 128, BF16>(a, stream) : ret_chunk_launch<256, 64, BF16>(a, stream);
   return fail(kErrUnsupported, "ret_chunk_fwd: dqk=%d (the state tile needs 128 or 256)", a.dqk);
 }
 

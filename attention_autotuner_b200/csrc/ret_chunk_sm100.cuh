@@ -161,6 +161,17 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 #pragma unroll
         for (int b = 0; b < VB; ++b) tma_load_3d(sV + b * BOX, &tmV, v_full, n_off + b * 64, c * 128, bh);
         ++nkv;
+        if (c + 1 < nchunk) {
+          // the buffers are single (shared memory is full at dqk = 256), so the next chunk's loads start only when this
+          // chunk's MMAs have released them: ask the L2 for those tiles now, so that they come from L2 rather than HBM
+#pragma unroll
+          for (int b = 0; b < KB; ++b) {
+            tma_prefetch_3d(&tmQ, b * 64, (c + 1) * 128, bh);
+            tma_prefetch_3d(&tmK, b * 64, (c + 1) * 128, bh);
+          }
+#pragma unroll
+          for (int b = 0; b < VB; ++b) tma_prefetch_3d(&tmV, n_off + b * 64, (c + 1) * 128, bh);
+        }
       }
       if (!ok) {
         // abort path: let the copies already issued land before this CTA's shared memory is released

@@ -60,6 +60,9 @@ WORKLOADS = {
     "C2small": (2, 16, 4096, 4096, 128, 128, "fp16", False),
     "C2bwdsmall": (2, 16, 4096, 4096, 128, 128, "fp16", False),
     "C4small": (2, 8, 2048, 2048, 256, 512, "fp16", True),
+    # chunkwise (recurrent-state) RetNet forward: the unnormalised retention, cost linear in L
+    "R3chunk": (8, 8, 2048, 2048, 256, 512, "fp16", True),
+    "R16kchunk": (1, 8, 16384, 16384, 256, 512, "fp16", True),
     # long sequences, bf16, 512 (batch, head) slices split over the ranks
     "C5sq": (16, 32, 16384, 16384, 128, 128, "bf16", False),
     "C5sqcausal": (16, 32, 16384, 16384, 128, 128, "bf16", True),
@@ -69,8 +72,9 @@ METRIC = "attn fwd TFLOPS at B=8,H=16,L=4096,d=128 fp16"
 UNIT = "TFLOP/s"
 ATTN_BWD = ("C2bwd", "C2bwdcausal", "C2bwdsmall")
 RETNET = {"C3": "fwd", "C4": "fwd+bwd", "C3mask": "fwd", "C4mask": "fwd+bwd", "C4small": "fwd+bwd"}
+CHUNKWISE = ("R3chunk", "R16kchunk")
 STRONG = ("C5sq", "C5sqcausal", "C5dec")
-EXTRA_SHORT = ("C2causal", "C2bf16", "C2bf16causal", "C3", "C3mask", "C4", "C4mask", "C2bwd")
+EXTRA_SHORT = ("C2causal", "C2bf16", "C2bf16causal", "C3", "C3mask", "C4", "C4mask", "C2bwd", "R3chunk", "R16kchunk")
 SUSTAINED = ("C2", "C4")
 SEED = 20240229
 # dram__bytes_read.sum + dram__bytes_write.sum per step from the ncu captures summarised under profiles/
@@ -79,6 +83,9 @@ NCU_TRAFFIC_BYTES = {"C2": 515.2e6, "C3": 383.6e6, "C4": 1725.3e6}
 
 
 def metric_name(workload):
+    if workload in CHUNKWISE:
+        B, H, Lq = WORKLOADS[workload][:3]
+        return "RetNet chunkwise fwd TFLOPS at B=%d,H=%d,L=%d,dqk=256,dv=512 fp16 (FLOPs of the chunkwise algorithm)" % (B, H, Lq)
     if workload in RETNET:
         return "RetNet %s TFLOPS at B=%d,H=8,L=2048,dqk=256,dv=512 fp16 (decay mask%s, unmasked pairs counted)" % (
             RETNET[workload], WORKLOADS[workload][0], " as a mask tensor" if workload.endswith("mask") else "")
@@ -91,7 +98,7 @@ def metric_name(workload):
 
 
 def kernel_of(workload):
-    return ("chain_pair_sm100_kernel" if workload in RETNET else
+    return ("ret_chunk_sm100_kernel" if workload in CHUNKWISE else "chain_pair_sm100_kernel" if workload in RETNET else
             "fa_bwd_sm100_kernel" if workload in ATTN_BWD else "fa_fwd_sm100_kernel")
 
 
@@ -107,6 +114,9 @@ def flops_fwd(B, H, Lq, Lkv, dqk, dv, causal):
 def flops_of(workload, n_slices=None):
     """Algorithmic FLOPs of one step over `n_slices` (batch, head) slices (default: the whole batch)."""
     B, H, Lq, Lkv, dqk, dv, dtype, causal = WORKLOADS[workload]
+    if workload in CHUNKWISE:  # per 128-position chunk: Q K^T, W V, Q S, K^T V
+        per_chunk = 2.0 * 128 * 128 * dqk + 2.0 * 128 * 128 * dv + 4.0 * 128 * dqk * dv
+        return (B * H if n_slices is None else n_slices) * ((Lq + 127) // 128) * per_chunk
     f = flops_fwd(1, 1, Lq, Lkv, dqk, dv, causal) * (B * H if n_slices is None else n_slices)
     if RETNET.get(workload) == "fwd+bwd":
         f += f / (dqk + dv) * (3 * dqk + 2 * dv)
@@ -191,8 +201,12 @@ def cpu_reference_run(workload, steps, warmup, budget_s=20.0):
     ret = RETNET.get(workload)
     masks = oracle.decay_mask(H, Lq, Lkv) if ret else None
 
+    gam = oracle.decay_gammas(H)
+
     def run_slice(i, sl):
-        if workload in ATTN_BWD:
+        if workload in CHUNKWISE:  # the same function over all pairs (the reference's recurrent kernel is CUDA only)
+            oracle.retnet_retention(sl[0][None, None], sl[1][None, None], sl[2][None, None], gam[i % H: i % H + 1], scale)
+        elif workload in ATTN_BWD:
             oracle.attention_bwd_autograd(sl[0], sl[1], sl[2], sl[3], scale, causal)
         elif not ret:
             oracle.attention_fwd(sl[0], sl[1], sl[2], scale, causal)
@@ -247,6 +261,7 @@ class Runner:
         self.scale = dqk ** -0.5
         self.sp = ctypes.c_void_p(stream.cuda_stream)
         self.ret = RETNET.get(name)
+        self.chunk = name in CHUNKWISE
         self.bwd = name in ATTN_BWD
         g = torch.Generator(device=dev)
 
@@ -263,7 +278,9 @@ class Runner:
         self.o = torch.empty(B, H, Lq, dv, device=dev, dtype=self.tdt)
         self.launches = 1
         self.mask = self.decay = self.do = None
-        if self.ret:
+        if self.chunk:
+            self.gam = (1.0 - torch.pow(2.0, -5.0 - torch.arange(H, dtype=torch.float64))).float().to(dev)
+        elif self.ret:
             WH = WORKLOADS[name][1]
             self.gam = (1.0 - torch.pow(2.0, -5.0 - torch.arange(WH, dtype=torch.float64))).float().to(dev)
             self.r = torch.empty(B, H, Lq, device=dev, dtype=torch.float32)
@@ -288,7 +305,10 @@ class Runner:
     def step(self):
         B, H, Lq, Lkv, dqk, dv = self.shape
         lib, chk = self.lib, self._lib.check
-        if self.ret:
+        if self.chunk:
+            chk(lib.attn_b200_ret_chunk_fwd(P(self.q), P(self.k), P(self.v), P(self.gam), P(self.o), B, H, Lq, dqk, dv, self.code,
+                                            self.scale, self.sp))
+        elif self.ret:
             chk(lib.attn_b200_ret_fwd(P(self.q), P(self.k), P(self.v), P(self.mask), P(self.o), P(self.r), B, H, Lq, Lkv, dqk,
                                       dv, self.code, self.scale, P(self.decay), 1, self.sp))
             if self.ret != "fwd":
@@ -311,7 +331,10 @@ class Runner:
         from attention_autotuner_b200.ops.attention_interface import flash_attn_func
         from attention_autotuner_b200.ops.retnet_interface import RetNetAttnFunc
         arch = B200()
-        if self.ret:
+        if self.chunk:
+            from attention_autotuner_b200.ops.retnet_interface import retnet_chunkwise
+            retnet_chunkwise(self.q, self.k, self.v, self.gam, arch, scale=self.scale)
+        elif self.ret:
             if self.ret == "fwd":
                 with torch.no_grad():
                     RetNetAttnFunc(self.q, self.k, self.v, self.mask, arch, True, scale=self.scale, decay=self.decay)
@@ -429,7 +452,7 @@ def main():
 
     # ------------------------------------------------------------------ end to end through the public operator
     e2e_ms, e2e_steps = None, 0
-    can_e2e = not args.no_e2e and not run.bwd and run.mask is None
+    can_e2e = not args.no_e2e and not run.bwd and not run.chunk and run.mask is None
     if can_e2e:
         arch = B200()
         qh, kh, vh = (t.cpu().pin_memory() for t in (run.q, run.k, run.v))

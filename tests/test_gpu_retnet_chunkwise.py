@@ -52,6 +52,19 @@ def test_against_the_position_by_position_recurrence(lib, dqk, dv):
     assert (ref - ref2).abs().max().item() < 1e-4 * max(1.0, ref2.abs().max().item())
 
 
+@pytest.mark.parametrize("dqk,dv", [(256, 512), (128, 128)])
+def test_many_slices_take_the_wide_tile(lib, dqk, dv):
+    """With at least a hundred (slice, 128-column) pairs every CTA owns 128 columns of V (fewer pairs: 64, so that
+    more SMs get a CTA); both tiles must give the same function."""
+    B, H, L = 4, 32 if dv == 128 else 8, 300
+    q, k, v = rand(77, B, H, L, dqk, dv)
+    gam = oracle.decay_gammas(H)
+    scale = dqk ** -0.5
+    o = run_chunk(lib, q, k, v, gam, scale)
+    ref = oracle.retnet_retention(q, k, v, gam, scale)
+    assert oracle.report(f"chunkwise wide tile dqk={dqk} dv={dv}", oracle.error_stats(o, ref), "fp16", scale_by_peak=True)
+
+
 @pytest.mark.parametrize("L", [1, 100, 128, 129, 1000, 2048])
 def test_lengths(lib, L):
     H = 2
