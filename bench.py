@@ -74,7 +74,7 @@ ATTN_BWD = ("C2bwd", "C2bwdcausal", "C2bwdsmall")
 RETNET = {"C3": "fwd", "C4": "fwd+bwd", "C3mask": "fwd", "C4mask": "fwd+bwd", "C4small": "fwd+bwd"}
 CHUNKWISE = ("R3chunk", "R16kchunk")
 STRONG = ("C5sq", "C5sqcausal", "C5dec")
-EXTRA_SHORT = ("C2causal", "C2bf16", "C2bf16causal", "C3", "C3mask", "C4", "C4mask", "C2bwd", "R3chunk", "R16kchunk")
+EXTRA_SHORT = ("C4", "C3", "C2causal", "C2bf16", "C2bf16causal", "C3mask", "C4mask", "C2bwd", "R3chunk", "R16kchunk")
 SUSTAINED = ("C2", "C4")
 SEED = 20240229
 # dram__bytes_read.sum + dram__bytes_write.sum per step from the ncu captures summarised under profiles/
@@ -499,14 +499,18 @@ def main():
 
         def short_leg(r: Runner, reps=20):
             """Reference timing method: flush, one event pair per launch, median and p20/p80; C ABI and operator."""
+            smp = ClockSampler(local_rank)
+            if rank == 0:
+                smp.start()
             st = time_launches(r.step, reps=reps, warmup=3, flusher=flusher, stream=stream, budget_ms=400.0)
+            ck = smp.stop() if rank == 0 else None
             op = time_launches(r.op_step, reps=reps, warmup=2, flusher=flusher, stream=stream, budget_ms=400.0)
             ms, op_ms = max_over_ranks(st["median_ms"], op["median_ms"])
             tf = r.flops / (ms * 1e-3) / 1e12
             return {"metric": metric_name(r.name), "ms_per_step": ms, "p20_ms": st["p20_ms"], "p80_ms": st["p80_ms"],
                     "reps": st["reps"], "tflops_per_gpu": tf, "tflops": tf * world, "frac": tf / peak_tf,
                     "op_ms": op_ms, "op_tflops_per_gpu": r.flops / (op_ms * 1e-3) / 1e12,
-                    "launches_per_step": r.launches, "kernel": kernel_of(r.name), "scaling": "weak",
+                    "launches_per_step": r.launches, "kernel": kernel_of(r.name), "scaling": "weak", "clocks": ck,
                     "timing": "256 MB L2 flush before every launch, one CUDA event pair per launch, median"}, \
                 r.launches * (st["reps"] + op["reps"] + 6)
 
@@ -544,11 +548,12 @@ def main():
                     "peak_sustained": peak_sus, "clocks": ck}, r.launches * (n + 3)
 
         # the headline workload with the reference's timing method and through the operator, then its sustained leg
+        # Order: every short leg first (each a fraction of a second, the GPU at its boost clock), the long-sequence legs
+        # next, the two sustained legs last: a 2.5 s run at the power cap leaves the GPU warm and its clock low for a
+        # while, which would otherwise leak into whatever short leg follows it.
         workloads["C2"], nl = short_leg(run)
         gpu_launches += nl
-        workloads["C2"]["sustained"], nl = sustained_leg(run, args.sustained_seconds)
-        gpu_launches += nl
-        check_status("C2 legs")
+        check_status("C2 leg")
     del run
     torch.cuda.empty_cache()
     if extras:
@@ -556,9 +561,6 @@ def main():
             r = Runner(name, dev, lib, stream, rank=rank)
             workloads[name], nl = short_leg(r)
             gpu_launches += nl
-            if name in SUSTAINED:
-                workloads[name]["sustained"], nl = sustained_leg(r, args.sustained_seconds)
-                gpu_launches += nl
             check_status(name)
             del r
             torch.cuda.empty_cache()
@@ -584,6 +586,13 @@ def main():
             workloads[name] = entry
             gpu_launches += r.launches * (st["reps"] + 2)
             check_status(name)
+            del r
+            torch.cuda.empty_cache()
+        for name in SUSTAINED:
+            r = Runner(name, dev, lib, stream, rank=rank)
+            workloads[name]["sustained"], nl = sustained_leg(r, args.sustained_seconds)
+            gpu_launches += nl
+            check_status(name + " sustained")
             del r
             torch.cuda.empty_cache()
         # validation collectives (outside every timed region): scatter a small tensor from rank 0, regenerate the shard

@@ -61,7 +61,7 @@ def test_golden_vectors_of_the_reference_formula(lib, golden, name):
 
 
 def test_config1_full(lib):
-    """BASELINE config 1: B=2 H=4 L=512 d=64 fp16 non-causal scale 1/8, every slice."""
+    """The small benchmark shape B=2 H=4 L=512 d=64 fp16 non-causal scale 1/8, every slice."""
     c = oracle.CONFIGS["C1"]
     qs, ks, vs = [], [], []
     for b in range(c["B"]):
@@ -146,7 +146,7 @@ def test_deterministic_and_linear_in_v(lib):
 
 
 def test_config2_full_size_properties(lib):
-    """BASELINE config 2 at full size (B=8 H=16 L=4096 d=128, fp16 and bf16, causal and not): two sampled
+    """The headline benchmark shape at full size (B=8 H=16 L=4096 d=128, fp16 and bf16, causal and not): two sampled
     (batch, head) slices against the oracle, and softmax rows summing to one (V = ones gives O = 1)."""
     c = oracle.CONFIGS["C2"]
     B, H, L, d = c["B"], c["H"], c["Lq"], c["dqk"]

@@ -176,7 +176,7 @@ def test_unnormalised_scores_above_fp16_range_are_reported_not_silently_clamped(
 
 
 def test_linearity_and_determinism_at_config3_size(lib):
-    """BASELINE config 3/4 at full size (B=8 H=8 L=2048 dqk=256 dv=512 fp16, scale 1/16, decay mask): two runs
+    """The RetNet benchmark shape at full size (B=8 H=8 L=2048 dqk=256 dv=512 fp16, scale 1/16, decay mask): two runs
     bit-identical (no atomics anywhere), O linear in V, sampled slices against the oracle."""
     c = oracle.CONFIGS["C4"]
     B, H, L, dqk, dv = c["B"], c["H"], c["Lq"], c["dqk"], c["dv"]

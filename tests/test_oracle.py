@@ -92,7 +92,7 @@ def test_flop_model():
     assert oracle.pairs(4096, 4096, True) == 4096 * 4097 // 2
     assert oracle.pairs(2, 5, True) == 4 + 5
     assert oracle.flops_ret_bwd(1, 1, 8, 8, 4, 6) == 2 * 64 * (12 + 12)
-    # BASELINE config 2: 1.0995 TFLOP
+    # B=8 H=16 L=4096 d=128 forward: 1.0995 TFLOP
     assert math.isclose(oracle.flops_fwd(8, 16, 4096, 4096, 128, 128), 1.0995e12, rel_tol=1e-3)
 
 
