@@ -292,7 +292,10 @@ def test_host_buffer_operator_matches_the_device_operator():
     ref = flash_attn_func(q.cuda(), k.cuda(), v.cuda(), B200(), True, 0.1).cpu()
     for chunks in (None, 2, 1, 7):
         out = flash_attn_host(q, k, v, B200(), True, 0.1, chunks=chunks)
-        torch.cuda.synchronize()
-        assert torch.equal(out, ref)
+        assert torch.equal(out, ref)          # no device synchronisation here: the call returns complete host results
+    # wait=False hands back the event instead; the result is complete once it has been synchronised
+    out, done = flash_attn_host(q, k, v, B200(), True, 0.1, wait=False)
+    done.synchronize()
+    assert torch.equal(out, ref)
     with pytest.raises(ValueError):
         flash_attn_host(q.cuda(), k, v, B200())

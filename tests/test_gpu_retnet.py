@@ -324,11 +324,9 @@ def test_host_buffer_operator_forward_backward():
     o.backward(do.cuda())
     ref = [t.detach().cpu() for t in (o, qd.grad, kd.grad, vd.grad)]
     got = retnet_host(q, k, v, B200(), decay=gam, causal=True, scale=0.125, dout=do)
-    torch.cuda.synchronize()
-    for a, b in zip(got, ref):
+    for a, b in zip(got, ref):                # no device synchronisation: the results are complete on return
         assert torch.equal(a, b)
     fwd_only = retnet_host(q, k, v, B200(), decay=gam, causal=True, scale=0.125, chunks=2)
-    torch.cuda.synchronize()
     assert torch.equal(fwd_only, ref[0])
     m = oracle.decay_mask(H, L, L, gam)
     oref, _ = oracle.retnet_fwd(q, k, v, m, 0.125)
