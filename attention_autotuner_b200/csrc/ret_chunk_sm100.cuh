@@ -16,18 +16,20 @@
 //     ACC = Q_c S                                 [128 x DVC]   S as 16-bit copy in shared memory (MN-major B operand)
 //     ACC[i] *= gamma^(i+1)                       in tensor memory, by the thread that owns row i
 //     W   = Z .* gamma^(i-j) for j <= i, else 0   fp32 in registers, 16-bit written over Z in tensor memory
+//     K_c[j] *= gamma^(127-j)                     in place in shared memory, once Q K^T has read the plain tile
+//     S   = g S + K_c^T V_c                       fp32 in tensor memory; K_c^T (scaled rows) is the MN-major A operand
 //     ACC += W V_c                                W from tensor memory
 //     O_c = scale * ACC
-//     V_c[j] *= gamma^(127-j)                     in place in shared memory, once W V_c has read the plain tile
-//     S   = g S + K_c^T V_c                       fp32 in tensor memory; K_c^T is the MN-major A operand
 //
 // Every decay factor is applied where its value is at most 1 and in fp32 or on a term whose weight it is: W carries
-// gamma^(i-j) computed in fp32 registers, the carried term is scaled in the fp32 accumulator, and the scaled V rows
-// only feed the state update, where a row that underflows in 16 bits is a contribution that small. So no
+// gamma^(i-j) computed in fp32 registers, the carried term is scaled in the fp32 accumulator, and the scaled K rows
+// only feed the state update, where a row that underflows in 16 bits is a contribution that small. Scaling K (not V)
+// lets the state update start right after Q K^T instead of after W V, so the state copy for the next chunk and the
+// release of the K and V buffers come early and the next chunk's loads run under this chunk's epilogue. So no
 // intermediate exceeds the magnitudes of Q K^T and V whatever gamma in (0, 1] is, and no scratch memory is needed.
 //
 // Roles: warps 0-3 element-wise warpgroup (thread t owns TMEM lane t: a row of Z / ACC, or a row of the state, and
-// row t of the V tile), warp 4 issues every MMA (converged warp, one elected lane; a single issuer keeps all
+// a share of the K tile), warp 4 issues every MMA (converged warp, one elected lane; a single issuer keeps all
 // tensor-memory hazards in program order), warp 5 lane 0 is the TMA producer. Tensor memory: Z at [0,128), ACC at
 // [128,128+DVC), the state halves (dqk rows 0-127, 128-255) at [256,256+DVC) and [384,384+DVC).
 #pragma once
@@ -67,7 +69,7 @@ struct RetChunkConfig {
 
 enum RetChunkTag : int {
   kRcQ = 51, kRcK = 52, kRcV = 53, kRcQFree = 54, kRcKVFree = 55, kRcZ = 56, kRcW = 57, kRcAcc = 58, kRcAccFree = 59,
-  kRcU = 60, kRcState = 61, kRcY = 62, kRcVScaled = 63
+  kRcU = 60, kRcState = 61, kRcY = 62, kRcKScaled = 63
 };
 
 template <class Cfg>
@@ -96,7 +98,7 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint64_t* u_done = bars + 9;     // state update of the chunk complete                (MMA -> element-wise)
   uint64_t* s_ready = bars + 10;   // decayed state in TMEM and its 16-bit copy in smem (element-wise -> MMA), 128 arrivals
   uint64_t* y_done = bars + 11;    // Q S complete                                      (MMA -> element-wise)
-  uint64_t* v_scaled = bars + 12;  // rows of the V tile scaled in place                (element-wise -> MMA), 128 arrivals
+  uint64_t* k_scaled = bars + 12;  // rows of the K tile scaled in place                (element-wise -> MMA), 128 arrivals
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 13);
   CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 1);
 
@@ -119,7 +121,7 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     mbar_init(u_done, 1);
     mbar_init(s_ready, 128);
     mbar_init(y_done, 1);
-    mbar_init(v_scaled, 128);
+    mbar_init(k_scaled, 128);
     ab->flag = 0;
     fence_mbar_init();
   }
@@ -224,19 +226,9 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
       if (elect_one()) tc_commit(q_free);  // Z and Q S are the only readers of the Q chunk
       __syncwarp();
+      // state update as soon as the rows of the K tile carry gamma^(127-j): S_h (already multiplied by g) += K_c[:, half h]^T V_c
       ok = mbar_wait_warp(v_full, ph, ab, kRcV);
-      if (ok) ok = mbar_wait_warp(w_full, ph, ab, kRcW);
-      if (!ok) break;
-      tc_fence_after();
-      if (elect_one()) {
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ts(tACC, tZ + ks * 8, umma_smem_desc(v_addr + ks * 2048, BOX, 1024), idesc_y, (c > 0 || ks > 0) ? 1u : 0u);
-        tc_commit(acc_done);
-      }
-      __syncwarp();
-      // state update once the rows of the V tile carry gamma^(127-j): S_h (already multiplied by g) += K_c[:, half h]^T V_c
-      ok = mbar_wait_warp(v_scaled, ph, ab, kRcVScaled);
+      if (ok) ok = mbar_wait_warp(k_scaled, ph, ab, kRcKScaled);
       if (!ok) break;
       tc_fence_after();
       if (elect_one()) {
@@ -248,6 +240,16 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     umma_smem_desc(v_addr + ks * 2048, BOX, 1024), idesc_u, (c > 0 || ks > 0) ? 1u : 0u);
         }
         tc_commit(u_done);
+      }
+      __syncwarp();
+      ok = mbar_wait_warp(w_full, ph, ab, kRcW);
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts(tACC, tZ + ks * 8, umma_smem_desc(v_addr + ks * 2048, BOX, 1024), idesc_y, (c > 0 || ks > 0) ? 1u : 0u);
+        tc_commit(acc_done);
         tc_commit(kv_free);
       }
       __syncwarp();
@@ -260,7 +262,6 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const float lg = log2f(p.decay[h]);
     const float row_decay = exp2f(tid * lg);                 // gamma^i, row factor of W (columns bring gamma^-j)
     const float carry = exp2f((tid + 1) * lg);               // gamma^(i+1): the carried state seen from row i
-    const float vrow = exp2f((127 - tid) * lg);              // gamma^(127-j) for row j = tid of the V tile
     const float g128 = exp2f(128.0f * lg);
     const uint64_t g2 = f2_pack(g128, g128);
     const uint64_t carry2 = f2_pack(carry, carry);
@@ -273,8 +274,36 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       // ---- W = Z .* gamma^(i-j), keys after the row's own position removed (the forward flavour of the chain kernels'
       //      element-wise step: row factor gamma^i, running column factor gamma^-j, triangular predicate)
       ok = mbar_wait_warp(z_full, ph, ab, kRcZ);
+      if (ok) ok = mbar_wait_warp(k_full, ph, ab, kRcK);  // long complete; makes the TMA's writes visible to this thread
       if (!ok) break;
       tc_fence_after();
+      // ---- Q K^T has read the plain K tile: scale its rows in place for the state update. A row takes one factor, so
+      //      the work is shared by address, not by row: the 32 lanes of a warp cover four consecutive 128-byte lines at a
+      //      time (lane l: line l / 8, 16-byte group l % 8), which is free of bank conflicts; a thread per row would put
+      //      all lanes of a warp on the same banks.
+      {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int krow_idx = warp * 32 + it * 4 + (lane >> 3);
+          const float kf = exp2f((127 - krow_idx) * lg);  // gamma^(127-j)
+          const uint64_t kr2 = f2_pack(kf, kf);
+#pragma unroll
+          for (int b = 0; b < KB; ++b) {
+            uint4* ptr = reinterpret_cast<uint4*>(sK + b * BOX + krow_idx * 128 + (lane & 7) * 16);
+            uint4 u = *ptr;
+            uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float lo, hi;
+              f2_unpack(fmul2(chain_unpack_pair<BF16>(w[e]), kr2), lo, hi);
+              w[e] = pack2<BF16>(lo, hi);
+            }
+            *ptr = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(k_scaled);
+      }
       {
         float unused_sum = 0.f;
         chain_ew_decay2<kChainFwd, BF16, 0, false>(tz, row_decay, lg, 0.f, 0.f, true, tid, unused_sum);
@@ -303,62 +332,6 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(w_full);
-
-      // ---- W V_c has read the plain V tile: scale its rows in place for the state update (row j = tid)
-      ok = mbar_wait_warp(acc_done, ph, ab, kRcAcc);
-      if (ok) ok = mbar_wait_warp(v_full, ph, ab, kRcV);  // long complete; makes the TMA's writes visible to this thread
-      if (!ok) break;
-      tc_fence_after();
-      {
-        const uint64_t vr2 = f2_pack(vrow, vrow);
-#pragma unroll
-        for (int b = 0; b < VB; ++b) {
-          uint4* line = reinterpret_cast<uint4*>(sV + b * BOX + tid * 128);  // the row's 128-byte line of box b
-#pragma unroll
-          for (int q8 = 0; q8 < 8; ++q8) {
-            uint4 u = line[q8];
-            uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float lo, hi;
-              f2_unpack(fmul2(chain_unpack_pair<BF16>(w[e]), vr2), lo, hi);
-              w[e] = pack2<BF16>(lo, hi);
-            }
-            line[q8] = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        }
-        fence_proxy_async_smem();
-        mbar_arrive(v_scaled);
-      }
-
-      // ---- O_c = scale * ACC
-      {
-        const int row = c * 128 + tid;
-        uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (static_cast<size_t>(bh) * p.L + row) * p.dv + n_off;
-#pragma unroll
-        for (int c0 = 0; c0 < DVC; c0 += 32) {
-          uint32_t rr[32];
-          tmem_ld32(ta + c0, rr);
-          tc_wait_ld();
-          if (c0 + 32 >= DVC) {
-            tc_fence_before();
-            mbar_arrive(acc_free);
-          }
-          if (row < p.L) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 16) {
-              uint32_t v[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                float x0, x1;
-                f2_unpack(fmul2(f2_pack(__uint_as_float(rr[i + 2 * e]), __uint_as_float(rr[i + 2 * e + 1])), sc2), x0, x1);
-                v[e] = pack2<BF16>(x0, x1);
-              }
-              st_global_v8(orow + c0 + i, v);
-            }
-          }
-        }
-      }
 
       // ---- carried state for the next chunk: 16-bit copy of S into shared memory, S <- g S in tensor memory
       if (c + 1 < nchunk) {
@@ -401,6 +374,38 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tc_fence_before();
         mbar_arrive(s_ready);
       }
+      // ---- O_c = scale * ACC
+      ok = mbar_wait_warp(acc_done, ph, ab, kRcAcc);
+      if (!ok) break;
+      tc_fence_after();
+      {
+        const int row = c * 128 + tid;
+        uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (static_cast<size_t>(bh) * p.L + row) * p.dv + n_off;
+#pragma unroll
+        for (int c0 = 0; c0 < DVC; c0 += 32) {
+          uint32_t rr[32];
+          tmem_ld32(ta + c0, rr);
+          tc_wait_ld();
+          if (c0 + 32 >= DVC) {
+            tc_fence_before();
+            mbar_arrive(acc_free);
+          }
+          if (row < p.L) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 16) {
+              uint32_t v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                float x0, x1;
+                f2_unpack(fmul2(f2_pack(__uint_as_float(rr[i + 2 * e]), __uint_as_float(rr[i + 2 * e + 1])), sc2), x0, x1);
+                v[e] = pack2<BF16>(x0, x1);
+              }
+              st_global_v8(orow + c0 + i, v);
+            }
+          }
+        }
+      }
+
     }
   }
 
