@@ -48,6 +48,10 @@ def _declare(lib):
     lib.attn_b200_ret_bwd.argtypes = rb
     lib.attn_b200_ret_bwd_profile.restype = cf
     lib.attn_b200_ret_bwd_profile.argtypes = rb
+    lib.attn_b200_ret_bwd_ws.restype = ci
+    lib.attn_b200_ret_bwd_ws.argtypes = [vp] * 10 + [ctypes.c_size_t] + [ci] * 7 + [cf, vp, ci, vp]
+    lib.attn_b200_ret_bwd_workspace_bytes.restype = ctypes.c_size_t
+    lib.attn_b200_ret_bwd_workspace_bytes.argtypes = [ci, ci, ci]
     lib.attn_b200_selftest_gemm_ss.restype = ci
     lib.attn_b200_selftest_gemm_ss.argtypes = [vp, vp, vp, ci, ci, ci, vp]
     lib.attn_b200_selftest_gemm_ts.restype = ci

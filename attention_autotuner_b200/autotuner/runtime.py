@@ -156,7 +156,8 @@ class Runtime:
     def apply(self, torch_array: list, device=None, *, scale=None, causal=False, stream=None, extra_ptrs=(),
               decay=None):
         """Launches the kernel on the tensors in the operation's fixed order
-        (attention: [q,k,v,o]; retnet: [q,k,v,mask,o,r]; retnet bwd: [q,k,v,mask,do,r,dq,dk,dv,dq_accum]).
+        (attention: [q,k,v,o]; retnet: [q,k,v,mask,o,r]; retnet bwd: [q,k,v,mask,do,r,dq,dk,dv,dq_accum], the last one
+        optional scratch of any dtype: with a mask tensor the backward keeps a transposed copy of the mask there).
         scale=None keeps the reference's constants through the legacy ``kernel_entry`` symbol when no other
         option is used. Raises KernelError on a non-zero status."""
         t0 = torch_array[0]
@@ -186,6 +187,10 @@ class Runtime:
                     args.append(ctypes.c_void_p(decay.data_ptr()) if decay is not None else ctypes.c_void_p(0))
                     args.append(ctypes.c_int(1 if causal else 0))
                 args.append(ctypes.c_void_p(stream))
+                if op == "ret_bwd":
+                    # the scratch tensor (the reference's dq_accum slot, last in the array) goes with its size in bytes
+                    acc = torch_array[9] if len(torch_array) > 9 else None
+                    args.append(ctypes.c_size_t(acc.numel() * acc.element_size() if acc is not None else 0))
                 ret = lib.kernel_entry_ex(*args)
         if ret != 0:
             raise KernelError(f"{self.libname}: status {ret}: {lib.last_error().decode()}")

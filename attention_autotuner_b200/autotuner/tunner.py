@@ -193,4 +193,6 @@ class RetBwdTunner(_RetBase):
         return 2.0 * B * H * pairs * (3 * dqk + 2 * dv)
 
     def _profile_args(self):
-        return self._ptrs(10), self._tail()
+        acc = self.torch_array[9] if len(self.torch_array) > 9 else None
+        nbytes = acc.numel() * acc.element_size() if acc is not None else 0
+        return self._ptrs(10), self._tail() + [ctypes.c_size_t(nbytes)]  # the scratch tensor's size in bytes comes last

@@ -114,8 +114,10 @@ int ret_common(bool bwd, const RetArgs& a, int dtype, void* stream, bool profile
 
 RetArgs ret_args(const void* q, const void* k, const void* v, const void* mask, const float* decay, void* o, float* r,
                  const void* dout, void* dq, void* dk, void* dv_out, int B, int H, int Lq, int Lkv, int dqk, int dv,
-                 float scale, int causal) {
+                 float scale, int causal, void* workspace = nullptr, size_t workspace_bytes = 0) {
   RetArgs a{};
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
   a.q = q; a.k = k; a.v = v; a.mask = mask; a.decay = decay; a.o = o; a.r = r;
   a.dout = dout; a.dq = dq; a.dk = dk; a.dv_out = dv_out;
   a.BH = B * H; a.H = H; a.Lq = Lq; a.Lkv = Lkv; a.dqk = dqk; a.dv = dv; a.scale = scale; a.causal = causal;
@@ -180,24 +182,43 @@ float attn_b200_ret_fwd_profile(const void* q, const void* k, const void* v, con
   return rc == kOk ? ms : -1.f;
 }
 
+// Size of the reference's dq_accum tensor (fp32 [B, H, Lq, dqk]): what a caller of the reference's ABI hands over.
+static size_t dq_accum_bytes(const void* dq_accum, int B, int H, int Lq, int dqk) {
+  if (dq_accum == nullptr || B <= 0 || H <= 0 || Lq <= 0 || dqk <= 0) return 0;
+  return static_cast<size_t>(B) * H * Lq * dqk * sizeof(float);
+}
+
+int attn_b200_ret_bwd_ws(const void* q, const void* k, const void* v, const void* mask, const void* dout, const float* r,
+                         void* dq, void* dk, void* dv_out, void* workspace, size_t workspace_bytes, int B, int H, int Lq,
+                         int Lkv, int dqk, int dv, int dtype, float scale, const float* decay, int causal, void* stream) {
+  if (B <= 0 || H <= 0) return fail(kErrInvalidArgument, "ret_bwd: B and H must be positive");
+  return ret_common(true, ret_args(q, k, v, mask, decay, nullptr, const_cast<float*>(r), dout, dq, dk, dv_out, B, H, Lq,
+                                   Lkv, dqk, dv, scale, causal, workspace, workspace_bytes), dtype, stream, false, nullptr);
+}
+
+size_t attn_b200_ret_bwd_workspace_bytes(int H, int Lq, int Lkv) {
+  if (H <= 0 || Lq <= 0 || Lkv <= 0) return 0;
+  return static_cast<size_t>(H) * Lq * Lkv * 2u;
+}
+
 int attn_b200_ret_bwd(const void* q, const void* k, const void* v, const void* mask, const void* dout, const float* r,
                       void* dq, void* dk, void* dv_out, float* dq_accum, int B, int H, int Lq, int Lkv, int dqk, int dv,
                       int dtype, float scale, const float* decay, int causal, void* stream) {
-  (void)dq_accum;  // accepted for signature compatibility; the kernels need no scratch
-  if (B <= 0 || H <= 0) return fail(kErrInvalidArgument, "ret_bwd: B and H must be positive");
-  return ret_common(true, ret_args(q, k, v, mask, decay, nullptr, const_cast<float*>(r), dout, dq, dk, dv_out, B, H, Lq,
-                                   Lkv, dqk, dv, scale, causal), dtype, stream, false, nullptr);
+  // dq_accum is scratch in the reference's ABI (fp32 [B, H, Lq, dqk], python/ops/retnet_interface.py:48-54); here it
+  // is scratch too: room for a transposed copy of the mask when it is large enough, unused otherwise
+  return attn_b200_ret_bwd_ws(q, k, v, mask, dout, r, dq, dk, dv_out, dq_accum, dq_accum_bytes(dq_accum, B, H, Lq, dqk), B, H,
+                              Lq, Lkv, dqk, dv, dtype, scale, decay, causal, stream);
 }
 
 float attn_b200_ret_bwd_profile(const void* q, const void* k, const void* v, const void* mask, const void* dout,
                                 const float* r, void* dq, void* dk, void* dv_out, float* dq_accum, int B, int H, int Lq,
                                 int Lkv, int dqk, int dv, int dtype, float scale, const float* decay, int causal,
                                 void* stream) {
-  (void)dq_accum;
   float ms = -1.f;
   if (B <= 0 || H <= 0) return -1.f;
   int rc = ret_common(true, ret_args(q, k, v, mask, decay, nullptr, const_cast<float*>(r), dout, dq, dk, dv_out, B, H,
-                                     Lq, Lkv, dqk, dv, scale, causal), dtype, stream, true, &ms);
+                                     Lq, Lkv, dqk, dv, scale, causal, dq_accum, dq_accum_bytes(dq_accum, B, H, Lq, dqk)),
+                      dtype, stream, true, &ms);
   return rc == kOk ? ms : -1.f;
 }
 

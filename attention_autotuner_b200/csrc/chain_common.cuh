@@ -16,6 +16,7 @@ struct ChainParams {
   float* r_out;          // Fwd: [BH, Lq] normaliser r = max(sum_j |S~|, 1), written by z == 0
   const float* r_in;     // RowQ / RowK: [BH, Lq]
   const uint16_t* mask;  // general mask [H, Lq, Lkv] (16-bit, same dtype as the operands) or nullptr
+  const uint16_t* mask_t;  // RowK flavours only: transposed copy [H, Lkv, Lq] of the mask in scratch memory, or nullptr
   const float* decay;    // per-head gamma [H] or nullptr (exactly one of mask / decay is set)
   int H, Lq, Lkv;
   float scale;
@@ -173,6 +174,43 @@ __device__ __forceinline__ void chain_mask_prefetch(const ChainParams& p, int h,
     mk[4 * v8 + 1] = u.y;
     mk[4 * v8 + 2] = u.z;
     mk[4 * v8 + 3] = u.w;
+  }
+}
+
+//   RowK with a transposed copy of the mask (mask_t[h][key][query], made once per backward call in scratch memory by
+//   mask_transpose_kernel): the thread's column of the mask is a row of the copy, read like the Fwd / RowQ rows.
+template <int QD0>
+__device__ __forceinline__ void chain_mask_prefetch_t(const ChainParams& p, int h, int key, int col0, uint32_t (&mk)[32]) {
+  const uint16_t* mp = p.mask_t + (static_cast<size_t>(h) * p.Lkv + key) * p.Lq + col0 + QD0 * 32;
+#pragma unroll
+  for (int v8 = 0; v8 < 8; ++v8) {
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (key < p.Lkv && col0 + QD0 * 32 + v8 * 8 < p.Lq) u = __ldg(reinterpret_cast<const uint4*>(mp) + v8);
+    mk[4 * v8 + 0] = u.x;
+    mk[4 * v8 + 1] = u.y;
+    mk[4 * v8 + 2] = u.z;
+    mk[4 * v8 + 3] = u.w;
+  }
+}
+
+// out[h][j][i] = in[h][i][j] for a 16-bit tensor in [H, rows, cols]: 32 x 32 tiles through shared memory (padded rows,
+// no bank conflicts), coalesced on both sides. grid = (ceil(cols / 32), ceil(rows / 32), H), block = (32, 8).
+__global__ void mask_transpose_kernel(const uint16_t* __restrict__ in, uint16_t* __restrict__ out, int rows, int cols) {
+  __shared__ uint16_t tile[32][34];
+  const size_t plane = static_cast<size_t>(rows) * cols;
+  const uint16_t* src = in + blockIdx.z * plane;
+  uint16_t* dst = out + blockIdx.z * plane;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+#pragma unroll
+  for (int i = threadIdx.y; i < 32; i += 8) {
+    const int r = r0 + i, c = c0 + threadIdx.x;
+    tile[i][threadIdx.x] = (r < rows && c < cols) ? src[static_cast<size_t>(r) * cols + c] : uint16_t(0);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = threadIdx.y; i < 32; i += 8) {
+    const int c = c0 + i, r = r0 + threadIdx.x;  // out row = in column
+    if (c < cols && r < rows) dst[static_cast<size_t>(c) * rows + r] = tile[threadIdx.x][i];
   }
 }
 

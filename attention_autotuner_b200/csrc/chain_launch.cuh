@@ -28,6 +28,10 @@ struct RetArgs {
   void* dq;          // [BH, Lq, dqk]
   void* dk;          // [BH, Lkv, dqk]
   void* dv_out;      // [BH, Lkv, dv]
+  // backward with a mask tensor: optional scratch for a transposed copy of the mask (H * Lq * Lkv 16-bit values,
+  // 16-byte aligned); nullptr or too small: the kernels read columns of the mask and transpose them in registers
+  void* workspace;
+  size_t workspace_bytes;
   int BH, H, Lq, Lkv, dqk, dv;
   float scale;
   int causal;        // with a general mask: 1 = mask is lower triangular, skip the blocks above the diagonal
@@ -210,16 +214,31 @@ int ret_bwd_launch(const RetArgs& a, cudaStream_t stream) {
   static_assert(DV % DVC == 0 && DQK % DQC == 0, "chunking");
   ChainParams p = ret_params(a);
   p.r_in = a.r;
+  // Mask tensor: the dV and dK kernels own keys and need columns of M[h][query][key]. With scratch memory at hand the
+  // mask is transposed once per call (one coalesced pass over H * Lq * Lkv values) and those kernels read rows of the
+  // copy with 16-byte loads; without it every warp reads 32 x 32 tiles by rows and transposes them in registers
+  // (three shuffle rounds per 8 x 8 block, on the element-wise warps' critical path).
+  const size_t mask_bytes = static_cast<size_t>(a.H) * a.Lq * a.Lkv * 2u;
+  const uint16_t* mask_t = nullptr;
+  if (a.mask && a.workspace && aligned16(a.workspace) && a.workspace_bytes >= mask_bytes && a.Lq % 8 == 0) {
+    dim3 tgrid((a.Lkv + 31) / 32, (a.Lq + 31) / 32, a.H);
+    mask_transpose_kernel<<<tgrid, dim3(32, 8, 1), 0, stream>>>(reinterpret_cast<const uint16_t*>(a.mask),
+                                                              reinterpret_cast<uint16_t*>(a.workspace), a.Lq, a.Lkv);
+    if ((rc = check_launch("ret_bwd mask transpose"))) return rc;
+    mask_t = reinterpret_cast<const uint16_t*>(a.workspace);
+  }
   auto go = [&](auto general_tag) -> int {
     constexpr bool G = decltype(general_tag)::value;
     ChainParams pv = p;
     pv.out = a.dv_out;
     pv.ld_out = a.dv;
+    pv.mask_t = mask_t;
     int r1 = chain_go<PAIR, DQK, DVC, kChainRowK, G, BF16>(a.k, a.Lkv, a.q, a.Lq, a.dout, a.dv, pv, a.BH, stream, "ret_bwd dV");
     if (r1) return r1;
     ChainParams pk = p;
     pk.out = a.dk;
     pk.ld_out = a.dqk;
+    pk.mask_t = mask_t;
     r1 = chain_go<PAIR, DV, DQC, kChainRowK, G, BF16>(a.v, a.Lkv, a.dout, a.Lq, a.q, a.dqk, pk, a.BH, stream, "ret_bwd dK", true);
     if (r1) return r1;
     ChainParams pq = p;

@@ -453,8 +453,14 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
           else chain_mask_prefetch<MODE, 2>(p, h, grow, col0, mk);
         } else if constexpr (GENERAL) {
           // RowK: the thread's column of the mask, read by rows by the whole warp and transposed in registers
-          if (hh == 0) chain_mask_prefetch_rowk<0>(p, h, grow - lane, lane, col0, mk);
-          else chain_mask_prefetch_rowk<2>(p, h, grow - lane, lane, col0, mk);
+          if (p.mask_t != nullptr) {  // a transposed copy of the mask exists: the thread's column is a row of it
+            if (hh == 0) chain_mask_prefetch_t<0>(p, h, grow, col0, mk);
+            else chain_mask_prefetch_t<2>(p, h, grow, col0, mk);
+          } else if (hh == 0) {
+            chain_mask_prefetch_rowk<0>(p, h, grow - lane, lane, col0, mk);
+          } else {
+            chain_mask_prefetch_rowk<2>(p, h, grow - lane, lane, col0, mk);
+          }
         }
         float rowf = rowf_base;
         if (decay_mode) rowf *= exp2f((MODE == kChainRowK ? (col0 - row0) : (row0 - col0)) * lg);

@@ -446,8 +446,13 @@ chain_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_constan
         chain_mask_prefetch<MODE, 0>(p, h, grow, col0, mk0);
         chain_mask_prefetch<MODE, 2>(p, h, grow, col0, mk1);
       } else if constexpr (GENERAL) {
-        chain_mask_prefetch_rowk<0>(p, h, grow - lane, lane, col0, mk0);
-        chain_mask_prefetch_rowk<2>(p, h, grow - lane, lane, col0, mk1);
+        if (p.mask_t != nullptr) {  // a transposed copy of the mask exists: the thread's column is a row of it
+          chain_mask_prefetch_t<0>(p, h, grow, col0, mk0);
+          chain_mask_prefetch_t<2>(p, h, grow, col0, mk1);
+        } else {
+          chain_mask_prefetch_rowk<0>(p, h, grow - lane, lane, col0, mk0);
+          chain_mask_prefetch_rowk<2>(p, h, grow - lane, lane, col0, mk1);
+        }
       }
       float rowf = rowf_base;
       if (decay_mode) rowf *= exp2f((MODE == kChainRowK ? (col0 - row0) : (row0 - col0)) * lg);

@@ -49,7 +49,13 @@ def retnet_backward(q, k, v, mask, do, r, device_type: Arch, causal=False, scale
     dq = torch.empty_like(q)
     dk = torch.empty_like(k)
     dv = torch.empty_like(v)
-    arr = [q, k, v, mask, do, r, dq, dk, dv, None]  # no dq_accum scratch: each output tile has one owner
+    # The last slot is the reference's dq_accum scratch (python/ops/retnet_interface.py:48-54). Nothing is accumulated
+    # in it here (each output tile has one owner); with a mask tensor it gives the dV / dK kernels room for a transposed
+    # copy of the mask (H * Lq * Lkv values), which they read by rows instead of transposing columns in registers.
+    scratch = None
+    if mask is not None and q.shape[2] % 8 == 0:
+        scratch = torch.empty(mask.shape[0] * q.shape[2] * k.shape[2], dtype=q.dtype, device=q.device)
+    arr = [q, k, v, mask, do, r, dq, dk, dv, scratch]
     cc = RetBwdTunner(arch=device_type, torch_array=arr, scale=scale, causal=causal, decay=decay).tune()
     Runtime(device_type, cc).apply(arr, scale=1.0 if scale is None else scale, causal=causal, decay=decay)
     return dq, dk, dv

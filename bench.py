@@ -287,7 +287,10 @@ class Runner:
             self.do = gen(Lq, dv, 4)
             self.dq, self.dk, self.dvo = torch.empty_like(self.q), torch.empty_like(self.k), torch.empty_like(self.v)
             self.launches = 1 if self.ret == "fwd" else 4
+            self.dq_accum = None
             if name.endswith("mask"):
+                # the reference's call form passes a pre-zeroed fp32 dq_accum of this shape; here it is scratch
+                self.dq_accum = torch.zeros(B, H, Lq, dqk, device=dev, dtype=torch.float32)
                 idx = torch.arange(Lq, device=dev, dtype=torch.float64)
                 diff = idx[:, None] - torch.arange(Lkv, device=dev, dtype=torch.float64)[None, :]
                 self.mask = torch.where(diff >= 0, self.gam.double()[:, None, None] ** diff.clamp(min=0),
@@ -313,7 +316,7 @@ class Runner:
                                       dv, self.code, self.scale, P(self.decay), 1, self.sp))
             if self.ret != "fwd":
                 chk(lib.attn_b200_ret_bwd(P(self.q), P(self.k), P(self.v), P(self.mask), P(self.do), P(self.r), P(self.dq),
-                                          P(self.dk), P(self.dvo), None, B, H, Lq, Lkv, dqk, dv, self.code, self.scale,
+                                          P(self.dk), P(self.dvo), P(self.dq_accum), B, H, Lq, Lkv, dqk, dv, self.code, self.scale,
                                           P(self.decay), 1, self.sp))
         elif self.bwd:
             chk(lib.attn_b200_fa_fwd(P(self.q), P(self.k), P(self.v), P(self.o), P(self.lse), B, H, Lq, Lkv, dqk, dv, self.code,

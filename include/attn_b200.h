@@ -23,6 +23,8 @@
 #ifndef ATTN_B200_H_
 #define ATTN_B200_H_
 
+#include <stddef.h>
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -111,10 +113,14 @@ float attn_b200_ret_fwd_profile(const void* q, const void* k, const void* v, con
  *   P = S~ / r,  dV = P^T dO,  G = ((dO V^T) / r) .* M * scale,  dK = G^T Q,  dQ = G K.
  * Replaces python/ops/retnet_interface.py:36-55 -> kernel_entry -> ret_bwd_colblock + convert_dq
  * (csrc/kernels/retnet/bwd/bwd_colblock.h:81, 742). Tensor order follows the reference's
- * [q,k,v,mask,do,r,dq,dk,dv,dq_accum]; dq_accum (fp32 [B,H,Lq,dqk] in the reference) is accepted and
- * ignored, may be NULL: every output tile is owned by one CTA, nothing is accumulated with atomics.
+ * [q,k,v,mask,do,r,dq,dk,dv,dq_accum]. Every output tile is owned by one CTA: nothing is accumulated with atomics.
  *   dout [B,H,Lq,dv]  r [B,H,Lq] (from the forward)  dq [B,H,Lq,dqk]  dk [B,H,Lkv,dqk]  dv_out [B,H,Lkv,dv]
  * Outputs are fully overwritten.
+ *   dq_accum: scratch of the reference's shape (fp32 [B,H,Lq,dqk]) or NULL. The reference accumulates dQ in it; here it is
+ *   scratch for something else: with a mask TENSOR, the kernels that own keys (dV, dK) need columns of M[h][query][key], and
+ *   when dq_accum is given, holds at least H*Lq*Lkv 16-bit values (2*B*dqk >= Lkv) and Lq % 8 == 0, the mask is
+ *   transposed into it once per call and read by rows; otherwise the columns are read and transposed in registers
+ *   (same results, slower). Its contents are undefined after the call. Ignored with `decay`.
  */
 int attn_b200_ret_bwd(const void* q, const void* k, const void* v, const void* mask, const void* dout, const float* r,
                       void* dq, void* dk, void* dv_out, float* dq_accum, int B, int H, int Lq, int Lkv, int dqk, int dv,
@@ -123,6 +129,15 @@ float attn_b200_ret_bwd_profile(const void* q, const void* k, const void* v, con
                                 const float* r, void* dq, void* dk, void* dv_out, float* dq_accum, int B, int H, int Lq,
                                 int Lkv, int dqk, int dv, int dtype, float scale, const float* decay, int causal,
                                 void* stream);
+
+/* The same backward with the scratch given explicitly: `workspace` (device memory, 16-byte aligned, owned by the caller)
+ * of `workspace_bytes` bytes; attn_b200_ret_bwd_workspace_bytes(H, Lq, Lkv) = H*Lq*Lkv*2 is what the transposed copy of
+ * a mask tensor needs. NULL or too small: the slower in-register path. No counterpart in the reference (its scratch
+ * is the dq_accum argument above). */
+size_t attn_b200_ret_bwd_workspace_bytes(int H, int Lq, int Lkv);
+int attn_b200_ret_bwd_ws(const void* q, const void* k, const void* v, const void* mask, const void* dout, const float* r,
+                         void* dq, void* dk, void* dv_out, void* workspace, size_t workspace_bytes, int B, int H, int Lq,
+                         int Lkv, int dqk, int dv, int dtype, float scale, const float* decay, int causal, void* stream);
 
 /*
  * Chunkwise (recurrent-state) RetNet forward: the unnormalised retention
@@ -199,7 +214,7 @@ typedef float (*attn_b200_ret_profile_ex_t)(const void* q, const void* k, const 
                                             void* stream);
 
 /* operation "ret_bwd" (reference: csrc/kernels/retnet/bwd/profile_code.py:50 profile, :98 kernel_entry); dqaccum is
- * accepted and ignored, may be NULL */
+ * scratch of the reference's shape or NULL (see attn_b200_ret_bwd); the _ex forms take its size in bytes last */
 typedef int (*attn_b200_ret_bwd_kernel_entry_t)(void* q, void* k, void* v, void* mask, void* dout, float* r, void* dq,
                                                 void* dk, void* dv, float* dqaccum, int B, int H, int Seq_k, int Seq_q);
 typedef float (*attn_b200_ret_bwd_profile_t)(void* q, void* k, void* v, void* mask, void* dout, float* r, void* dq, void* dk,
@@ -207,11 +222,11 @@ typedef float (*attn_b200_ret_bwd_profile_t)(void* q, void* k, void* v, void* ma
 typedef int (*attn_b200_ret_bwd_kernel_entry_ex_t)(const void* q, const void* k, const void* v, const void* mask,
                                                    const void* dout, const float* r, void* dq, void* dk, void* dv,
                                                    float* dqaccum, int B, int H, int Seq_k, int Seq_q, float scale,
-                                                   const float* decay, int causal, void* stream);
+                                                   const float* decay, int causal, void* stream, size_t dqaccum_bytes);
 typedef float (*attn_b200_ret_bwd_profile_ex_t)(const void* q, const void* k, const void* v, const void* mask,
                                                 const void* dout, const float* r, void* dq, void* dk, void* dv,
                                                 float* dqaccum, int B, int H, int Seq_q, int Seq_k, float scale,
-                                                const float* decay, int causal, void* stream);
+                                                const float* decay, int causal, void* stream, size_t dqaccum_bytes);
 
 #ifdef __cplusplus
 }

@@ -248,6 +248,48 @@ def test_config4_every_slice_against_the_oracle(lib, form):
     assert oracle.within(worst["o"], "fp16", scale_by_peak=False), worst["o"]
 
 
+@pytest.mark.parametrize("Lq,Lkv,dqk,dv", [(512, 512, 128, 128), (200, 328, 64, 128), (456, 456, 256, 512), (136, 640, 64, 64)])
+def test_backward_with_scratch_for_the_transposed_mask(lib, Lq, Lkv, dqk, dv):
+    """With a mask tensor the kernels that own keys (dV, dK) need columns of the mask. Given scratch memory
+    (attn_b200_ret_bwd_ws, or the reference's dq_accum slot of attn_b200_ret_bwd when it is large enough) the mask is
+    transposed once and read by rows; without it the columns are transposed in registers. Same bits either way, and
+    right against the oracle."""
+    B, H = 2, 2
+    q, k, v, do, mask = rand_case(Lq + Lkv + dqk, B, H, Lq, Lkv, dqk, dv)
+    base = run_fwd_bwd(lib, q, k, v, do, mask=mask, scale=0.2)            # no scratch
+    check_all(base, q, k, v, do, mask.float(), 0.2)
+    qd, kd, vd, dod, md, rd = q.cuda(), k.cuda(), v.cuda(), do.cuda(), mask.cuda(), base[1].cuda()
+    need = lib.attn_b200_ret_bwd_workspace_bytes(H, Lq, Lkv)
+    assert need == H * Lq * Lkv * 2
+    outs = []
+    for mode in ("ws", "dq_accum"):
+        dq = torch.full((B, H, Lq, dqk), float("nan"), device="cuda", dtype=torch.float16)
+        dk = torch.full((B, H, Lkv, dqk), float("nan"), device="cuda", dtype=torch.float16)
+        dvo = torch.full((B, H, Lkv, dv), float("nan"), device="cuda", dtype=torch.float16)
+        if mode == "ws":
+            ws = torch.empty(need + 64, dtype=torch.uint8, device="cuda")
+            _lib.check(lib.attn_b200_ret_bwd_ws(P(qd), P(kd), P(vd), P(md), P(dod), P(rd), P(dq), P(dk), P(dvo), P(ws), ws.numel(),
+                                                B, H, Lq, Lkv, dqk, dv, 0, 0.2, None, 0, None))
+        else:  # the reference's call form: a pre-zeroed fp32 [B, H, Lq, dqk] tensor (large enough only when 2*B*dqk >= Lkv)
+            acc = torch.zeros(B, H, Lq, dqk, device="cuda", dtype=torch.float32)
+            _lib.check(lib.attn_b200_ret_bwd(P(qd), P(kd), P(vd), P(md), P(dod), P(rd), P(dq), P(dk), P(dvo), P(acc), B, H, Lq, Lkv,
+                                             dqk, dv, 0, 0.2, None, 0, None))
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0
+        outs.append((dq.cpu(), dk.cpu(), dvo.cpu()))
+    for got in outs:
+        for a, b in zip(got, base[2:]):
+            assert torch.equal(a, b)
+    # a workspace that is too small is simply not used
+    small = torch.empty(64, dtype=torch.uint8, device="cuda")
+    dq = torch.empty(B, H, Lq, dqk, device="cuda", dtype=torch.float16)
+    dk, dvo = torch.empty_like(kd), torch.empty_like(vd)
+    _lib.check(lib.attn_b200_ret_bwd_ws(P(qd), P(kd), P(vd), P(md), P(dod), P(rd), P(dq), P(dk), P(dvo), P(small), 64, B, H, Lq, Lkv,
+                                        dqk, dv, 0, 0.2, None, 0, None))
+    torch.cuda.synchronize()
+    assert torch.equal(dq.cpu(), base[2]) and torch.equal(dk.cpu(), base[3])
+
+
 def test_python_operator_forward_backward(lib):
     from attention_autotuner_b200.ops.retnet_interface import RetNetAttnFunc
     q, k, v, do, mask = rand_case(17, 2, 2, 256, 256, 64, 64)
