@@ -50,6 +50,10 @@ def _declare(lib):
     lib.attn_b200_ret_bwd_profile.argtypes = rb
     lib.attn_b200_ret_bwd_ws.restype = ci
     lib.attn_b200_ret_bwd_ws.argtypes = [vp] * 10 + [ctypes.c_size_t] + [ci] * 7 + [cf, vp, ci, vp]
+    lib.attn_b200_ret_bwd_noalloc.restype = ci
+    lib.attn_b200_ret_bwd_noalloc.argtypes = [vp] * 9 + [ci] * 7 + [cf, vp, ci, vp]
+    lib.attn_b200_ret_bwd_noalloc_max_bytes.restype = ctypes.c_size_t
+    lib.attn_b200_ret_bwd_noalloc_max_bytes.argtypes = []
     lib.attn_b200_ret_bwd_workspace_bytes.restype = ctypes.c_size_t
     lib.attn_b200_ret_bwd_workspace_bytes.argtypes = [ci, ci, ci]
     lib.attn_b200_selftest_gemm_ss.restype = ci

@@ -4,6 +4,8 @@
 // kernel headers.
 #include "../../include/attn_b200.h"
 
+#include <mutex>
+
 #include "chain_launch.cuh"
 #include "fa_bwd_launch.cuh"
 #include "fa_fwd_launch.cuh"
@@ -13,7 +15,40 @@
 
 using namespace ab200;
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Scratch of attn_b200_ret_bwd_noalloc: device memory that belongs to the library itself, for callers that cannot
+// hand over a workspace and must not cause an allocation. A file-scope array: every device that loads this library
+// holds these bytes from the moment the module is loaded until the process exits. In host code the NAME of the array is
+// only a stand-in for the symbol; the address a kernel can use comes from cudaGetSymbolAddress (noalloc_scratch below).
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr size_t kNoAllocScratchBytes = 32u << 20;  // 32 MiB: a transposed 16-bit mask of up to 16 Mi elements (H * Lq * Lkv)
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
 namespace {
+
+// Device address of g_noalloc_scratch on the calling thread's current device. Looked up once per device, with that
+// device current (the first call of attn_b200_ret_bwd_noalloc on a device does it, which also binds the device's
+// context to the thread), and remembered.
+int noalloc_scratch(void** out) {
+  constexpr int kMaxDevices = 64;
+  static void* table[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return fail(kErrCuda, "ret_bwd_noalloc: no usable current device");
+  std::lock_guard<std::mutex> lock(mu);
+  if (table[dev] == nullptr) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      (void)cudaGetLastError();
+      return fail(kErrCuda, "ret_bwd_noalloc: cudaGetSymbolAddress(scratch) on device %d: %s", dev, cudaGetErrorString(e));
+    }
+    table[dev] = ptr;
+  }
+  *out = table[dev];
+  return kOk;
+}
 
 // Default flash-attention tiles per (dqk, dv-chunk): two ping-ponging query tiles when tensor memory
 // and shared memory allow it, otherwise one.
@@ -220,6 +255,26 @@ float attn_b200_ret_bwd_profile(const void* q, const void* k, const void* v, con
                                      Lq, Lkv, dqk, dv, scale, causal, dq_accum, dq_accum_bytes(dq_accum, B, H, Lq, dqk)),
                       dtype, stream, true, &ms);
   return rc == kOk ? ms : -1.f;
+}
+
+size_t attn_b200_ret_bwd_noalloc_max_bytes(void) { return kNoAllocScratchBytes; }
+
+int attn_b200_ret_bwd_noalloc(const void* q, const void* k, const void* v, const void* mask, const void* dout, const float* r,
+                              void* dq, void* dk, void* dv_out, int B, int H, int Lq, int Lkv, int dqk, int dv, int dtype,
+                              float scale, const float* decay, int causal, void* stream) {
+  if (B <= 0 || H <= 0 || Lq <= 0 || Lkv <= 0) return fail(kErrInvalidArgument, "ret_bwd_noalloc: sizes must be positive");
+  // the only scratch the backward uses is the transposed copy of a mask tensor; it has to fit the library's own array
+  const size_t need = mask != nullptr ? static_cast<size_t>(H) * Lq * Lkv * 2u : 0;
+  if (need > kNoAllocScratchBytes)
+    return fail(kErrInvalidArgument,
+                "ret_bwd_noalloc: the mask needs %zu bytes of scratch (H * Lq * Lkv * 2) but this entry point holds %zu "
+                "(H * Lq * Lkv <= %zu); call attn_b200_ret_bwd_ws with a workspace of your own for larger masks",
+                need, kNoAllocScratchBytes, kNoAllocScratchBytes / 2);
+  void* scratch = nullptr;
+  if (int rc = noalloc_scratch(&scratch)) return rc;
+  NoAllocScope no_alloc;  // nothing below may allocate: no pinned status mirror, no cudaFree(nullptr)
+  return ret_common(true, ret_args(q, k, v, mask, decay, nullptr, const_cast<float*>(r), dout, dq, dk, dv_out, B, H, Lq,
+                                   Lkv, dqk, dv, scale, causal, scratch, kNoAllocScratchBytes), dtype, stream, false, nullptr);
 }
 
 int attn_b200_ret_chunk_fwd(const void* q, const void* k, const void* v, const float* decay, void* o, int B, int H, int L,

@@ -73,6 +73,19 @@ inline int check_launch(const char* what) {
   return kOk;
 }
 
+// Set (per thread) for the duration of an entry point that promised its caller to allocate nothing: the helpers below
+// that would otherwise create something on their first use on a device (the pinned status mirror, the context-binding
+// cudaFree(nullptr)) skip that step while it is set. Every other entry point leaves it clear.
+inline bool& no_alloc_scope_flag() {
+  static thread_local bool flag = false;
+  return flag;
+}
+struct NoAllocScope {
+  bool prev;
+  NoAllocScope() : prev(no_alloc_scope_flag()) { no_alloc_scope_flag() = true; }
+  ~NoAllocScope() { no_alloc_scope_flag() = prev; }
+};
+
 // Host-visible mirror of the device status words of THIS library on the calling thread's current device: four ints in
 // mapped pinned host memory ([0] status, [1] detail, [2] numeric flag) that report_timeout() / report_saturation() write
 // next to the device-side words.
@@ -90,6 +103,7 @@ static volatile int* status_mirror() {
     return nullptr;
   }
   if (table[dev] != nullptr) return table[dev];
+  if (no_alloc_scope_flag()) return nullptr;  // not created yet, and the caller may not allocate: do without it
   std::lock_guard<std::mutex> lock(mu);
   if (table[dev] != nullptr) return table[dev];
   int* host = nullptr;
@@ -114,7 +128,7 @@ static volatile int* status_mirror() {
 // word is read from the host-mapped mirror.
 static int check_prior_status(const char* what) {
   volatile int* m = status_mirror();
-  if (m == nullptr) return kErrCuda;
+  if (m == nullptr) return no_alloc_scope_flag() ? kOk : kErrCuda;
   if (m[0] != 0) {
     const int det = m[1];
     return fail(kErrDevice,
@@ -178,6 +192,7 @@ inline int bind_device_of(const void* ptr, const char* what) {
   if (at.type == cudaMemoryTypeDevice && cur != at.device)
     return fail(kErrInvalidArgument, "%s: tensors live on device %d but the calling thread's current device is %d", what,
                 at.device, cur);
+  if (no_alloc_scope_flag()) return kOk;  // the entry point has bound the context itself (cudaGetSymbolAddress)
   cudaError_t e = cudaFree(nullptr);  // binds the primary context to this thread if it is not yet
   if (e != cudaSuccess) return fail(kErrCuda, "%s: context initialisation: %s", what, cudaGetErrorString(e));
   return kOk;

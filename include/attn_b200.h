@@ -140,6 +140,32 @@ int attn_b200_ret_bwd_ws(const void* q, const void* k, const void* v, const void
                          int Lkv, int dqk, int dv, int dtype, float scale, const float* decay, int causal, void* stream);
 
 /*
+ * The RetNet backward for callers that can neither bring scratch memory nor let the library allocate any. Such callers
+ * exist wherever device memory is handed out by something other than cudaMalloc at call time: a serving process that
+ * gave the whole HBM to its own pool at start-up and forbids allocations on the request path (an allocation there
+ * synchronises the device and can fail under fragmentation), a plug-in running inside a host framework whose memory
+ * budget it must not exceed, code on a latency-critical path where cudaMalloc's implicit synchronisation is not
+ * acceptable. attn_b200_ret_bwd_ws wants a workspace from them and the Python operator allocates one; this entry
+ * point does neither: the transposed copy of the mask goes into an array that is part of the library image itself.
+ *   Same tensors and meaning as attn_b200_ret_bwd, without the dq_accum argument.
+ *   Limit: the array has attn_b200_ret_bwd_noalloc_max_bytes() = 32 MiB, i.e. a mask tensor of at most H*Lq*Lkv = 16 Mi
+ *   elements (8 heads x 1448 x 1448, 4 x 2048 x 2048, 16 x 1024 x 1024); a larger mask is rejected with
+ *   ATTN_B200_ERR_INVALID_ARGUMENT and a message that names both sizes. With `decay` no scratch is used and there is no
+ *   limit. Every device that loads the library holds the 32 MiB until the process exits.
+ *   The call makes no cudaMalloc / cudaFree / cudaHostAlloc and calls no allocating library routine. The FIRST call on a
+ *   device looks up the array's device address (cudaGetSymbolAddress, with that device current) and remembers it;
+ *   make that first call before any stream capture begins on that device.
+ *   The array is shared by all calls and keeps what the last call wrote; nothing in it has to start at zero (each
+ *   call overwrites the part it reads), but two calls whose kernels overlap on the GPU (different streams, or threads
+ *   without ordering between them) race on it: order them on one stream or with events.
+ * No counterpart in the reference (its backward takes its scratch, dq_accum, from the caller).
+ */
+size_t attn_b200_ret_bwd_noalloc_max_bytes(void);
+int attn_b200_ret_bwd_noalloc(const void* q, const void* k, const void* v, const void* mask, const void* dout, const float* r,
+                              void* dq, void* dk, void* dv_out, int B, int H, int Lq, int Lkv, int dqk, int dv, int dtype,
+                              float scale, const float* decay, int causal, void* stream);
+
+/*
  * Chunkwise (recurrent-state) RetNet forward: the unnormalised retention
  *     O[i] = scale * sum_{j <= i} gamma_h^(i-j) (q_i . k_j) v_j
  * evaluated chunk by chunk with a running state, so the work grows with L instead of L^2. Replaces the reference's
