@@ -463,7 +463,9 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
       const int bh = it.bh, row0 = it.row0, n_iter = it.n_iter;
       const int grow = row0 + tid;
       if (n_iter == 0) {
-        // no block contributes to this tile: zeros
+        // no block contributes to this tile: zeros (written, like every output of this kernel, only after the kernels
+        // before it in the stream have completed: one of them may still be reading scratch data parked in `out`)
+        pdl_grid_dependency_wait();
         if (grp == 0 && grow < rows_len) {
           uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + (static_cast<size_t>(bh) * rows_len + grow) * D;
           for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
@@ -675,6 +677,9 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
       ok = mbar_wait_warp(acc_done, kacc & 1, ab, kFbAccDone);
       if (!ok) break;
       tc_fence_after();
+      // A programmatic dependent computes its first tile while its predecessor drains, but stores nothing before
+      // that kernel has completed: the fused dK/dV kernel reads per-query terms parked in the dq buffer.
+      if (kacc == 0) pdl_grid_dependency_wait();
       const uint32_t ta = tmem_addr(tACC, lane_base, 0);
 #pragma unroll
       for (int c0 = 0; c0 < D; c0 += 32) {

@@ -212,6 +212,13 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// Untiled bulk copy global -> shared memory of this CTA; both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -342,6 +349,18 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_
   return d;
 }
 
+// The same descriptor without swizzle, for small K-major operands written by threads or by a plain bulk copy: the
+// tile is made of core matrices of 8 rows x 16 bytes stored contiguously (128 bytes each);
+//   LBO = bytes between the two core matrices of a 16-element K slice, SBO = bytes between 8-row groups.
+__device__ __forceinline__ uint64_t umma_smem_desc_noswizzle(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
+  return d;
+}
+
 // D[tmem] (+)= A[smem] * B[smem]. One thread issues.
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                         uint32_t accumulate) {
@@ -386,6 +405,17 @@ __device__ __forceinline__ uint32_t ex2_approx_h2(uint32_t xh2) {
 __device__ __forceinline__ uint32_t hadd2_u32(uint32_t a, uint32_t b) {
   uint32_t r;
   asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+// Product of two packed pairs of 16-bit floats (fp16 or bf16), rounded to nearest.
+template <bool BF16>
+__device__ __forceinline__ uint32_t mul2_16(uint32_t a, uint32_t b) {
+  uint32_t r;
+  if constexpr (BF16) {
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  } else {
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  }
   return r;
 }
 // The two fp16 halves of a register as a packed fp32 pair (low half first).

@@ -93,9 +93,43 @@ def test_many_slices_deterministic_and_linear_in_dout(lib):
         assert oracle.within(oracle.error_stats(got[:1, :4], want), "fp16", scale_by_peak=True)
 
 
-def test_more_query_blocks_than_the_delta_cache_holds(lib):
-    """The dK kernel caches delta for the first 32 query blocks of a slice; 33 blocks exercise both paths."""
+@pytest.mark.parametrize("split", ["0", "1"])
+def test_more_query_blocks_than_the_delta_cache_holds(lib, monkeypatch, split):
+    """The three-kernel form's dK kernel caches delta for the first 32 query blocks of a slice; 33 blocks exercise both
+    of its paths (and many ring turns of the fused kernel)."""
+    monkeypatch.setenv("ATTN_B200_FA_BWD_SPLIT", split)
     q, k, v, do = rand_case(17, 1, 2, 4224, 256, 64, torch.float16)
+    check(run_fwd_bwd(lib, q, k, v, do, 0.125, False), q, k, v, do, 0.125, False, "fp16")
+
+
+@pytest.mark.parametrize("split", ["1", "0"])
+@pytest.mark.parametrize("d,causal", [(128, False), (64, True)])
+def test_three_kernel_form_and_fused_form(lib, monkeypatch, split, d, causal):
+    """dK and dV come from one fused kernel by default; ATTN_B200_FA_BWD_SPLIT=1 selects the form with one kernel per
+    gradient (also taken for very short query sequences). Both are checked against the oracle."""
+    monkeypatch.setenv("ATTN_B200_FA_BWD_SPLIT", split)
+    q, k, v, do = rand_case(23, 1, 3, 520, 520 if causal else 300, d, torch.float16)
+    check(run_fwd_bwd(lib, q, k, v, do, 0.1, causal), q, k, v, do, 0.1, causal, "fp16")
+
+
+@pytest.mark.parametrize("dtype_name,mag", [("fp16", 1.0 / 64), ("fp16", 512.0), ("bf16", 1e-4), ("bf16", 1e4)])
+def test_small_and_large_output_gradients(lib, dtype_name, mag):
+    """The fused kernel folds -lse / scale and -delta into its GEMMs as sums of three 16-bit pieces; gradients far from
+    unit size (loss scaling, tiny learning signals) must keep their relative accuracy. Errors are judged on
+    gradients / mag."""
+    dt = torch.float16 if dtype_name == "fp16" else torch.bfloat16
+    q, k, v, do = rand_case(29, 1, 2, 384, 448, 128, dt)
+    do = (do.float() * mag).to(dt)
+    grads = run_fwd_bwd(lib, q, k, v, do, 0.09, False)
+    ref = oracle.attention_bwd(q, k, v, do, 0.09, False)
+    for got, want, name in zip(grads, ref, ("dq", "dk", "dv")):
+        st = oracle.error_stats(got.float() / mag, want / mag)
+        assert oracle.within(st, dtype_name, scale_by_peak=True), (name, mag, st)
+
+
+def test_short_query_sequences_take_the_three_kernel_form(lib):
+    """Fewer than 16 queries at d = 64: the dq buffer cannot hold a block of per-query terms."""
+    q, k, v, do = rand_case(31, 2, 2, 9, 200, 64, torch.float16)
     check(run_fwd_bwd(lib, q, k, v, do, 0.125, False), q, k, v, do, 0.125, False, "fp16")
 
 
