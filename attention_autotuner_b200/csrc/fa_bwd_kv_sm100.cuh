@@ -16,12 +16,13 @@
 // The reference has no attention backward (python/ops/attention_interface.py:38-39 is `pass`); the formulas are the
 // derivative of its forward (python/utils/ref_op.py:2-6) with the softmax recomputed from the forward's log-sum-exp.
 //
-// Z1 and Z2 are single buffered (tensor memory: Z1, Z2, dV and dK accumulators = 4 x 128 columns at D = 128), but the
-// two chains S^T -> P^T -> dV and dP^T -> dS^T -> dK interleave: one warp issues, in this order,
-//     [dV += W1(t) dO_t ; Z1(t+1)]   [dK += W2(t) Q_t ; Z2(t+1)]
-// so the tensor pipe works on one chain while the element-wise warps work on the other.
-// Roles (512 threads): warps 0-3 and 8-11 element-wise (two threads per key row: query columns 0-63 / 64-127),
-// warp 4 MMA issue, warp 6 lane 0 TMA producer, warps 12-15 epilogue (accumulators -> 16 bit -> global).
+// Z1 and Z2 are single buffered (tensor memory: Z1, Z2, dV and dK accumulators = 4 x 128 columns at D = 128), but Z1
+// is produced and consumed in two halves of 64 query columns, so three chains interleave: one warp issues, in this
+// order,
+//     [dV += W1a(t) dO_t[0:64] ; Z1a(t+1)]   [dV += W1b(t) dO_t[64:128] ; Z1b(t+1)]   [dK += W2(t) Q_t ; Z2(t+1)]
+// and the tensor pipe works on one chain while the element-wise warps work on another.
+// Roles (512 threads): warps 0-3 and 8-11 element-wise (two threads per key row),
+// warps 4 and 5 MMA issue (one per chain), warp 6 lane 0 TMA producer, warps 12-15 epilogue (accumulators -> 16 bit -> global).
 #pragma once
 
 #include <cuda_bf16.h>
@@ -136,6 +137,10 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   constexpr bool BF16 = Cfg::BF16;
   // AB200_FA_BWD_KV_POLY=1: one column pair in AB200_FA_BWD_KV_POLY_EVERY takes its exponentials as a cubic on the
   // FMA pipes instead of the special-function unit
+#ifndef AB200_FKV_MMA_UNROLL
+#define AB200_FKV_MMA_UNROLL 16
+#endif
+  constexpr int MU = AB200_FKV_MMA_UNROLL;  // unroll factor of the MMA issue loops
 #ifndef AB200_FA_BWD_KV_POLY
 #define AB200_FA_BWD_KV_POLY 0
 #endif
@@ -156,10 +161,10 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   uint64_t* r_free = bars + 1;               // [1] the last first-GEMMs of a work item are complete
   uint64_t* slot_full = bars + 2;            // [NSLOT]
   uint64_t* slot_empty = slot_full + NSLOT;  // [NSLOT]
-  uint64_t* z1_full = slot_empty + NSLOT;    // [1]
-  uint64_t* z2_full = z1_full + 1;           // [1]
-  uint64_t* w1_full = z2_full + 1;           // [1] P^T written over Z1
-  uint64_t* w2_full = w1_full + 1;           // [1] P^T .* Z2 written over Z2
+  uint64_t* z1_full = slot_empty + NSLOT;    // [2] one per half of Z1 (query columns 0-63 / 64-127 of the block)
+  uint64_t* z2_full = z1_full + 2;           // [1]
+  uint64_t* w1_full = z2_full + 1;           // [2] P^T of a half written over that half of Z1
+  uint64_t* w2_full = w1_full + 2;           // [1] P^T .* Z2 written over Z2
   uint64_t* acc_done = w2_full + 1;          // [1]
   uint64_t* acc_free = acc_done + 1;         // [1]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
@@ -199,16 +204,18 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 
   if (threadIdx.x == 0) {
     mbar_init(r_full, 1);
-    mbar_init(r_free, 1);
+    mbar_init(r_free, 2);  // one commit from each of the two MMA warps
     for (int i = 0; i < NSLOT; ++i) {
       mbar_init(&slot_full[i], 1);
-      mbar_init(&slot_empty[i], 1);
+      mbar_init(&slot_empty[i], 2);  // every streamed tile is read by both MMA warps
     }
-    mbar_init(z1_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&z1_full[i], 1);
+      mbar_init(&w1_full[i], 256);
+    }
     mbar_init(z2_full, 1);
-    mbar_init(w1_full, 256);
     mbar_init(w2_full, 256);
-    mbar_init(acc_done, 1);
+    mbar_init(acc_done, 2);
     mbar_init(acc_free, 128);
     ab->flag = 0;
     fence_mbar_init();
@@ -243,6 +250,12 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
   pdl_launch_dependents();
+#ifdef AB200_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    g_fa_bwd_trace[2][0][0] = clock64();
+    g_fa_bwd_trace[2][0][1] = static_cast<long long>(globaltimer_ns());
+  }
+#endif
   const uint32_t tZ1 = tmem_base;
   const uint32_t tZ2 = tmem_base + 128;
   const uint32_t tACCV = tmem_base + 256;
@@ -288,9 +301,13 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
           if (bi > slot) mbar_wait_drain(&slot_full[slot], ((bi - 1 - slot) / NSLOT) & 1, 2000000ull);
       }
     }
-  } else if (warp == 4) {
-    // ------------------------------------------------------------------ MMA issuer (converged warp, one elected lane)
+  } else if (warp == 4 || warp == 5) {
+    // ------------------------------------------------------------------ MMA issuers (converged warps, one elected lane)
+    // Warp 4 owns the chain S^T -> P^T -> dV (Z1, dV accumulator), warp 5 the chain dP^T -> dS^T -> dK (Z2, dK
+    // accumulator): a tcgen05.mma costs its issuing thread about 50 cycles whatever its shape, and the 40 MMAs of a
+    // block would keep one thread busy for as long as the tensor pipe needs to execute them.
     constexpr uint32_t idesc_z = umma_idesc(128, 128, BF16, false, false);
+    constexpr uint32_t idesc_zh = umma_idesc(128, 64, BF16, false, false);
     constexpr uint32_t idesc_acc = umma_idesc(128, D, BF16, false, true);
     bool ok = true;
     int g0 = 0, kacc = 0;
@@ -298,46 +315,102 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     const uint32_t zero_addr = x_addr + (2 + NBX) * XB;
     const uint64_t x1_desc = umma_smem_desc_noswizzle(x_addr, zero_addr - x_addr, 128);
     const uint64_t x2_desc = umma_smem_desc_noswizzle(x_addr + XB, zero_addr - (x_addr + XB), 128);
-    // Z1 (second = false) or Z2 (second = true) of global block g
-    auto gemm1 = [&](int g, bool second, bool last_of_item) {
-      const int item = 2 * g + (second ? 1 : 0);
-      const int slot = item % NSLOT;
-      ok = mbar_wait_warp(&slot_full[slot], (item / NSLOT) & 1, ab, kFkSlotFull);
+    auto wait_item = [&](int item) {
+      ok = mbar_wait_warp(&slot_full[item % NSLOT], (item / NSLOT) & 1, ab, kFkSlotFull);
+    };
+    // K step j (16 queries) of half h of a W tile: the 32 values of queries h*64 ... +31 sit in columns
+    // [h*64, h*64+16), those of queries h*64+32 ... +63 in [h*64+32, h*64+48) (each written by the group that read them)
+    auto w_col = [](int h, int j) -> uint32_t { return static_cast<uint32_t>(h * 64 + (j < 2 ? j * 8 : 32 + (j - 2) * 8)); };
+    // Half h of Z1 (query columns h * 64 ... h * 64 + 63) of global block g: N = 64
+    auto gemm1a = [&](int g, int h, bool last_of_item) {
+      wait_item(2 * g);
       if (!ok) return;
+      if (lane == 0) AB200_FBTR(1, g, 2 + h);
+      const int slot = (2 * g) % NSLOT;
+      const uint32_t a = ring_addr + slot * ITEM + h * 8192;  // rows h * 64 ... of every box
+      const uint32_t bx = x_addr + (2 + (g % NBX)) * XB + h * 1024;  // landed with the Q item of this block
       tc_fence_after();
       if (elect_one()) {
-        const uint32_t a = ring_addr + slot * ITEM;
-        const uint32_t tz = second ? tZ2 : tZ1;
-        const uint32_t r = second ? r2_addr : r1_addr;
-#pragma unroll
+        const uint32_t tz = tZ1 + h * 64;
+#pragma unroll MU
         for (int b = 0; b < DB; ++b)
-#pragma unroll
+#pragma unroll MU
           for (int ks = 0; ks < 4; ++ks)
-            umma_ss(tz, umma_smem_desc(r + b * BOX + ks * 32, 16, 1024), umma_smem_desc(a + b * BOX + ks * 32, 16, 1024),
-                    idesc_z, (b > 0 || ks > 0) ? 1u : 0u);
-        const uint32_t bx = x_addr + (2 + (g % NBX)) * XB;  // landed with the Q item of this block
-        umma_ss(tz, second ? x2_desc : x1_desc, umma_smem_desc_noswizzle(bx, zero_addr - bx, 128), idesc_z, 1u);
-        tc_commit(second ? z2_full : z1_full);
-        if (second && last_of_item) tc_commit(r_free);
+            umma_ss(tz, umma_smem_desc(r1_addr + b * BOX + ks * 32, 16, 1024), umma_smem_desc(a + b * BOX + ks * 32, 16, 1024),
+                    idesc_zh, (b > 0 || ks > 0) ? 1u : 0u);
+#ifndef AB200_FKV_NOX
+        umma_ss(tz, x1_desc, umma_smem_desc_noswizzle(bx, zero_addr - bx, 128), idesc_zh, 1u);
+#endif
+        tc_commit(&z1_full[h]);
+        if (h == 1) {
+          tc_commit(&slot_empty[slot]);  // this warp's last use of the Q item (the other one: dK += W2 Q)
+          if (last_of_item) tc_commit(r_free);
+        }
       }
       __syncwarp();
     };
-    // dV += W1 dO_t (second = false) or dK += W2 Q_t (second = true) of global block g
-    auto gemm2 = [&](int g, bool second, bool first_of_item, bool last_of_item) {
-      ok = mbar_wait_warp(second ? w2_full : w1_full, g & 1, ab, second ? kFkW2Full : kFkW1Full);
+    // dV += W1[half h] dO_t[rows of half h]
+    auto gemm2a = [&](int g, int h, bool first_of_item, bool last_of_item) {
+      ok = mbar_wait_warp(&w1_full[h], g & 1, ab, kFkW1Full);
+      if (ok && h == 0) wait_item(2 * g + 1);
       if (!ok) return;
-      const int slot = (2 * g + (second ? 0 : 1)) % NSLOT;  // full: the first GEMM of this block waited for it
+      if (lane == 0) AB200_FBTR(1, g, 4 + h);
+      const int slot = (2 * g + 1) % NSLOT;
+      const uint32_t a = ring_addr + slot * ITEM;
       tc_fence_after();
       if (elect_one()) {
-        const uint32_t a = ring_addr + slot * ITEM;
-        const uint32_t tw = second ? tZ2 : tZ1;
-        const uint32_t acc = second ? tACCK : tACCV;
-#pragma unroll
+#pragma unroll MU
+        for (int j = 0; j < 4; ++j)
+          umma_ts(tACCV, tZ1 + w_col(h, j), umma_smem_desc(a + (h * 4 + j) * 2048, BOX, 1024), idesc_acc,
+                  (!first_of_item || h > 0 || j > 0) ? 1u : 0u);
+        if (h == 1) {
+          tc_commit(&slot_empty[slot]);  // this warp's last use of the dO item (the other one: Z2)
+          if (last_of_item) tc_commit(acc_done);
+        }
+      }
+      __syncwarp();
+    };
+    // Z2 of global block g
+    auto gemm1b = [&](int g, bool last_of_item) {
+      wait_item(2 * g);  // the term tile travels with the Q item
+      if (ok) wait_item(2 * g + 1);
+      if (!ok) return;
+      const int slot = (2 * g + 1) % NSLOT;
+      const uint32_t a = ring_addr + slot * ITEM;
+      const uint32_t bx = x_addr + (2 + (g % NBX)) * XB;
+      tc_fence_after();
+      if (elect_one()) {
+#pragma unroll MU
+        for (int b = 0; b < DB; ++b)
+#pragma unroll MU
+          for (int ks = 0; ks < 4; ++ks)
+            umma_ss(tZ2, umma_smem_desc(r2_addr + b * BOX + ks * 32, 16, 1024), umma_smem_desc(a + b * BOX + ks * 32, 16, 1024),
+                    idesc_z, (b > 0 || ks > 0) ? 1u : 0u);
+#ifndef AB200_FKV_NOX
+        umma_ss(tZ2, x2_desc, umma_smem_desc_noswizzle(bx, zero_addr - bx, 128), idesc_z, 1u);
+#endif
+        tc_commit(z2_full);
+        tc_commit(&slot_empty[slot]);
+        if (last_of_item) tc_commit(r_free);
+      }
+      __syncwarp();
+      if (lane == 0) AB200_FBTR(1, g, 7);
+    };
+    // dK += W2 Q_t
+    auto gemm2b = [&](int g, bool first_of_item, bool last_of_item) {
+      ok = mbar_wait_warp(w2_full, g & 1, ab, kFkW2Full);
+      if (!ok) return;
+      if (lane == 0) AB200_FBTR(1, g, 6);
+      const int slot = (2 * g) % NSLOT;  // full: Z2 of this block waited for it
+      const uint32_t a = ring_addr + slot * ITEM;
+      tc_fence_after();
+      if (elect_one()) {
+#pragma unroll MU
         for (int ks = 0; ks < 8; ++ks)
-          umma_ts(acc, tw + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8), umma_smem_desc(a + ks * 2048, BOX, 1024), idesc_acc,
+          umma_ts(tACCK, tZ2 + w_col(ks >> 2, ks & 3), umma_smem_desc(a + ks * 2048, BOX, 1024), idesc_acc,
                   (!first_of_item || ks > 0) ? 1u : 0u);
         tc_commit(&slot_empty[slot]);
-        if (second && last_of_item) tc_commit(acc_done);
+        if (last_of_item) tc_commit(acc_done);
       }
       __syncwarp();
     };
@@ -348,27 +421,37 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       if (n == 0) continue;
       ok = mbar_wait_warp(r_full, kacc & 1, ab, kFkR);
       if (!ok) break;
-      gemm1(g0, false, n == 1);
-      if (ok) gemm1(g0, true, n == 1);
+      if (warp == 4) {
+        gemm1a(g0, 0, n == 1);
+        if (ok) gemm1a(g0, 1, n == 1);
+      } else {
+        gemm1b(g0, n == 1);
+      }
       for (int t = 0; t < n && ok; ++t) {
         const int g = g0 + t;
         if (t == 0 && kacc > 0) {
           ok = mbar_wait_warp(acc_free, (kacc - 1) & 1, ab, kFkAccFree);
           if (!ok) break;
         }
-        gemm2(g, false, t == 0, t + 1 == n);
-        if (ok && t + 1 < n) gemm1(g + 1, false, t + 2 == n);
-        if (ok) gemm2(g, true, t == 0, t + 1 == n);
-        if (ok && t + 1 < n) gemm1(g + 1, true, t + 2 == n);
+        if (warp == 4) {
+          // a half of Z1 is free again as soon as the dV MMAs that read its W1 are issued (MMAs execute in order)
+          gemm2a(g, 0, t == 0, t + 1 == n);
+          if (ok && t + 1 < n) gemm1a(g + 1, 0, t + 2 == n);
+          if (ok) gemm2a(g, 1, t == 0, t + 1 == n);
+          if (ok && t + 1 < n) gemm1a(g + 1, 1, t + 2 == n);
+        } else {
+          gemm2b(g, t == 0, t + 1 == n);
+          if (ok && t + 1 < n) gemm1b(g + 1, t + 2 == n);
+        }
       }
       g0 += n;
       ++kacc;
     }
   } else if (warp < 4 || (warp >= 8 && warp < 12)) {
     // ------------------------------------------------------------------ element-wise warpgroups
-    // Group 0 (warps 0-3) handles query columns 0-63 of every block, group 1 (warps 8-11) columns 64-127; thread `tid`
-    // of either group owns TMEM lane (key row) tid. The 16-bit results go over the accumulator they came from:
-    // columns 0-63 of the block at [0,32), columns 64-127 at [64,96), each half written by the group that read it.
+    // A block is worked in two halves of 64 query columns; of each half, group 0 (warps 0-3) takes the first 32 columns
+    // and group 1 (warps 8-11) the other 32; thread `tid` of either group owns TMEM lane (key row) tid. The 16-bit
+    // results go over the first 16 of the 32 accumulator columns their thread read.
     const int grp = warp >> 3;
     const int tid = threadIdx.x & 127;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32);
@@ -397,70 +480,84 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       for (int t = 0; t < n_iter; ++t) {
         const int g = g0 + t;
         const bool diag = p.causal && (it.t_start + t) * 128 == row0;  // the only block that straddles the diagonal
-        const uint32_t tz1 = tmem_addr(tZ1, lane_base, 0);
-        const uint32_t tz2 = tmem_addr(tZ2, lane_base, 0);
-        uint32_t pp[32];  // this thread's 64 values of P^T, packed
+        const uint32_t tz1 = tmem_addr(tZ1, lane_base, grp * 32);
+        const uint32_t tz2 = tmem_addr(tZ2, lane_base, grp * 32);
+        uint32_t pp[32];  // this thread's 2 x 32 values of P^T, packed
         if (threadIdx.x == 0) AB200_FBTR(0, g, 0);
-        ok = mbar_wait_warp(z1_full, g & 1, ab, kFkZ1Full);
-        if (!ok) break;
-        if (threadIdx.x == 0) AB200_FBTR(0, g, 1);
-        tc_fence_after();
-        {
-          uint32_t z[2][32];
-          tmem_ld32(tz1 + (2 * grp) * 32, z[0]);
-          tmem_ld32(tz1 + (2 * grp + 1) * 32, z[1]);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          ok = mbar_wait_warp(&z1_full[h], g & 1, ab, kFkZ1Full);
+          if (!ok) break;
+          if (threadIdx.x == 0) AB200_FBTR(0, g, 1 + 2 * h);
+          tc_fence_after();
+          uint32_t z[32];
+#ifdef AB200_FKV_NOEW
+#pragma unroll
+          for (int c = 0; c < 32; ++c) z[c] = 0;
+#else
+          tmem_ld32(tz1 + h * 64, z);
           tc_wait_ld();
+#endif
+          if (threadIdx.x == 0 && g > 0) AB200_FBTR(2, g, 4 * h);
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {
-#pragma unroll
-            for (int c = 0; c < 32; c += 2) {
-              const uint64_t a2 = fmul2(f2_pack(__uint_as_float(z[q][c]), __uint_as_float(z[q][c + 1])), sl2);
-              float p0, p1;
-              if (AB200_FA_BWD_KV_POLY && ((c >> 1) % AB200_FA_BWD_KV_POLY_EVERY == 0)) {
-                exp2_poly2(a2, p0, p1);
-              } else {
-                float a0, a1;
-                f2_unpack(a2, a0, a1);
-                p0 = ex2_approx(a0);
-                p1 = ex2_approx(a1);
-              }
-              if (diag) {
-                const int cc = (2 * grp + q) * 32 + c;  // query inside the block; the key inside the block is tid
-                if (cc < tid) p0 = 0.f;
-                if (cc + 1 < tid) p1 = 0.f;
-              }
-              pp[q * 16 + (c >> 1)] = pack2<BF16>(p0, p1);
+          for (int c = 0; c < 32; c += 2) {
+#ifdef AB200_FKV_NOEW
+            pp[h * 16 + (c >> 1)] = 0;
+            continue;
+#endif
+            const uint64_t a2 = fmul2(f2_pack(__uint_as_float(z[c]), __uint_as_float(z[c + 1])), sl2);
+            float p0, p1;
+            if (AB200_FA_BWD_KV_POLY && ((c >> 1) % AB200_FA_BWD_KV_POLY_EVERY == 0)) {
+              exp2_poly2(a2, p0, p1);
+            } else {
+              float a0, a1;
+              f2_unpack(a2, a0, a1);
+              p0 = ex2_approx(a0);
+              p1 = ex2_approx(a1);
             }
-            tmem_st16(tz1 + grp * 64 + q * 16, &pp[q * 16]);
+            if (diag) {
+              const int cc = h * 64 + grp * 32 + c;  // query inside the block; the key inside the block is tid
+              if (cc < tid) p0 = 0.f;
+              if (cc + 1 < tid) p1 = 0.f;
+            }
+            pp[h * 16 + (c >> 1)] = pack2<BF16>(p0, p1);
           }
+#ifndef AB200_FKV_NOEW
+          if (threadIdx.x == 0 && g > 0) AB200_FBTR(2, g, 4 * h + 1);
+          tmem_st16(tz1 + h * 64, &pp[h * 16]);
+          tc_wait_st();
+          if (threadIdx.x == 0 && g > 0) AB200_FBTR(2, g, 4 * h + 2);
+#endif
+          tc_fence_before();
+          mbar_arrive(&w1_full[h]);
+          if (threadIdx.x == 0) AB200_FBTR(0, g, 2 + 2 * h);
         }
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(w1_full);
-        if (threadIdx.x == 0) AB200_FBTR(0, g, 2);
+        if (!ok) break;
         ok = mbar_wait_warp(z2_full, g & 1, ab, kFkZ2Full);
         if (!ok) break;
-        if (threadIdx.x == 0) AB200_FBTR(0, g, 3);
+        if (threadIdx.x == 0) AB200_FBTR(0, g, 5);
         tc_fence_after();
         {
+#ifndef AB200_FKV_NOEW
           uint32_t z[2][32];
-          tmem_ld32(tz2 + (2 * grp) * 32, z[0]);
-          tmem_ld32(tz2 + (2 * grp + 1) * 32, z[1]);
+          tmem_ld32(tz2, z[0]);
+          tmem_ld32(tz2 + 64, z[1]);
           tc_wait_ld();
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {
+          for (int h = 0; h < 2; ++h) {
             uint32_t pk[16];
 #pragma unroll
             for (int c = 0; c < 32; c += 2)
-              pk[c >> 1] = mul2_16<BF16>(pp[q * 16 + (c >> 1)],
-                                         pack2<BF16>(__uint_as_float(z[q][c]), __uint_as_float(z[q][c + 1])));
-            tmem_st16(tz2 + grp * 64 + q * 16, pk);
+              pk[c >> 1] = mul2_16<BF16>(pp[h * 16 + (c >> 1)],
+                                         pack2<BF16>(__uint_as_float(z[h][c]), __uint_as_float(z[h][c + 1])));
+            tmem_st16(tz2 + h * 64, pk);
           }
+#endif
         }
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(w2_full);
-        if (threadIdx.x == 0) AB200_FBTR(0, g, 4);
+        if (threadIdx.x == 0) AB200_FBTR(0, g, 6);
       }
       if (!ok) break;
       g0 += n_iter;
@@ -514,6 +611,12 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   __syncwarp();
   tc_fence_before();
   __syncthreads();
+#ifdef AB200_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    g_fa_bwd_trace[2][0][2] = clock64();
+    g_fa_bwd_trace[2][0][3] = static_cast<long long>(globaltimer_ns());
+  }
+#endif
   if (warp == 4) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);

@@ -169,6 +169,9 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, C
   for (uint32_t it = 0;; ++it) {
     bool ok = mbar_try_wait(bar, parity);
     if (__all_sync(0xffffffffu, ok)) return true;
+#ifdef AB200_POLL_SLEEP
+    __nanosleep(AB200_POLL_SLEEP);
+#endif
     if ((it & 63u) == 63u) {
       int give_up = 0;
       if ((threadIdx.x & 31) == 0) {
