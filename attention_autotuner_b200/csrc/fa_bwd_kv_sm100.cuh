@@ -16,11 +16,12 @@
 // The reference has no attention backward (python/ops/attention_interface.py:38-39 is `pass`); the formulas are the
 // derivative of its forward (python/utils/ref_op.py:2-6) with the softmax recomputed from the forward's log-sum-exp.
 //
-// Z1 and Z2 are single buffered (tensor memory: Z1, Z2, dV and dK accumulators = 4 x 128 columns at D = 128), but Z1
-// is produced and consumed in two halves of 64 query columns, so three chains interleave: one warp issues, in this
-// order,
-//     [dV += W1a(t) dO_t[0:64] ; Z1a(t+1)]   [dV += W1b(t) dO_t[64:128] ; Z1b(t+1)]   [dK += W2(t) Q_t ; Z2(t+1)]
-// and the tensor pipe works on one chain while the element-wise warps work on another.
+// Z1 and Z2 are single buffered (tensor memory: Z1, Z2, dV and dK accumulators = 4 x 128 columns at D = 128), but the
+// two chains S^T -> P^T -> dV and dP^T -> dS^T -> dK interleave, each issued by a warp of its own:
+//     warp 4:  [dV += W1(t)[:, 0:64] dO_t[0:64]]  [dV += W1(t)[:, 64:128] dO_t[64:128] ; Z1(t+1)]
+//     warp 5:  [dK += W2(t) Q_t ; Z2(t+1)]
+// so the tensor pipe works on one chain while the element-wise warps work on the other; P^T is handed over in two
+// halves of 64 query columns so that the first half of its MMAs runs under the exponentials of the second.
 // Roles (512 threads): warps 0-3 and 8-11 element-wise (two threads per key row),
 // warps 4 and 5 MMA issue (one per chain), warp 6 lane 0 TMA producer, warps 12-15 epilogue (accumulators -> 16 bit -> global).
 #pragma once
@@ -115,7 +116,7 @@ struct FaBwdKvConfig {
   static constexpr int BOX_BYTES = 128 * 128;
   static constexpr int ITEM_BYTES = DB * BOX_BYTES;    // one streamed tile (Q_t or dO_t)
   static constexpr int R_BYTES = 128 * D * 2;          // one resident tile (K or V)
-  static constexpr int NSLOT = D == 128 ? 4 : 8;       // ring: items 2g (Q) and 2g + 1 (dO) of block g
+  static constexpr int NSLOT = 4;                      // ring: items 2g (Q) and 2g + 1 (dO) of block g, two blocks deep
   static constexpr int NBX = NSLOT / 2;                // per-query term tiles, one per Q item in flight
   static constexpr int X_BYTES = 2048;                 // 128 rows x 8 values x 2 bytes
   static constexpr int X_REGION = (3 + NBX) * X_BYTES; // X1, X2, B ring, zeros
@@ -161,11 +162,11 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   uint64_t* r_free = bars + 1;               // [1] the last first-GEMMs of a work item are complete
   uint64_t* slot_full = bars + 2;            // [NSLOT]
   uint64_t* slot_empty = slot_full + NSLOT;  // [NSLOT]
-  uint64_t* z1_full = slot_empty + NSLOT;    // [2] one per half of Z1 (query columns 0-63 / 64-127 of the block)
-  uint64_t* z2_full = z1_full + 2;           // [1]
+  uint64_t* z1_full = slot_empty + NSLOT;    // [1]
+  uint64_t* z2_full = z1_full + 1;           // [1]
   uint64_t* w1_full = z2_full + 1;           // [2] P^T of a half written over that half of Z1
-  uint64_t* w2_full = w1_full + 2;           // [1] P^T .* Z2 written over Z2
-  uint64_t* acc_done = w2_full + 1;          // [1]
+  uint64_t* w2_full = w1_full + 2;           // [2] P^T .* Z2 of a half written over that half of Z2
+  uint64_t* acc_done = w2_full + 2;          // [1]
   uint64_t* acc_free = acc_done + 1;         // [1]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
   CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 2);
@@ -209,12 +210,12 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       mbar_init(&slot_full[i], 1);
       mbar_init(&slot_empty[i], 2);  // every streamed tile is read by both MMA warps
     }
+    mbar_init(z1_full, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&z1_full[i], 1);
       mbar_init(&w1_full[i], 256);
+      mbar_init(&w2_full[i], 256);
     }
     mbar_init(z2_full, 1);
-    mbar_init(w2_full, 256);
     mbar_init(acc_done, 2);
     mbar_init(acc_free, 128);
     ab->flag = 0;
@@ -307,7 +308,6 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     // accumulator): a tcgen05.mma costs its issuing thread about 50 cycles whatever its shape, and the 40 MMAs of a
     // block would keep one thread busy for as long as the tensor pipe needs to execute them.
     constexpr uint32_t idesc_z = umma_idesc(128, 128, BF16, false, false);
-    constexpr uint32_t idesc_zh = umma_idesc(128, 64, BF16, false, false);
     constexpr uint32_t idesc_acc = umma_idesc(128, D, BF16, false, true);
     bool ok = true;
     int g0 = 0, kacc = 0;
@@ -315,37 +315,38 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     const uint32_t zero_addr = x_addr + (2 + NBX) * XB;
     const uint64_t x1_desc = umma_smem_desc_noswizzle(x_addr, zero_addr - x_addr, 128);
     const uint64_t x2_desc = umma_smem_desc_noswizzle(x_addr + XB, zero_addr - (x_addr + XB), 128);
+    // Descriptors are built once; an MMA's operand is its tile's descriptor plus a constant (the address field counts
+    // 16-byte units and no tile crosses the 256 KB the field can hold), so that issuing an MMA costs two additions.
+    const uint64_t d_r1 = umma_smem_desc(r1_addr, 16, 1024), d_r2 = umma_smem_desc(r2_addr, 16, 1024);
+    const uint64_t d_ring_k = umma_smem_desc(ring_addr, 16, 1024);    // streamed tile as K-major B operand (first GEMMs)
+    const uint64_t d_ring_mn = umma_smem_desc(ring_addr, BOX, 1024);  // streamed tile as MN-major B operand (second GEMMs)
+    const uint64_t d_bx = umma_smem_desc_noswizzle(x_addr + 2 * XB, zero_addr - (x_addr + 2 * XB), 128);  // term tile 0
     auto wait_item = [&](int item) {
       ok = mbar_wait_warp(&slot_full[item % NSLOT], (item / NSLOT) & 1, ab, kFkSlotFull);
     };
     // K step j (16 queries) of half h of a W tile: the 32 values of queries h*64 ... +31 sit in columns
     // [h*64, h*64+16), those of queries h*64+32 ... +63 in [h*64+32, h*64+48) (each written by the group that read them)
     auto w_col = [](int h, int j) -> uint32_t { return static_cast<uint32_t>(h * 64 + (j < 2 ? j * 8 : 32 + (j - 2) * 8)); };
-    // Half h of Z1 (query columns h * 64 ... h * 64 + 63) of global block g: N = 64
-    auto gemm1a = [&](int g, int h, bool last_of_item) {
+    // Z1 of global block g
+    auto gemm1a = [&](int g, bool last_of_item) {
       wait_item(2 * g);
       if (!ok) return;
-      if (lane == 0) AB200_FBTR(1, g, 2 + h);
+      if (lane == 0) AB200_FBTR(1, g, 2);
       const int slot = (2 * g) % NSLOT;
-      const uint32_t a = ring_addr + slot * ITEM + h * 8192;  // rows h * 64 ... of every box
-      const uint32_t bx = x_addr + (2 + (g % NBX)) * XB + h * 1024;  // landed with the Q item of this block
+      const uint64_t da = d_ring_k + ((slot * ITEM) >> 4);
+      // the term tile landed with the Q item of this block; a tile further on moves the zero tile one tile closer
+      const uint64_t dx = d_bx + (((g % NBX) * XB) >> 4) - (static_cast<uint64_t>(((g % NBX) * XB) >> 4) << 16);
       tc_fence_after();
       if (elect_one()) {
-        const uint32_t tz = tZ1 + h * 64;
 #pragma unroll MU
         for (int b = 0; b < DB; ++b)
 #pragma unroll MU
           for (int ks = 0; ks < 4; ++ks)
-            umma_ss(tz, umma_smem_desc(r1_addr + b * BOX + ks * 32, 16, 1024), umma_smem_desc(a + b * BOX + ks * 32, 16, 1024),
-                    idesc_zh, (b > 0 || ks > 0) ? 1u : 0u);
-#ifndef AB200_FKV_NOX
-        umma_ss(tz, x1_desc, umma_smem_desc_noswizzle(bx, zero_addr - bx, 128), idesc_zh, 1u);
-#endif
-        tc_commit(&z1_full[h]);
-        if (h == 1) {
-          tc_commit(&slot_empty[slot]);  // this warp's last use of the Q item (the other one: dK += W2 Q)
-          if (last_of_item) tc_commit(r_free);
-        }
+            umma_ss(tZ1, d_r1 + ((b * BOX + ks * 32) >> 4), da + ((b * BOX + ks * 32) >> 4), idesc_z, (b > 0 || ks > 0) ? 1u : 0u);
+        umma_ss(tZ1, x1_desc, dx, idesc_z, 1u);
+        tc_commit(z1_full);
+        tc_commit(&slot_empty[slot]);  // this warp's last use of the Q item (the other one: dK += W2 Q)
+        if (last_of_item) tc_commit(r_free);
       }
       __syncwarp();
     };
@@ -356,13 +357,12 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       if (!ok) return;
       if (lane == 0) AB200_FBTR(1, g, 4 + h);
       const int slot = (2 * g + 1) % NSLOT;
-      const uint32_t a = ring_addr + slot * ITEM;
+      const uint64_t da = d_ring_mn + ((slot * ITEM + h * 4 * 2048) >> 4);
       tc_fence_after();
       if (elect_one()) {
 #pragma unroll MU
         for (int j = 0; j < 4; ++j)
-          umma_ts(tACCV, tZ1 + w_col(h, j), umma_smem_desc(a + (h * 4 + j) * 2048, BOX, 1024), idesc_acc,
-                  (!first_of_item || h > 0 || j > 0) ? 1u : 0u);
+          umma_ts(tACCV, tZ1 + w_col(h, j), da + ((j * 2048) >> 4), idesc_acc, (!first_of_item || h > 0 || j > 0) ? 1u : 0u);
         if (h == 1) {
           tc_commit(&slot_empty[slot]);  // this warp's last use of the dO item (the other one: Z2)
           if (last_of_item) tc_commit(acc_done);
@@ -376,19 +376,16 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       if (ok) wait_item(2 * g + 1);
       if (!ok) return;
       const int slot = (2 * g + 1) % NSLOT;
-      const uint32_t a = ring_addr + slot * ITEM;
-      const uint32_t bx = x_addr + (2 + (g % NBX)) * XB;
+      const uint64_t da = d_ring_k + ((slot * ITEM) >> 4);
+      const uint64_t dx = d_bx + (((g % NBX) * XB) >> 4) - (static_cast<uint64_t>(((g % NBX) * XB) >> 4) << 16);
       tc_fence_after();
       if (elect_one()) {
 #pragma unroll MU
         for (int b = 0; b < DB; ++b)
 #pragma unroll MU
           for (int ks = 0; ks < 4; ++ks)
-            umma_ss(tZ2, umma_smem_desc(r2_addr + b * BOX + ks * 32, 16, 1024), umma_smem_desc(a + b * BOX + ks * 32, 16, 1024),
-                    idesc_z, (b > 0 || ks > 0) ? 1u : 0u);
-#ifndef AB200_FKV_NOX
-        umma_ss(tZ2, x2_desc, umma_smem_desc_noswizzle(bx, zero_addr - bx, 128), idesc_z, 1u);
-#endif
+            umma_ss(tZ2, d_r2 + ((b * BOX + ks * 32) >> 4), da + ((b * BOX + ks * 32) >> 4), idesc_z, (b > 0 || ks > 0) ? 1u : 0u);
+        umma_ss(tZ2, x2_desc, dx, idesc_z, 1u);
         tc_commit(z2_full);
         tc_commit(&slot_empty[slot]);
         if (last_of_item) tc_commit(r_free);
@@ -396,21 +393,22 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       __syncwarp();
       if (lane == 0) AB200_FBTR(1, g, 7);
     };
-    // dK += W2 Q_t
-    auto gemm2b = [&](int g, bool first_of_item, bool last_of_item) {
-      ok = mbar_wait_warp(w2_full, g & 1, ab, kFkW2Full);
+    // dK += W2[half h] Q_t[rows of half h]
+    auto gemm2b = [&](int g, int h, bool first_of_item, bool last_of_item) {
+      ok = mbar_wait_warp(&w2_full[h], g & 1, ab, kFkW2Full);
       if (!ok) return;
       if (lane == 0) AB200_FBTR(1, g, 6);
       const int slot = (2 * g) % NSLOT;  // full: Z2 of this block waited for it
-      const uint32_t a = ring_addr + slot * ITEM;
+      const uint64_t da = d_ring_mn + ((slot * ITEM + h * 4 * 2048) >> 4);
       tc_fence_after();
       if (elect_one()) {
 #pragma unroll MU
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ts(tACCK, tZ2 + w_col(ks >> 2, ks & 3), umma_smem_desc(a + ks * 2048, BOX, 1024), idesc_acc,
-                  (!first_of_item || ks > 0) ? 1u : 0u);
-        tc_commit(&slot_empty[slot]);
-        if (last_of_item) tc_commit(acc_done);
+        for (int j = 0; j < 4; ++j)
+          umma_ts(tACCK, tZ2 + w_col(h, j), da + ((j * 2048) >> 4), idesc_acc, (!first_of_item || h > 0 || j > 0) ? 1u : 0u);
+        if (h == 1) {
+          tc_commit(&slot_empty[slot]);
+          if (last_of_item) tc_commit(acc_done);
+        }
       }
       __syncwarp();
     };
@@ -422,8 +420,7 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       ok = mbar_wait_warp(r_full, kacc & 1, ab, kFkR);
       if (!ok) break;
       if (warp == 4) {
-        gemm1a(g0, 0, n == 1);
-        if (ok) gemm1a(g0, 1, n == 1);
+        gemm1a(g0, n == 1);
       } else {
         gemm1b(g0, n == 1);
       }
@@ -434,13 +431,18 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
           if (!ok) break;
         }
         if (warp == 4) {
-          // a half of Z1 is free again as soon as the dV MMAs that read its W1 are issued (MMAs execute in order)
+          // the first half of the dV MMAs runs while the element-wise warps still work on the second half of P^T;
+          // Z1 is free again as soon as the MMAs that read W1 are issued (MMAs execute in order)
           gemm2a(g, 0, t == 0, t + 1 == n);
-          if (ok && t + 1 < n) gemm1a(g + 1, 0, t + 2 == n);
           if (ok) gemm2a(g, 1, t == 0, t + 1 == n);
-          if (ok && t + 1 < n) gemm1a(g + 1, 1, t + 2 == n);
+          if (ok && t + 1 < n) gemm1a(g + 1, t + 2 == n);
         } else {
-          gemm2b(g, t == 0, t + 1 == n);
+          // The MMAs of this chain can run under the next block's exponentials; those of the other chain cannot (P^T of
+          // the next block needs its Z1), and the tensor core takes MMAs in the order they are issued: so this warp
+          // lets Z1 of the next block complete first. (With a ring of two blocks the barrier cannot run a whole
+          // phase ahead of this wait: Z1 of block g + 2 needs the Q slot that the MMAs below release.)
+          gemm2b(g, 0, t == 0, t + 1 == n);
+          if (ok) gemm2b(g, 1, t == 0, t + 1 == n);
           if (ok && t + 1 < n) gemm1b(g + 1, t + 2 == n);
         }
       }
@@ -482,82 +484,60 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         const bool diag = p.causal && (it.t_start + t) * 128 == row0;  // the only block that straddles the diagonal
         const uint32_t tz1 = tmem_addr(tZ1, lane_base, grp * 32);
         const uint32_t tz2 = tmem_addr(tZ2, lane_base, grp * 32);
-        uint32_t pp[32];  // this thread's 2 x 32 values of P^T, packed
         if (threadIdx.x == 0) AB200_FBTR(0, g, 0);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          ok = mbar_wait_warp(&z1_full[h], g & 1, ab, kFkZ1Full);
+          uint32_t pp[16];  // this thread's 32 values of P^T of this half, packed
+          if (h == 0) ok = mbar_wait_warp(z1_full, g & 1, ab, kFkZ1Full);
           if (!ok) break;
           if (threadIdx.x == 0) AB200_FBTR(0, g, 1 + 2 * h);
           tc_fence_after();
-          uint32_t z[32];
-#ifdef AB200_FKV_NOEW
+          {
+            uint32_t z[32];
+            tmem_ld32(tz1 + h * 64, z);
+            tc_wait_ld();
 #pragma unroll
-          for (int c = 0; c < 32; ++c) z[c] = 0;
-#else
-          tmem_ld32(tz1 + h * 64, z);
-          tc_wait_ld();
-#endif
-          if (threadIdx.x == 0 && g > 0) AB200_FBTR(2, g, 4 * h);
-#pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-#ifdef AB200_FKV_NOEW
-            pp[h * 16 + (c >> 1)] = 0;
-            continue;
-#endif
-            const uint64_t a2 = fmul2(f2_pack(__uint_as_float(z[c]), __uint_as_float(z[c + 1])), sl2);
-            float p0, p1;
-            if (AB200_FA_BWD_KV_POLY && ((c >> 1) % AB200_FA_BWD_KV_POLY_EVERY == 0)) {
-              exp2_poly2(a2, p0, p1);
-            } else {
-              float a0, a1;
-              f2_unpack(a2, a0, a1);
-              p0 = ex2_approx(a0);
-              p1 = ex2_approx(a1);
+            for (int c = 0; c < 32; c += 2) {
+              const uint64_t a2 = fmul2(f2_pack(__uint_as_float(z[c]), __uint_as_float(z[c + 1])), sl2);
+              float p0, p1;
+              if (AB200_FA_BWD_KV_POLY && ((c >> 1) % AB200_FA_BWD_KV_POLY_EVERY == 0)) {
+                exp2_poly2(a2, p0, p1);
+              } else {
+                float a0, a1;
+                f2_unpack(a2, a0, a1);
+                p0 = ex2_approx(a0);
+                p1 = ex2_approx(a1);
+              }
+              if (diag) {
+                const int cc = h * 64 + grp * 32 + c;  // query inside the block; the key inside the block is tid
+                if (cc < tid) p0 = 0.f;
+                if (cc + 1 < tid) p1 = 0.f;
+              }
+              pp[c >> 1] = pack2<BF16>(p0, p1);
             }
-            if (diag) {
-              const int cc = h * 64 + grp * 32 + c;  // query inside the block; the key inside the block is tid
-              if (cc < tid) p0 = 0.f;
-              if (cc + 1 < tid) p1 = 0.f;
-            }
-            pp[h * 16 + (c >> 1)] = pack2<BF16>(p0, p1);
+            tmem_st16(tz1 + h * 64, pp);
           }
-#ifndef AB200_FKV_NOEW
-          if (threadIdx.x == 0 && g > 0) AB200_FBTR(2, g, 4 * h + 1);
-          tmem_st16(tz1 + h * 64, &pp[h * 16]);
+          if (h == 0) {
+            ok = mbar_wait_warp(z2_full, g & 1, ab, kFkZ2Full);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          {
+            uint32_t z[32], pk[16];
+            tmem_ld32(tz2 + h * 64, z);
+            tc_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 32; c += 2)
+              pk[c >> 1] = mul2_16<BF16>(pp[c >> 1], pack2<BF16>(__uint_as_float(z[c]), __uint_as_float(z[c + 1])));
+            tmem_st16(tz2 + h * 64, pk);
+          }
           tc_wait_st();
-          if (threadIdx.x == 0 && g > 0) AB200_FBTR(2, g, 4 * h + 2);
-#endif
           tc_fence_before();
           mbar_arrive(&w1_full[h]);
+          mbar_arrive(&w2_full[h]);
           if (threadIdx.x == 0) AB200_FBTR(0, g, 2 + 2 * h);
         }
         if (!ok) break;
-        ok = mbar_wait_warp(z2_full, g & 1, ab, kFkZ2Full);
-        if (!ok) break;
-        if (threadIdx.x == 0) AB200_FBTR(0, g, 5);
-        tc_fence_after();
-        {
-#ifndef AB200_FKV_NOEW
-          uint32_t z[2][32];
-          tmem_ld32(tz2, z[0]);
-          tmem_ld32(tz2 + 64, z[1]);
-          tc_wait_ld();
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t pk[16];
-#pragma unroll
-            for (int c = 0; c < 32; c += 2)
-              pk[c >> 1] = mul2_16<BF16>(pp[h * 16 + (c >> 1)],
-                                         pack2<BF16>(__uint_as_float(z[h][c]), __uint_as_float(z[h][c + 1])));
-            tmem_st16(tz2 + h * 64, pk);
-          }
-#endif
-        }
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(w2_full);
-        if (threadIdx.x == 0) AB200_FBTR(0, g, 6);
       }
       if (!ok) break;
       g0 += n_iter;

@@ -181,6 +181,9 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
 #define AB200_FA_BWD_POLY 0
 #endif
   constexpr bool FUSED = DUAL && (ROWK ? (AB200_FA_BWD_FUSED_DK != 0) : (AB200_FA_BWD_FUSED_DQ != 0));
+  // LEAN (the dQ kernel): dS is formed as a packed 16-bit product P .* (dP - delta) and the factor `scale` is applied
+  // once per output element in the epilogue instead of once per score.
+  constexpr bool LEAN = !ROWK && !FUSED;
   constexpr int NZ = DUAL ? 2 : 3;   // Z1 buffers: the dV kernel has no Z2 and uses its columns for a third one
   constexpr int PER_BLOCK = NC + 1;  // ring items per 128-wide block: C1 (, C2), T
 
@@ -478,7 +481,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
         const float delta = fa_bwd_delta_warp<D, BF16>(p.o, p.dout, bh, grow - lane, p.Lq, lane);
         if (grow < p.Lq) {
           row_nl2 = -p.lse[static_cast<size_t>(bh) * p.Lq + grow] * kLog2e;
-          row_nds = -delta * p.scale;
+          row_nds = LEAN ? -delta : -delta * p.scale;
         }
       }
       for (int t = 0; t < n_iter; ++t) {
@@ -574,6 +577,12 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
 #pragma unroll
             for (int c = 0; c < 32; c += 2) {
               uint64_t nds = f2_pack(row_nds, row_nds);
+              if constexpr (LEAN) {
+                float t0, t1;
+                f2_unpack(fadd2(f2_pack(__uint_as_float(z2[c]), __uint_as_float(z2[c + 1])), nds), t0, t1);
+                pk[c >> 1] = mul2_16<BF16>(pp[q * 16 + (c >> 1)], pack2<BF16>(t0, t1));
+                continue;
+              }
               if (ROWK) nds = f2_pack(__shfl_sync(0xffffffffu, col_nds[q], c), __shfl_sync(0xffffffffu, col_nds[q], c + 1));
               const uint64_t t2 = ffma2(f2_pack(__uint_as_float(z2[c]), __uint_as_float(z2[c + 1])), sc2, nds);
               uint64_t pr2;
@@ -681,6 +690,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
       // that kernel has completed: the fused dK/dV kernel reads per-query terms parked in the dq buffer.
       if (kacc == 0) pdl_grid_dependency_wait();
       const uint32_t ta = tmem_addr(tACC, lane_base, 0);
+      const float out_mul = LEAN ? p.scale : 1.f;
 #pragma unroll
       for (int c0 = 0; c0 < D; c0 += 32) {
         uint32_t rr[32];
@@ -696,7 +706,8 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
           for (int i = 0; i < 32; i += 16) {
             uint32_t v[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = pack2<BF16>(__uint_as_float(rr[i + 2 * e]), __uint_as_float(rr[i + 2 * e + 1]));
+            for (int e = 0; e < 8; ++e)
+              v[e] = pack2<BF16>(__uint_as_float(rr[i + 2 * e]) * out_mul, __uint_as_float(rr[i + 2 * e + 1]) * out_mul);
             st_global_v8(orow + c0 + i, v);
           }
         }
