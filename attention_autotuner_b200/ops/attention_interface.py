@@ -6,7 +6,7 @@ q [B,H,Lq,dqk], k [B,H,Lkv,dqk], v [B,H,Lkv,dv], fp16 or bf16 CUDA tensors. ``so
 the reference's fixed 0.125 (attention_interface.py / ref_op.py:3). The reference accepts ``causal`` and
 ignores it (csrc/kernels/attention/regfuse/regfuse.h:59-60); here it masks key j > i + (Lkv - Lq).
 Backward is empty in the reference (attention_interface.py:38-39: autograd gets None). Here it runs the
-flash-attention backward kernels (csrc/fa_bwd_sm100.cuh) when q, k and v share a head dimension of 64 or 128, and
+flash-attention backward kernels (csrc/fa_bwd_kv_sm100.cuh, csrc/fa_bwd_sm100.cuh) when q, k and v share a head dimension of 64 or 128, and
 raises for every other shape instead of returning None.
 """
 import ctypes

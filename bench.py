@@ -99,7 +99,7 @@ def metric_name(workload):
 
 def kernel_of(workload):
     return ("ret_chunk_sm100_kernel" if workload in CHUNKWISE else "chain_pair_sm100_kernel" if workload in RETNET else
-            "fa_bwd_sm100_kernel" if workload in ATTN_BWD else "fa_fwd_sm100_kernel")
+            "fa_bwd_kv_sm100_kernel" if workload in ATTN_BWD else "fa_fwd_sm100_kernel")
 
 
 def flops_fwd(B, H, Lq, Lkv, dqk, dv, causal):

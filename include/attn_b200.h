@@ -74,8 +74,11 @@ float attn_b200_fa_fwd_profile(const void* q, const void* k, const void* v, void
 /*
  * Flash-attention backward:  dQ, dK, dV of the forward above, given its output o, its log-sum-exp lse and dO.
  * The reference declares this backward and leaves it empty (python/ops/attention_interface.py:38-39); this entry
- * point is what that method would bind. Three kernels (dV, dK, dQ), each owning its output tile: no atomics and no
- * workspace; P is recomputed from lse, delta = rowsum(dO .* O) is computed inside the kernels.
+ * point is what that method would bind. Every output tile is owned by one CTA: no atomics and no workspace; P is
+ * recomputed from lse. Three launches: a small kernel that computes delta = rowsum(dO .* O) and -lse / scale per
+ * query, one kernel for dK and dV together, one for dQ. The per-query terms (16 bytes per query) are parked in the dq
+ * buffer until the dQ kernel, which runs last, overwrites it: dq must not overlap any input, and ATTN_B200_FA_BWD_SPLIT=1
+ * in the environment (or fewer than 16 queries) selects the older form with one kernel per gradient instead.
  *   q, o, dout, dq [B,H,Lq,d]   k, v, dk, dv [B,H,Lkv,d]   (dtype)    lse [B,H,Lq] fp32 (from attn_b200_fa_fwd)
  *   d in {64,128} for q, k and v alike. causal != 0 needs Lq == Lkv. scale as given to the forward.
  */
@@ -83,7 +86,7 @@ int attn_b200_fa_bwd(const void* q, const void* k, const void* v, const void* o,
                      void* dq, void* dk, void* dv, int B, int H, int Lq, int Lkv, int d, int dtype, float scale,
                      int causal, void* stream);
 
-/* Same arguments; timing loop as attn_b200_fa_fwd_profile. Returns ms per backward (three launches), or -1. */
+/* Same arguments; timing loop as attn_b200_fa_fwd_profile. Returns ms per backward (its three launches), or -1. */
 float attn_b200_fa_bwd_profile(const void* q, const void* k, const void* v, const void* o, const void* dout,
                                const float* lse, void* dq, void* dk, void* dv, int B, int H, int Lq, int Lkv, int d,
                                int dtype, float scale, int causal, void* stream);
