@@ -180,6 +180,9 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
 #ifndef AB200_FA_BWD_POLY
 #define AB200_FA_BWD_POLY 0
 #endif
+#ifndef AB200_FA_BWD_POLY_EVERY
+#define AB200_FA_BWD_POLY_EVERY 2
+#endif
   constexpr bool FUSED = DUAL && (ROWK ? (AB200_FA_BWD_FUSED_DK != 0) : (AB200_FA_BWD_FUSED_DQ != 0));
   // LEAN (the dQ kernel): dS is formed as a packed 16-bit product P .* (dP - delta) and the factor `scale` is applied
   // once per output element in the epilogue instead of once per score.
@@ -523,7 +526,7 @@ fa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_const
           // AB200_FA_BWD_POLY=1 puts every other pair on the FMA pipes; measured at B=8 H=16 L=4096 d=128: 5.3-5.7 ms
           // per backward against 5.1-5.3 ms with all of them on the special-function unit (the step is bound by
           // instruction issue, not by that unit)
-          if (AB200_FA_BWD_POLY && ((c >> 1) & 1)) {
+          if (AB200_FA_BWD_POLY && ((c >> 1) % AB200_FA_BWD_POLY_EVERY == 0)) {
             exp2_poly2(f2_pack(a0, a1), p0, p1);
           } else {
             p0 = ex2_approx(a0);
