@@ -1,7 +1,8 @@
-// Host launcher of the flash-attention backward: three launches of fa_bwd_sm100_kernel (dV, dK, dQ) on one
-// stream. The reference has no counterpart (python/ops/attention_interface.py:38-39); the argument order follows
-// its backward shims for RetNet (csrc/kernels/retnet/bwd/profile_code.py:50-115): inputs, saved forward results,
-// gradients out.
+// Host launcher of the flash-attention backward. Default form: fa_bwd_prep_kernel (per-query terms into the dq
+// buffer), fa_bwd_kv_sm100_kernel (dK and dV), fa_bwd_sm100_kernel<dQ>, on one stream; the older form (one
+// fa_bwd_sm100_kernel per gradient: dV, dK, dQ) runs for very short query sequences and on request. The reference has
+// no counterpart (python/ops/attention_interface.py:38-39); the argument order follows its backward shims for RetNet
+// (csrc/kernels/retnet/bwd/profile_code.py:50-115): inputs, saved forward results, gradients out.
 #pragma once
 
 #include <math.h>

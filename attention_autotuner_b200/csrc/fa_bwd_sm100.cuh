@@ -1,4 +1,5 @@
-// Flash-attention backward for sm_100a as three kernels that each own their output tile (no atomics, no fp32
+// Flash-attention backward for sm_100a, one kernel per gradient (the dQ flavour is the last launch of every backward;
+// dV and dK run only where fa_bwd_kv_sm100.cuh does not): three kernels that each own their output tile (no atomics, no fp32
 // accumulation buffer in global memory, bit-reproducible), built on the two-GEMM chain skeleton of chain_sm100.cuh
 // with a second "GEMM1" where the element-wise step needs both S and dP:
 //
