@@ -537,7 +537,7 @@ chain_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmR, const __grid_co
 #pragma unroll
       for (int round = 0; round < NROUND; ++round) {
         if (round == 1) {
-          // the stores of round 0 must have read the staging slots before they are overwritten
+          // the stores of pass 0 must have read the staging slots before they are overwritten
           if (tid == 0) tma_store_wait_read0();
           asm volatile("bar.sync 3, 128;" ::: "memory");
         }

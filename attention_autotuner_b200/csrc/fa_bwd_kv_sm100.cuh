@@ -19,9 +19,11 @@
 // Z1 and Z2 are single buffered (tensor memory: Z1, Z2, dV and dK accumulators = 4 x 128 columns at D = 128), but the
 // two chains S^T -> P^T -> dV and dP^T -> dS^T -> dK interleave, each issued by a warp of its own:
 //     warp 4:  [dV += W1(t)[:, 0:64] dO_t[0:64]]  [dV += W1(t)[:, 64:128] dO_t[64:128] ; Z1(t+1)]
-//     warp 5:  [dK += W2(t) Q_t ; Z2(t+1)]
-// so the tensor pipe works on one chain while the element-wise warps work on the other; P^T is handed over in two
-// halves of 64 query columns so that the first half of its MMAs runs under the exponentials of the second.
+//     warp 5:  [dK += W2(t)[:, 0:64] Q_t[0:64]]   [dK += W2(t)[:, 64:128] Q_t[64:128] ; Z2(t+1)]
+// The element-wise warps work P^T (two halves of 64 query columns), then dS^T (two halves), handing each half over as
+// soon as it is written. The next block cannot start before its Z1, and the tensor core executes MMAs in the order
+// they are issued, so warp 5 holds its last group back until warp 4 has issued Z1(t+1); that group then runs under
+// the next block's exponentials.
 // Roles (512 threads): warps 0-3 and 8-11 element-wise (two threads per key row),
 // warps 4 and 5 MMA issue (one per chain), warp 6 lane 0 TMA producer, warps 12-15 epilogue (accumulators -> 16 bit -> global).
 #pragma once
@@ -166,7 +168,8 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   uint64_t* z2_full = z1_full + 1;           // [1]
   uint64_t* w1_full = z2_full + 1;           // [2] P^T of a half written over that half of Z1
   uint64_t* w2_full = w1_full + 2;           // [2] P^T .* Z2 of a half written over that half of Z2
-  uint64_t* acc_done = w2_full + 2;          // [1]
+  uint64_t* s_issued = w2_full + 2;          // [1] warp 4 has issued Z1 of the next block
+  uint64_t* acc_done = s_issued + 1;         // [1]
   uint64_t* acc_free = acc_done + 1;         // [1]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
   CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 2);
@@ -216,6 +219,7 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       mbar_init(&w2_full[i], 256);
     }
     mbar_init(z2_full, 1);
+    mbar_init(s_issued, 1);
     mbar_init(acc_done, 2);
     mbar_init(acc_free, 128);
     ab->flag = 0;
@@ -310,7 +314,7 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     constexpr uint32_t idesc_z = umma_idesc(128, 128, BF16, false, false);
     constexpr uint32_t idesc_acc = umma_idesc(128, D, BF16, false, true);
     bool ok = true;
-    int g0 = 0, kacc = 0;
+    int g0 = 0, kacc = 0, n_held = 0;
     const uint32_t r1_addr = smem_u32(sR1), r2_addr = smem_u32(sR2), ring_addr = smem_u32(sRing), x_addr = smem_u32(sX);
     const uint32_t zero_addr = x_addr + (2 + NBX) * XB;
     const uint64_t x1_desc = umma_smem_desc_noswizzle(x_addr, zero_addr - x_addr, 128);
@@ -328,7 +332,7 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     // [h*64, h*64+16), those of queries h*64+32 ... +63 in [h*64+32, h*64+48) (each written by the group that read them)
     auto w_col = [](int h, int j) -> uint32_t { return static_cast<uint32_t>(h * 64 + (j < 2 ? j * 8 : 32 + (j - 2) * 8)); };
     // Z1 of global block g
-    auto gemm1a = [&](int g, bool last_of_item) {
+    auto gemm1a = [&](int g, bool last_of_item, bool announce) {
       wait_item(2 * g);
       if (!ok) return;
       if (lane == 0) AB200_FBTR(1, g, 2);
@@ -347,6 +351,7 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         tc_commit(z1_full);
         tc_commit(&slot_empty[slot]);  // this warp's last use of the Q item (the other one: dK += W2 Q)
         if (last_of_item) tc_commit(r_free);
+        if (announce) mbar_arrive(s_issued);
       }
       __syncwarp();
     };
@@ -420,7 +425,7 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       ok = mbar_wait_warp(r_full, kacc & 1, ab, kFkR);
       if (!ok) break;
       if (warp == 4) {
-        gemm1a(g0, n == 1);
+        gemm1a(g0, n == 1, false);
       } else {
         gemm1b(g0, n == 1);
       }
@@ -435,13 +440,20 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
           // Z1 is free again as soon as the MMAs that read W1 are issued (MMAs execute in order)
           gemm2a(g, 0, t == 0, t + 1 == n);
           if (ok) gemm2a(g, 1, t == 0, t + 1 == n);
-          if (ok && t + 1 < n) gemm1a(g + 1, t + 2 == n);
+          if (ok && t + 1 < n) gemm1a(g + 1, t + 2 == n, true);
         } else {
           // The MMAs of this chain can run under the next block's exponentials; those of the other chain cannot (P^T of
           // the next block needs its Z1), and the tensor core takes MMAs in the order they are issued: so this warp
           // lets Z1 of the next block complete first. (With a ring of two blocks the barrier cannot run a whole
           // phase ahead of this wait: Z1 of block g + 2 needs the Q slot that the MMAs below release.)
           gemm2b(g, 0, t == 0, t + 1 == n);
+          // The tensor core takes MMAs in the order they are issued. What is left of this chain can run under the next
+          // block's exponentials; Z1 of the next block cannot: this warp lets warp 4 issue it first.
+          if (ok && t + 1 < n) {
+            ok = mbar_wait_warp(&w2_full[1], g & 1, ab, kFkW2Full);
+            if (ok) ok = mbar_wait_warp(s_issued, n_held & 1, ab, kFkZ1Full);
+            ++n_held;
+          }
           if (ok) gemm2b(g, 1, t == 0, t + 1 == n);
           if (ok && t + 1 < n) gemm1b(g + 1, t + 2 == n);
         }
@@ -485,57 +497,59 @@ fa_bwd_kv_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         const uint32_t tz1 = tmem_addr(tZ1, lane_base, grp * 32);
         const uint32_t tz2 = tmem_addr(tZ2, lane_base, grp * 32);
         if (threadIdx.x == 0) AB200_FBTR(0, g, 0);
+        uint32_t pp[32];  // this thread's 2 x 32 values of P^T, packed
+        ok = mbar_wait_warp(z1_full, g & 1, ab, kFkZ1Full);
+        if (!ok) break;
+        if (threadIdx.x == 0) AB200_FBTR(0, g, 1);
+        tc_fence_after();
+        // P^T first, both halves (the chain S^T -> P^T -> dV -> next S^T is the one the next block waits for) ...
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          uint32_t pp[16];  // this thread's 32 values of P^T of this half, packed
-          if (h == 0) ok = mbar_wait_warp(z1_full, g & 1, ab, kFkZ1Full);
-          if (!ok) break;
-          if (threadIdx.x == 0) AB200_FBTR(0, g, 1 + 2 * h);
-          tc_fence_after();
-          {
-            uint32_t z[32];
-            tmem_ld32(tz1 + h * 64, z);
-            tc_wait_ld();
+          uint32_t z[32];
+          tmem_ld32(tz1 + h * 64, z);
+          tc_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 32; c += 2) {
-              const uint64_t a2 = fmul2(f2_pack(__uint_as_float(z[c]), __uint_as_float(z[c + 1])), sl2);
-              float p0, p1;
-              if (AB200_FA_BWD_KV_POLY && ((c >> 1) % AB200_FA_BWD_KV_POLY_EVERY == 0)) {
-                exp2_poly2(a2, p0, p1);
-              } else {
-                float a0, a1;
-                f2_unpack(a2, a0, a1);
-                p0 = ex2_approx(a0);
-                p1 = ex2_approx(a1);
-              }
-              if (diag) {
-                const int cc = h * 64 + grp * 32 + c;  // query inside the block; the key inside the block is tid
-                if (cc < tid) p0 = 0.f;
-                if (cc + 1 < tid) p1 = 0.f;
-              }
-              pp[c >> 1] = pack2<BF16>(p0, p1);
+          for (int c = 0; c < 32; c += 2) {
+            const uint64_t a2 = fmul2(f2_pack(__uint_as_float(z[c]), __uint_as_float(z[c + 1])), sl2);
+            float p0, p1;
+            if (AB200_FA_BWD_KV_POLY && ((c >> 1) % AB200_FA_BWD_KV_POLY_EVERY == 0)) {
+              exp2_poly2(a2, p0, p1);
+            } else {
+              float a0, a1;
+              f2_unpack(a2, a0, a1);
+              p0 = ex2_approx(a0);
+              p1 = ex2_approx(a1);
             }
-            tmem_st16(tz1 + h * 64, pp);
+            if (diag) {
+              const int cc = h * 64 + grp * 32 + c;  // query inside the block; the key inside the block is tid
+              if (cc < tid) p0 = 0.f;
+              if (cc + 1 < tid) p1 = 0.f;
+            }
+            pp[h * 16 + (c >> 1)] = pack2<BF16>(p0, p1);
           }
-          if (h == 0) {
-            ok = mbar_wait_warp(z2_full, g & 1, ab, kFkZ2Full);
-            if (!ok) break;
-            tc_fence_after();
-          }
-          {
-            uint32_t z[32], pk[16];
-            tmem_ld32(tz2 + h * 64, z);
-            tc_wait_ld();
-#pragma unroll
-            for (int c = 0; c < 32; c += 2)
-              pk[c >> 1] = mul2_16<BF16>(pp[c >> 1], pack2<BF16>(__uint_as_float(z[c]), __uint_as_float(z[c + 1])));
-            tmem_st16(tz2 + h * 64, pk);
-          }
+          tmem_st16(tz1 + h * 64, &pp[h * 16]);
           tc_wait_st();
           tc_fence_before();
           mbar_arrive(&w1_full[h]);
+          if (threadIdx.x == 0) AB200_FBTR(0, g, 2 + h);
+        }
+        // ... then dS^T, both halves
+        ok = mbar_wait_warp(z2_full, g & 1, ab, kFkZ2Full);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t z[32], pk[16];
+          tmem_ld32(tz2 + h * 64, z);
+          tc_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; c += 2)
+            pk[c >> 1] = mul2_16<BF16>(pp[h * 16 + (c >> 1)], pack2<BF16>(__uint_as_float(z[c]), __uint_as_float(z[c + 1])));
+          tmem_st16(tz2 + h * 64, pk);
+          tc_wait_st();
+          tc_fence_before();
           mbar_arrive(&w2_full[h]);
-          if (threadIdx.x == 0) AB200_FBTR(0, g, 2 + 2 * h);
+          if (threadIdx.x == 0) AB200_FBTR(0, g, 4 + h);
         }
         if (!ok) break;
       }
