@@ -66,7 +66,7 @@ class AttnConfig(BaseConfig):
             d["cfg_type"] = "FaFwdConfig<{}, {}, {}, {}, {}, {}, {}, {}, {}>".format(
                 self.Kd, self.dv_chunk, self.q_tiles, self.kv_stages, d["bf16"], self.exp_emu, self.softmax_split,
                 self.mma_warps, self.exp_h2)
-            d["launcher"] = "fa_fwd_launch"
+            d["launcher"] = "fa_fwd_launch_auto"
         return d
 
     def __repr__(self) -> str:

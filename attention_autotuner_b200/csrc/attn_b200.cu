@@ -56,8 +56,9 @@ template <bool BF16>
 int fa_fwd_dispatch(const FaFwdArgs& a, int dqk, cudaStream_t st, bool profile, float* ms) {
   auto run = [&](auto cfg_tag) -> int {
     using Cfg = decltype(cfg_tag);
-    if (!profile) return fa_fwd_launch<Cfg>(a, st);
-    *ms = profile_loop([&] { return fa_fwd_launch<Cfg>(a, st); }, st);
+    auto launch = [&]() -> int { return fa_fwd_launch_auto<Cfg>(a, st); };
+    if (!profile) return launch();
+    *ms = profile_loop(launch, st);
     return *ms < 0.f ? kErrCuda : kOk;
   };
   // chunk of the V head dim handled per CTA

@@ -104,6 +104,35 @@ def test_ragged_and_rectangular(lib, Lq, Lkv, causal):
     assert (lse - lref).abs().max().item() < 1e-3
 
 
+@pytest.mark.parametrize("form", ["grid", "persistent"])
+@pytest.mark.parametrize("B,H,Lq,Lkv,dqk,dv,causal", [
+    (1, 2, 1, 300, 128, 128, False), (1, 2, 129, 127, 128, 128, False), (2, 3, 640, 640, 128, 128, True),
+    (1, 2, 300, 900, 128, 128, True), (1, 2, 900, 300, 128, 128, True), (3, 70, 520, 520, 64, 64, True),
+    (1, 4, 1300, 1300, 64, 128, False), (2, 2, 768, 768, 128, 64, True)])
+def test_both_forms_of_the_forward_kernel(lib, monkeypatch, form, B, H, Lq, Lkv, dqk, dv, causal):
+    """The forward exists as a grid of one CTA per 256 query rows and as a persistent grid walking a work list (chosen
+    automatically: persistent under a causal mask); ATTN_B200_FA_FWD_FORM forces one of them. Cases: a single query,
+    ragged lengths, more keys than queries and fewer (causal rows without any visible key), more work items than
+    SMs (several items per CTA, tiles past the end of Q), V narrower and wider than Q."""
+    monkeypatch.setenv("ATTN_B200_FA_FWD_FORM", form)
+    q, k, v = rand_qkv(41, B, H, Lq, Lkv, dqk, dv, torch.float16)
+    scale = dqk ** -0.5
+    if B * H > 16:   # the oracle on a few slices only
+        o, lse = run_capi(lib, q, k, v, scale, causal)
+        check(o[:1, :4], lse[:1, :4], q[:1, :4], k[:1, :4], v[:1, :4], scale, causal, "fp16")
+        check(o[-1:, -4:], lse[-1:, -4:], q[-1:, -4:], k[-1:, -4:], v[-1:, -4:], scale, causal, "fp16")
+    else:
+        o, lse = run_capi(lib, q, k, v, scale, causal)
+        if causal and Lkv < Lq:   # rows without a visible key: zeros and lse = -inf; the rest against the oracle
+            oref, lref = oracle.attention_fwd(q, k, v, scale, causal)
+            empty = torch.arange(Lq) + (Lkv - Lq) < 0
+            assert (o[:, :, empty] == 0).all() and torch.isinf(lse[:, :, empty]).all()
+            assert oracle.within(oracle.error_stats(o[:, :, ~empty], oref[:, :, ~empty]), "fp16")
+            assert (lse[:, :, ~empty] - lref[:, :, ~empty]).abs().max().item() < 1e-3
+        else:
+            check(o, lse, q, k, v, scale, causal, "fp16")
+
+
 @pytest.mark.parametrize("dqk,dv", [(256, 256), (256, 128), (128, 512), (64, 192), (128, 64), (256, 64), (64, 256)])
 def test_head_dim_matrix(lib, dqk, dv):
     """The reference's head-dim range: dqk % 64 == 0 <= 256, dv % 64 == 0 <= 512

@@ -195,7 +195,7 @@ def test_cta_pair_knob_in_configs_and_search_space():
     assert at.validate_kernel(pair)
     src = _create_entry_code(pair)
     assert "FaPairConfig<128, 8, false>" in src and "fa_fwd_pair_launch<Cfg>" in src
-    assert "fa_fwd_launch<Cfg>" in _create_entry_code(AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, dv_chunk=128))
+    assert "fa_fwd_launch_auto<Cfg>" in _create_entry_code(AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, dv_chunk=128))
     rt = RetTunner(B200(), [z, z, zv, None, zv, None], decay=torch.ones(1))
     assert RetConfig(128, 128, 256, 512).cta_pair == 1 and RetConfig(128, 128, 64, 64).cta_pair == 0
     assert not rt.validate_kernel(RetConfig(128, 128, 256, 512, dv_chunk=64, cta_pair=1))
