@@ -116,15 +116,19 @@ int fa_fwd_persist_launch(const FaFwdArgs& a, cudaStream_t stream) {
   return check_launch("fa_fwd launch");
 }
 
-// The form that is faster for the call: measured at B=8 H=16 L=4096 d=128, the persistent kernel wins under a causal
-// mask (989 against 965 TFLOP/s fp16: its CTAs' work items are short there, 16.5 KV blocks on average, so what it saves
-// at the item boundaries counts) and loses without one (1120 against 1150: one CTA per 256 rows lets the hardware
-// hand the next tile to whichever SM is free first).
+// The default tile (two query tiles, up to 128 V columns, no softmax variant) exists in both forms; the persistent one
+// runs where a CTA's work items are short, because what it saves lies at their boundaries. Measured against the grid
+// form in one session (d = 128, back-to-back launches), without a mask / under a causal one: 148 slices of L = 2048
+// +5 % / +18 %, B=8 H=16 L=4096 +1 % / +8 %, L = 8192 0 % / +3 %, B=16 H=32 L=16384 -2 % / -2 %, Lq=1024 x Lkv=16384
+// -3 % (with long items a static work list loses more to the slowest SM than the boundaries cost). The rule: persistent
+// up to 40 KV blocks per item on average (half of the blocks count under a causal mask).
 template <class Cfg>
 int fa_fwd_launch_auto(const FaFwdArgs& a, cudaStream_t stream) {
   if constexpr (Cfg::NQ == 2 && Cfg::SPLIT == 1 && Cfg::NMMA == 1 && Cfg::EXP_EMU == 0 && Cfg::EXP_H2 == 0 && Cfg::DV <= 128) {
     const int form = fa_fwd_form_requested();
-    if (form == 2 || (form == 0 && a.causal)) return fa_fwd_persist_launch<Cfg>(a, stream);
+    const int nblk = (a.Lkv + Cfg::BN - 1) / Cfg::BN;
+    const int avg_blocks = a.causal ? (nblk + 1) / 2 : nblk;
+    if (form == 2 || (form == 0 && avg_blocks <= 40)) return fa_fwd_persist_launch<Cfg>(a, stream);
   }
   return fa_fwd_launch<Cfg>(a, stream);
 }

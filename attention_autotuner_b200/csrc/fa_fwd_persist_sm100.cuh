@@ -131,7 +131,9 @@ fa_fwd_persist_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
   const uint32_t tmem_base = *tmem_base_slot;
 
   if (warp >= kMmaWarp) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    // 384 threads start with 168 registers each; the softmax threads take 208 (a 128-column score row), which
+    // leaves this warpgroup 88: 256 x 208 + 128 x 88 = 384 x 168
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
     if (warp == kTmaWarp) {
       // ------------------------------------------------------------------ TMA producer
       if (lane == 0) {
@@ -303,7 +305,7 @@ fa_fwd_persist_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
     for (int u = 0; u < n_steps && ok; ++u) {
       FaFwdItem it;
       if (!get_item(u, it)) continue;
-      const int n_my = it.nblk[s];
+      const int n_my = s == 0 ? it.nblk[0] : it.nblk[1];  // (a select: indexing by s would put the item in local memory)
       const int row = it.m_base + s * BM + row_in_tile;
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (static_cast<size_t>(it.bh) * p.Lq + row) * p.dv_total + it.dv_off;
       if (n_my == 0) {
