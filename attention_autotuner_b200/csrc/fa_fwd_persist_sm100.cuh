@@ -307,12 +307,25 @@ fa_fwd_persist_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
       if (!get_item(u, it)) continue;
       const int n_my = s == 0 ? it.nblk[0] : it.nblk[1];  // (a select: indexing by s would put the item in local memory)
       const int row = it.m_base + s * BM + row_in_tile;
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (static_cast<size_t>(it.bh) * p.Lq + row) * p.dv_total + it.dv_off;
+      // (the output address is formed where it is used: a 64-bit value less to keep across the block loop)
+      // and the item is decoded again for it: only the tile's row and block count stay live across the block loop)
+      const int m_tile = it.m_base + s * BM;
+      auto out_row = [&]() -> uint16_t* {
+        FaFwdItem io;
+        get_item(u, io);
+        return reinterpret_cast<uint16_t*>(p.o) + (static_cast<size_t>(io.bh) * p.Lq + row) * p.dv_total + io.dv_off;
+      };
+      auto lse_row = [&]() -> float* {
+        FaFwdItem io;
+        get_item(u, io);
+        return (p.lse != nullptr && io.dv_off == 0) ? p.lse + static_cast<size_t>(io.bh) * p.Lq + row : nullptr;
+      };
       if (n_my == 0) {
+        uint16_t* orow = out_row();
         // no visible key at all for this tile (causal with Lkv < Lq), or the tile lies past the end of Q
         if (row < p.Lq) {
           for (int c = 0; c < DV; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
-          if (p.lse != nullptr && it.dv_off == 0) p.lse[static_cast<size_t>(it.bh) * p.Lq + row] = -INFINITY;
+          if (float* l = lse_row()) *l = -INFINITY;
         }
         continue;
       }
@@ -334,7 +347,7 @@ fa_fwd_persist_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         const int n0 = j * BN;
         // masking: keys past Lkv (ragged tail) and, under causal, keys j > i + shift
         const bool tail_blk = (n0 + BN > p.Lkv);
-        const bool diag_blk = p.causal && (n0 + BN - 1 > it.m_base + s * BM + causal_shift);
+        const bool diag_blk = p.causal && (n0 + BN - 1 > m_tile + causal_shift);
         if (tail_blk || diag_blk) {
           int limit = p.Lkv - n0;  // columns [limit, BN) are masked
           if (p.causal) {
@@ -419,6 +432,7 @@ fa_fwd_persist_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
       tc_fence_after();
       const float inv_l = l_sum > 0.f ? 1.0f / l_sum : 0.f;
       {
+        uint16_t* orow = out_row();
         uint32_t r[DV];
 #pragma unroll
         for (int c0 = 0; c0 < DV; c0 += 32) tmem_ld32(tO + c0, r + c0);
@@ -436,8 +450,8 @@ fa_fwd_persist_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
           }
         }
       }
-      if (p.lse != nullptr && it.dv_off == 0 && row < p.Lq)
-        p.lse[static_cast<size_t>(it.bh) * p.Lq + row] = (l_sum > 0.f) ? (m_ref * p.scale + __logf(l_sum)) : -INFINITY;
+      if (row < p.Lq)
+        if (float* l = lse_row()) *l = (l_sum > 0.f) ? (m_ref * p.scale + __logf(l_sum)) : -INFINITY;
       cs += n_my;
     }
   }
