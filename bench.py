@@ -98,8 +98,16 @@ def metric_name(workload):
 
 
 def kernel_of(workload):
-    return ("ret_chunk_sm100_kernel" if workload in CHUNKWISE else "chain_pair_sm100_kernel" if workload in RETNET else
-            "fa_bwd_kv_sm100_kernel" if workload in ATTN_BWD else "fa_fwd_sm100_kernel")
+    if workload in CHUNKWISE:
+        return "ret_chunk_sm100_kernel"
+    if workload in RETNET:
+        return "chain_pair_sm100_kernel"
+    if workload in ATTN_BWD:
+        return "fa_bwd_kv_sm100_kernel"
+    # the forward runs as the persistent kernel where a CTA's work items are short (csrc/fa_fwd_launch.cuh)
+    B, H, Lq, Lkv, dqk, dv, dtype, causal = WORKLOADS[workload]
+    nblk = (Lkv + 127) // 128
+    return "fa_fwd_persist_sm100_kernel" if ((nblk + 1) // 2 if causal else nblk) <= 40 else "fa_fwd_sm100_kernel"
 
 
 def flops_fwd(B, H, Lq, Lkv, dqk, dv, causal):
