@@ -133,6 +133,19 @@ def test_both_forms_of_the_forward_kernel(lib, monkeypatch, form, B, H, Lq, Lkv,
             check(o, lse, q, k, v, scale, causal, "fp16")
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_both_forms_give_the_same_bits(lib, monkeypatch, causal):
+    """Same tile, same order of operations: the persistent and the grid form agree bit for bit (ragged lengths, several
+    work items per CTA)."""
+    q, k, v = rand_qkv(43, 2, 90, 700, 700, 128, 128, torch.float16)
+    out = {}
+    for form in ("grid", "persistent"):
+        monkeypatch.setenv("ATTN_B200_FA_FWD_FORM", form)
+        out[form] = run_capi(lib, q, k, v, 0.09, causal)
+    assert torch.equal(out["grid"][0], out["persistent"][0])
+    assert torch.equal(out["grid"][1], out["persistent"][1])
+
+
 @pytest.mark.parametrize("dqk,dv", [(256, 256), (256, 128), (128, 512), (64, 192), (128, 64), (256, 64), (64, 256)])
 def test_head_dim_matrix(lib, dqk, dv):
     """The reference's head-dim range: dqk % 64 == 0 <= 256, dv % 64 == 0 <= 512
