@@ -132,7 +132,9 @@ fa_fwd_persist_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
 
   if (warp >= kMmaWarp) {
     // 384 threads start with 168 registers each; the softmax threads take 208 (a 128-column score row), which
-    // leaves this warpgroup 88: 256 x 208 + 128 x 88 = 384 x 168
+    // leaves this warpgroup 88: 256 x 208 + 128 x 88 = 384 x 168. (setmaxnreg.inc waits, with no limit, until the
+    // registers it asks for have been released: the two numbers must add up to no more than the CTA was given.)
+    static_assert(256 * 208 + 128 * 88 <= 384 * 168, "register split of the warpgroups");
     asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
     if (warp == kTmaWarp) {
       // ------------------------------------------------------------------ TMA producer

@@ -189,6 +189,9 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   // With three warpgroups the launch-time register split (168/thread) starves the softmax threads, which
   // hold a full 128-column score row; each role branch moves registers accordingly (setmaxnreg).
   if (warp >= kMmaWarp) {
+    // (setmaxnreg.inc waits, with no limit, until the registers it asks for have been released: 256 x 208 for the
+    // softmax threads + 128 x 72 here must not exceed the 384 x 168 the CTA was given)
+    static_assert(256 * 208 + 128 * 72 <= 384 * 168, "register split of the warpgroups");
     if constexpr (NQ == 2 && SPLIT == 1) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ TMA producer
