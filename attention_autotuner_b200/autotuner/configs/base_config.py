@@ -109,6 +109,7 @@ class BaseConfig:
             cc.__dict__.setdefault("mma_warps", 1)
             cc.__dict__.setdefault("cta_pair", 0)
             cc.__dict__.setdefault("exp_h2", 0)
+            cc.__dict__.setdefault("persistent", -1)  # entries cached before the knob existed: chosen per call
         if cc.__dict__.get("operation") in ("ret", "ret_bwd"):
             cc.__dict__.setdefault("cta_pair", 0)  # entries cached before the knob existed were single-CTA
         return cc

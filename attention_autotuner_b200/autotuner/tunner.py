@@ -44,6 +44,12 @@ class AttnTunner(BaseTunner):
         if config.cta_pair and (config.q_tiles != 2 or config.dv_chunk != 128 or config.softmax_split != 1
                                 or config.exp_emu != 0 or config.mma_warps != 1):
             return False
+        persistent = getattr(config, "persistent", -1)
+        if persistent not in (-1, 0, 1):
+            return False
+        if persistent == 1 and (config.q_tiles != 2 or config.dv_chunk > 128 or config.softmax_split != 1 or config.exp_emu != 0
+                                or config.mma_warps != 1 or config.cta_pair or getattr(config, "exp_h2", 0)):
+            return False
         return True
 
     def generate_configs(self, Br: int, Bc: int, dim_qk: int, dim_v: int):
@@ -66,6 +72,12 @@ class AttnTunner(BaseTunner):
                         for stages in (4, 5):
                             configs.append(AttnConfig(Br, Bc, dim_qk, dim_v, q_tiles=2, kv_stages=stages, dv_chunk=dv_chunk,
                                                       exp_h2=h2, dtype=self.dtype))
+                # the form of the grid, forced either way (the default picks per call by the length of the work items)
+                if dv_chunk <= 128:
+                    for form in (0, 1):
+                        for stages in (4, 5):
+                            configs.append(AttnConfig(Br, Bc, dim_qk, dim_v, q_tiles=2, kv_stages=stages, dv_chunk=dv_chunk,
+                                                      persistent=form, dtype=self.dtype))
                 # CTA pairs (cta_group::2): 512 query rows per cluster
                 for stages in (3, 4):
                     configs.append(AttnConfig(Br, Bc, dim_qk, dim_v, q_tiles=2, kv_stages=stages, dv_chunk=dv_chunk,

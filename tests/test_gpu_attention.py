@@ -296,6 +296,24 @@ def test_softmax_split_and_exp_emulation_knobs(split, emu, mw, causal):
     check(o.cpu(), lse.cpu(), q, k, v, 0.11, causal, "fp16")
 
 
+@pytest.mark.parametrize("persistent", [0, 1])
+@pytest.mark.parametrize("causal", [False, True])
+def test_grid_form_knob_of_the_tuner(persistent, causal):
+    """`persistent` in a tile configuration forces one form of the grid (the default, -1, lets the launcher choose by
+    the length of the work items)."""
+    from attention_autotuner_b200.autotuner.configs import AttnConfig
+    from attention_autotuner_b200.autotuner.runtime import Runtime
+    q, k, v = rand_qkv(31, 2, 3, 700, 900, 128, 128, torch.float16)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    o = torch.zeros(2, 3, 700, 128, device="cuda", dtype=torch.float16)
+    lse = torch.zeros(2, 3, 700, device="cuda")
+    rt = Runtime(B200(), AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, persistent=persistent))
+    rt.apply([qd, kd, vd, o], scale=0.11, causal=causal, extra_ptrs=(lse.data_ptr(),))
+    torch.cuda.synchronize()
+    assert rt.device_status() == 0
+    check(o.cpu(), lse.cpu(), q, k, v, 0.11, causal, "fp16")
+
+
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("Lq,Lkv", [(512, 512), (640, 384), (200, 328), (1100, 1100)])
 def test_cta_pair_configuration(causal, Lq, Lkv, tmp_path):

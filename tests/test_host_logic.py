@@ -196,6 +196,17 @@ def test_cta_pair_knob_in_configs_and_search_space():
     src = _create_entry_code(pair)
     assert "FaPairConfig<128, 8, false>" in src and "fa_fwd_pair_launch<Cfg>" in src
     assert "fa_fwd_launch_auto<Cfg>" in _create_entry_code(AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, dv_chunk=128))
+    # the form of the grid is a knob too: chosen per call by default, or forced
+    grid_cfg = AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, dv_chunk=128, persistent=0)
+    pers_cfg = AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, dv_chunk=128, persistent=1)
+    assert "return fa_fwd_launch<Cfg>" in _create_entry_code(grid_cfg)
+    assert "return fa_fwd_persist_launch<Cfg>" in _create_entry_code(pers_cfg)
+    assert at.validate_kernel(grid_cfg) and at.validate_kernel(pers_cfg)
+    assert str(grid_cfg) != str(pers_cfg) != str(AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, dv_chunk=128))
+    assert not at.validate_kernel(AttnConfig(256, 128, 128, 128, q_tiles=2, kv_stages=4, dv_chunk=128, softmax_split=2, persistent=1))
+    assert not at.validate_kernel(AttnConfig(128, 128, 128, 128, q_tiles=1, kv_stages=4, dv_chunk=128, persistent=1))
+    assert any(getattr(c, "persistent", -1) == 1 for c in cfgs) and any(getattr(c, "persistent", -1) == 0 for c in cfgs)
+    assert AttnConfig.from_dict({k: v for k, v in grid_cfg.to_dict().items() if k != "persistent"}).persistent == -1
     rt = RetTunner(B200(), [z, z, zv, None, zv, None], decay=torch.ones(1))
     assert RetConfig(128, 128, 256, 512).cta_pair == 1 and RetConfig(128, 128, 64, 64).cta_pair == 0
     assert not rt.validate_kernel(RetConfig(128, 128, 256, 512, dv_chunk=64, cta_pair=1))
