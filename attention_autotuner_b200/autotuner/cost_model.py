@@ -88,6 +88,15 @@ def features(op: str, cfg: dict, problem: dict) -> np.ndarray:
         stages = cfg.get("kv_stages", 4)
         pair = 1.0 if cfg.get("cta_pair", 0) else 0.0
         tiles = problem["B"] * problem["H"] * np.ceil(problem["Lq"] / 128.0) * passes / SM_COUNT / 1e6
+        # the persistent form of the grid has no per-CTA prologue / epilogue to pay; left to the launcher (-1) it is
+        # taken up to 40 KV blocks per work item on average (csrc/fa_fwd_launch.cuh)
+        persistent = cfg.get("persistent", -1)
+        if persistent == -1 and q_tiles == 2 and chunk <= 128 and split == 1 and not cfg.get("exp_emu", 0) \
+                and not cfg.get("exp_h2", 0) and cfg.get("mma_warps", 1) == 1 and not cfg.get("cta_pair", 0):
+            nblk = np.ceil(problem["Lkv"] / 128.0)
+            persistent = 1 if (np.ceil(nblk / 2.0) if problem.get("causal", False) else nblk) <= 40 else 0
+        if persistent == 1:
+            tiles = 0.0
         return np.array([
             nb * t_tensor,
             nb * t_mufu * (q_tiles == 1),
