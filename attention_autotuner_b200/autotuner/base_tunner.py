@@ -173,10 +173,16 @@ class BaseTunner:
         profile_dict = {}
         latency = 1e8
         best_config = None
+        # Every candidate is timed twice and the second figure kept: loading a library leaves the GPU idle long enough
+        # to cool, and a 100 ms timing loop started on a cool chip reads up to 10 % faster than the same loop on a chip
+        # at its power limit, which favoured whatever was timed first or after a slow load.
+        twice = os.environ.get("ATTN_B200_TUNE_CONFIRM", "1") != "0"
         for cresult in cresults:
             if cresult is None or cresult.lib_name is None:
                 continue
             lib_latency = self.profile(cresult.lib_name)
+            if twice and lib_latency != 1e8:
+                lib_latency = self.profile(cresult.lib_name)
             if lib_latency == 1e8:
                 pprint.pprint(cresult.config)
                 print("profile runtime error")
@@ -184,6 +190,23 @@ class BaseTunner:
                 latency = lib_latency
                 best_config = cresult.config
             profile_dict[cresult.config] = lib_latency
+        # Confirmation pass. A timing loop of 100 ms is long enough for the GPU to reach its power limit, so the
+        # candidates timed first (on a cooler chip) look up to several per cent faster than they are. The candidates
+        # within 4 % of the best (at most six) are therefore timed twice more, in the opposite and then the original
+        # order, and ranked by the median of their three measurements. (The reference times every candidate once,
+        # python/autotuner/base_tunner.py:148-160.)
+        confirm = {}
+        if best_config is not None and os.environ.get("ATTN_B200_TUNE_CONFIRM", "1") != "0":
+            close = sorted((c for c, ms in profile_dict.items() if ms <= 1.04 * latency), key=lambda c: profile_dict[c])[:6]
+            if len(close) > 1:
+                lib_of = {cr.config: cr.lib_name for cr in cresults if cr is not None and cr.lib_name is not None}
+                confirm = {c: [profile_dict[c]] for c in close}
+                for order in (list(reversed(close)), close):
+                    for c in order:
+                        confirm[c].append(self.profile(lib_of[c]))
+                med = {c: sorted(v)[len(v) // 2] for c, v in confirm.items()}
+                best_config = min(close, key=lambda c: med[c])
+                latency = med[best_config]
         end = time.time()
         self.last_results = profile_dict
         if best_config is None:
@@ -219,7 +242,7 @@ class BaseTunner:
                 "results": [{"config": repr(c), "ms": ms,
                              "tflops": (fl / ms / 1e9 if ms < 1e8 else 0.0),
                              "frac_of_peak": (fl / ms / 1e9 / peak if ms < 1e8 and peak else 0.0),
-                             "predicted_ms": predicted.get(c)}
+                             "predicted_ms": predicted.get(c), "confirm_ms": confirm.get(c)}
                             for c, ms in profile_dict.items()],
                 "best": repr(best_config), "best_ms": latency, "search_time_s": end - st,
                 "compile_time_s": t_compile,
