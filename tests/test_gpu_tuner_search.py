@@ -1,0 +1,51 @@
+"""The tile search on a GPU, pruned to the cost model's three best candidates so that it stays short: compile ->
+time (every candidate twice, the near-best three times, ranked by the median) -> log in the reference's text format
+plus its JSON twin -> cache entry, which the next tune() returns without searching
+(reference flow: python/autotuner/base_tunner.py:129-195)."""
+import json
+import os
+
+import pytest
+import torch
+
+from attention_autotuner_b200.arch import B200
+from attention_autotuner_b200.autotuner.tunner import AttnTunner
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def test_pruned_search_writes_log_and_cache_and_the_choice_computes_correctly(tmp_path, monkeypatch):
+    monkeypatch.setenv("ATTN_B200_CACHE_DIR", str(tmp_path / "cache"))
+    monkeypatch.setenv("ATTN_B200_AUTOTUNE", "1")
+    g = torch.Generator().manual_seed(3)
+    q, k, v = (torch.randn(2, 8, 1024, 128, generator=g).half() for _ in range(3))
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    o = torch.empty_like(qd)
+    t = AttnTunner(B200(), [qd, kd, vd, o], scale=128 ** -0.5, causal=True)
+    cfg = t.tune(str(tmp_path / "logs"), top_k=3)
+    cands = {repr(c) for c in t.get_tuned_configs()}
+    assert repr(cfg) in cands
+    stem = tmp_path / "logs" / "profile_result_attn_128_128_sm100a_fp16_causal"
+    text = open(str(stem) + ".txt").read()
+    assert "best config:" in text and "search time:" in text and repr(cfg) in text
+    log = json.load(open(str(stem) + ".json"))
+    assert len(log["results"]) == 3 and log["cost_model"]["pruned_to_top_k"] == 3 and log["cost_model"]["candidates"] == len(cands)
+    confirmed = [r for r in log["results"] if r["confirm_ms"]]
+    assert len(confirmed) >= 2 and all(len(r["confirm_ms"]) == 3 for r in confirmed)
+    best = next(r for r in log["results"] if r["config"] == repr(cfg))
+    assert best["confirm_ms"] and abs(sorted(best["confirm_ms"])[1] - log["best_ms"]) < 1e-9
+    assert all(0 < r["ms"] < 50 and r["tflops"] > 50 for r in log["results"])
+    # the cache entry: no path inside, and the next tune() returns it without a search
+    cache_file = tmp_path / "cache" / "best_config_attention_128_128_sm100a_fp16_causal.json"
+    entry = json.load(open(cache_file))
+    assert not any(isinstance(val, str) and os.sep in val for val in entry.values())
+    t2 = AttnTunner(B200(), [qd, kd, vd, o], scale=128 ** -0.5, causal=True)
+    assert repr(t2.tune(search=False)) == repr(cfg)
+    # and the chosen configuration computes the right thing
+    from attention_autotuner_b200.autotuner.runtime import Runtime
+    lse = torch.empty(2, 8, 1024, device="cuda")
+    Runtime(B200(), cfg).apply([qd, kd, vd, o], scale=128 ** -0.5, causal=True, extra_ptrs=(lse.data_ptr(),))
+    torch.cuda.synchronize()
+    oref, _ = oracle.attention_fwd(q, k, v, 128 ** -0.5, True)
+    assert oracle.within(oracle.error_stats(o.cpu(), oref), "fp16")
