@@ -64,6 +64,10 @@ def _declare(lib):
     lib.attn_b200_selftest_pair.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, vp]
     lib.attn_b200_ret_chunk_fwd.restype = ci
     lib.attn_b200_ret_chunk_fwd.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, cf, vp]
+    lib.attn_b200_ret_chunk_workspace_bytes.restype = ctypes.c_size_t
+    lib.attn_b200_ret_chunk_workspace_bytes.argtypes = [ci, ci, ci, ci, ci, ci]
+    lib.attn_b200_ret_chunk_fwd_ws.restype = ci
+    lib.attn_b200_ret_chunk_fwd_ws.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.c_size_t, ci, ci, ci, ci, ci, ci, ci, cf, vp]
     lib.attn_b200_selftest_wait.restype = ci
     lib.attn_b200_selftest_wait.argtypes = [ci, ci, vp]
     for name, sig in _OPTIONAL.items():

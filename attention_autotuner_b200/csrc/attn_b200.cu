@@ -287,6 +287,25 @@ int attn_b200_ret_chunk_fwd(const void* q, const void* k, const void* v, const f
   return dtype == ATTN_B200_BF16 ? ret_chunk_dispatch<true>(a, st) : ret_chunk_dispatch<false>(a, st);
 }
 
+size_t attn_b200_ret_chunk_workspace_bytes(int B, int H, int L, int dqk, int dv, int segments) {
+  if (B <= 0 || H <= 0 || L <= 0 || dqk <= 0 || dv <= 0 || segments < 0) return 0;
+  const int g = segments > 0 ? segments : ret_chunk_preferred_segments(B * H, L, dv);
+  return ret_chunk_workspace_bytes(B * H, L, dqk, dv, g);
+}
+
+int attn_b200_ret_chunk_fwd_ws(const void* q, const void* k, const void* v, const float* decay, void* o, void* workspace,
+                               size_t workspace_bytes, int segments, int B, int H, int L, int dqk, int dv, int dtype, float scale,
+                               void* stream) {
+  if (B <= 0 || H <= 0) return fail(kErrInvalidArgument, "ret_chunk_fwd: B and H must be positive");
+  if (dtype != ATTN_B200_F16 && dtype != ATTN_B200_BF16) return fail(kErrInvalidArgument, "ret_chunk_fwd: dtype %d", dtype);
+  RetChunkArgs a{q, k, v, decay, o, B * H, H, L, dqk, dv, scale};
+  a.workspace = workspace;
+  a.workspace_bytes = workspace ? workspace_bytes : 0;
+  a.segments = segments;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return dtype == ATTN_B200_BF16 ? ret_chunk_dispatch<true>(a, st) : ret_chunk_dispatch<false>(a, st);
+}
+
 int attn_b200_selftest_gemm_ss(const void* a, const void* b, float* d, int N, int K, int dtype, void* stream) {
   return selftest_gemm_ss(a, b, d, N, K, dtype, reinterpret_cast<cudaStream_t>(stream));
 }

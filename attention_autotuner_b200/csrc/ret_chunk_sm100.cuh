@@ -32,6 +32,12 @@
 // a share of the K tile), warp 4 issues every MMA (converged warp, one elected lane; a single issuer keeps all
 // tensor-memory hazards in program order), warp 5 lane 0 is the TMA producer. Tensor memory: Z at [0,128), ACC at
 // [128,128+DVC), the state halves (dqk rows 0-127, 128-255) at [256,256+DVC) and [384,384+DVC).
+//
+// Few slices, long sequences: a walk in order leaves most SMs idle (a grid of BH * dv / DVC CTAs is all the parallelism
+// there is). With scratch memory the sequence is cut into segments of `seg` chunks (blockIdx.z): a first kernel
+// (ret_chunk_state_sm100_kernel) computes, for every segment but the last, the state that segment alone would leave
+// behind (T_g = sum_c g^(last - c) K_c'^T V_c, fp32, one tile per CTA), and this kernel starts segment g > 0 from
+// S = sum_{g' < g} gamma^(128 seg (g - 1 - g')) T_g', which is the state the walk in order would have carried there.
 #pragma once
 
 #include "chain_common.cuh"
@@ -43,6 +49,8 @@ struct RetChunkParams {
   const float* decay;    // [H] gammas
   int H, L, dv;
   float scale;
+  float* ws;             // segment states, [BH][dv / DVC][segments - 1][dqk / 128][DVC][128] fp32; null when gridDim.z == 1
+  int seg;               // chunks per segment (>= number of chunks when the sequence is walked in one piece)
 };
 
 template <int DQK_, int DVC_, bool BF16_>
@@ -69,7 +77,7 @@ struct RetChunkConfig {
 
 enum RetChunkTag : int {
   kRcQ = 51, kRcK = 52, kRcV = 53, kRcQFree = 54, kRcKVFree = 55, kRcZ = 56, kRcW = 57, kRcAcc = 58, kRcAccFree = 59,
-  kRcU = 60, kRcState = 61, kRcY = 62, kRcKScaled = 63
+  kRcU = 60, kRcState = 61, kRcY = 62, kRcKScaled = 63, kRsFull = 64, kRsEmpty = 65, kRsScaled = 66, kRsDone = 67
 };
 
 template <class Cfg>
@@ -106,7 +114,12 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const int lane = threadIdx.x & 31;
   const int bh = blockIdx.y;
   const int n_off = blockIdx.x * DVC;
-  const int nchunk = (p.L + 127) / 128;
+  const int nchunk_all = (p.L + 127) / 128;
+  const int seg_id = blockIdx.z;
+  const int c_begin = seg_id * p.seg;                         // first chunk of this CTA's segment
+  const int nchunk = min(nchunk_all - c_begin, p.seg);        // chunks this CTA walks (local index c below)
+  const bool init = seg_id > 0;                               // starts from the state the earlier segments leave behind
+  const uint32_t sb = init ? 1u : 0u;                         // that state is one more arrival on s_ready / y_done
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -152,27 +165,27 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         if (!ok) break;
         mbar_expect_tx(q_full, Cfg::QK_BYTES);
 #pragma unroll
-        for (int b = 0; b < KB; ++b) tma_load_3d(sQ + b * BOX, &tmQ, q_full, b * 64, c * 128, bh);
+        for (int b = 0; b < KB; ++b) tma_load_3d(sQ + b * BOX, &tmQ, q_full, b * 64, (c_begin + c) * 128, bh);
         ++nq;
         if (c > 0) ok = mbar_wait(kv_free, (c - 1) & 1, ab, kRcKVFree);
         if (!ok) break;
         mbar_expect_tx(k_full, Cfg::QK_BYTES);
 #pragma unroll
-        for (int b = 0; b < KB; ++b) tma_load_3d(sK + b * BOX, &tmK, k_full, b * 64, c * 128, bh);
+        for (int b = 0; b < KB; ++b) tma_load_3d(sK + b * BOX, &tmK, k_full, b * 64, (c_begin + c) * 128, bh);
         mbar_expect_tx(v_full, Cfg::V_BYTES);
 #pragma unroll
-        for (int b = 0; b < VB; ++b) tma_load_3d(sV + b * BOX, &tmV, v_full, n_off + b * 64, c * 128, bh);
+        for (int b = 0; b < VB; ++b) tma_load_3d(sV + b * BOX, &tmV, v_full, n_off + b * 64, (c_begin + c) * 128, bh);
         ++nkv;
         if (c + 1 < nchunk) {
           // the buffers are single (shared memory is full at dqk = 256), so the next chunk's loads start only when this
           // chunk's MMAs have released them: ask the L2 for those tiles now, so that they come from L2 rather than HBM
 #pragma unroll
           for (int b = 0; b < KB; ++b) {
-            tma_prefetch_3d(&tmQ, b * 64, (c + 1) * 128, bh);
-            tma_prefetch_3d(&tmK, b * 64, (c + 1) * 128, bh);
+            tma_prefetch_3d(&tmQ, b * 64, (c_begin + c + 1) * 128, bh);
+            tma_prefetch_3d(&tmK, b * 64, (c_begin + c + 1) * 128, bh);
           }
 #pragma unroll
-          for (int b = 0; b < VB; ++b) tma_prefetch_3d(&tmV, n_off + b * 64, (c + 1) * 128, bh);
+          for (int b = 0; b < VB; ++b) tma_prefetch_3d(&tmV, n_off + b * 64, (c_begin + c + 1) * 128, bh);
         }
       }
       if (!ok) {
@@ -206,10 +219,11 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tc_commit(z_full);
       }
       __syncwarp();
-      if (c > 0) {
+      const bool carried = c > 0 || init;
+      if (carried) {
         // the carried state: its 16-bit copy is in shared memory and ACC of the previous chunk has been read
-        ok = mbar_wait_warp(s_ready, (c - 1) & 1, ab, kRcState);
-        if (ok) ok = mbar_wait_warp(acc_free, (c - 1) & 1, ab, kRcAccFree);
+        ok = mbar_wait_warp(s_ready, (c - 1 + sb) & 1, ab, kRcState);
+        if (ok && c > 0) ok = mbar_wait_warp(acc_free, (c - 1) & 1, ab, kRcAccFree);
         if (!ok) break;
         tc_fence_after();
         if (elect_one()) {
@@ -237,7 +251,7 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
             umma_ss(tS + h * 128, umma_smem_desc(k_addr + (2 * h) * BOX + ks * 2048, BOX, 1024),
-                    umma_smem_desc(v_addr + ks * 2048, BOX, 1024), idesc_u, (c > 0 || ks > 0) ? 1u : 0u);
+                    umma_smem_desc(v_addr + ks * 2048, BOX, 1024), idesc_u, (carried || ks > 0) ? 1u : 0u);
         }
         tc_commit(u_done);
       }
@@ -248,7 +262,7 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_ts(tACC, tZ + ks * 8, umma_smem_desc(v_addr + ks * 2048, BOX, 1024), idesc_y, (c > 0 || ks > 0) ? 1u : 0u);
+          umma_ts(tACC, tZ + ks * 8, umma_smem_desc(v_addr + ks * 2048, BOX, 1024), idesc_y, (carried || ks > 0) ? 1u : 0u);
         tc_commit(acc_done);
         tc_commit(kv_free);
       }
@@ -268,7 +282,59 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const uint64_t sc2 = f2_pack(p.scale, p.scale);
     const uint32_t tz = tmem_addr(tZ, lane_base, 0);
     const uint32_t ta = tmem_addr(tACC, lane_base, 0);
+    // 32 columns of row `tid` of state half hh, fp32 in rr: 16-bit copy into shared memory (operand of the next Q S; four
+    // 16-byte groups of the row's 128-byte line in box c0 / 64, 128-byte swizzle), and g * S into tensor memory, where
+    // the next chunk's K^T V is added
+    auto put_state = [&](int hh, int c0, uint32_t (&rr)[32]) {
+      uint8_t* box = sSb + hh * Cfg::SB_HALF_BYTES + tid * 128 + (c0 >> 6) * BOX;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint4 v;
+        v.x = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 0]), __uint_as_float(rr[q4 * 8 + 1]));
+        v.y = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 2]), __uint_as_float(rr[q4 * 8 + 3]));
+        v.z = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 4]), __uint_as_float(rr[q4 * 8 + 5]));
+        v.w = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 6]), __uint_as_float(rr[q4 * 8 + 7]));
+        const int chunk16 = ((c0 & 63) >> 3) + q4;
+        *reinterpret_cast<uint4*>(box + ((chunk16 ^ (tid & 7)) << 4)) = v;
+      }
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float x0, x1;
+        f2_unpack(fmul2(f2_pack(__uint_as_float(rr[i]), __uint_as_float(rr[i + 1])), g2), x0, x1);
+        rr[i] = __float_as_uint(x0);
+        rr[i + 1] = __float_as_uint(x1);
+      }
+      tmem_st32(tmem_addr(tS + hh * 128, lane_base, 0) + c0, rr);
+    };
     bool ok = true;
+    if (init) {
+      // ---- the state the earlier segments leave behind: T_g' carried over the segments between g' and this one
+      const float* ws_tile = p.ws + (static_cast<size_t>(bh) * gridDim.x + blockIdx.x) * (gridDim.z - 1) * (DQK * DVC);
+#pragma unroll 1
+      for (int hh = 0; hh < NH; ++hh) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < DVC; c0 += 32) {
+          float acc[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+          for (int gp = seg_id - 1; gp >= 0; --gp) {
+            const float f = exp2f(128.0f * p.seg * (seg_id - 1 - gp) * lg);
+            if (f == 0.f) break;  // the same for every thread; earlier segments weigh even less
+            const float* src = ws_tile + (static_cast<size_t>(gp) * NH + hh) * (DVC * 128) + c0 * 128 + tid;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = fmaf(f, src[i * 128], acc[i]);
+          }
+          uint32_t rr[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) rr[i] = __float_as_uint(acc[i]);
+          put_state(hh, c0, rr);
+        }
+      }
+      tc_wait_st();
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(s_ready);
+    }
     for (int c = 0; c < nchunk && ok; ++c) {
       const uint32_t ph = c & 1;
       // ---- W = Z .* gamma^(i-j), keys after the row's own position removed (the forward flavour of the chain kernels'
@@ -310,8 +376,8 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         chain_ew_decay2<kChainFwd, BF16, 2, false>(tz, row_decay, lg, 0.f, 0.f, true, tid, unused_sum);
       }
       // ---- the carried term Q S, now in ACC, seen from row i: times gamma^(i+1)
-      if (c > 0) {
-        ok = mbar_wait_warp(y_done, (c - 1) & 1, ab, kRcY);
+      if (c > 0 || init) {
+        ok = mbar_wait_warp(y_done, (c - 1 + sb) & 1, ab, kRcY);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -341,32 +407,12 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 #pragma unroll
         for (int hh = 0; hh < NH; ++hh) {
           const uint32_t ts = tmem_addr(tS + hh * 128, lane_base, 0);
-          uint8_t* srow = sSb + hh * Cfg::SB_HALF_BYTES + tid * 128;  // row `tid` of every 64-column box
 #pragma unroll
           for (int c0 = 0; c0 < DVC; c0 += 32) {
             uint32_t rr[32];
             tmem_ld32(ts + c0, rr);
             tc_wait_ld();
-            // 32 columns = four 16-byte groups of the row's 128-byte line in box c0 / 64 (128-byte swizzle)
-            uint8_t* box = srow + (c0 >> 6) * BOX;
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              uint4 v;
-              v.x = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 0]), __uint_as_float(rr[q4 * 8 + 1]));
-              v.y = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 2]), __uint_as_float(rr[q4 * 8 + 3]));
-              v.z = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 4]), __uint_as_float(rr[q4 * 8 + 5]));
-              v.w = pack2<BF16>(__uint_as_float(rr[q4 * 8 + 6]), __uint_as_float(rr[q4 * 8 + 7]));
-              const int chunk16 = ((c0 & 63) >> 3) + q4;
-              *reinterpret_cast<uint4*>(box + ((chunk16 ^ (tid & 7)) << 4)) = v;
-            }
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              float x0, x1;
-              f2_unpack(fmul2(f2_pack(__uint_as_float(rr[i]), __uint_as_float(rr[i + 1])), g2), x0, x1);
-              rr[i] = __float_as_uint(x0);
-              rr[i + 1] = __float_as_uint(x1);
-            }
-            tmem_st32(ts + c0, rr);
+            put_state(hh, c0, rr);
           }
         }
         tc_wait_st();
@@ -379,7 +425,7 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       if (!ok) break;
       tc_fence_after();
       {
-        const int row = c * 128 + tid;
+        const int row = (c_begin + c) * 128 + tid;
         uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (static_cast<size_t>(bh) * p.L + row) * p.dv + n_off;
 #pragma unroll
         for (int c0 = 0; c0 < DVC; c0 += 32) {
@@ -415,6 +461,179 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   if (warp == 4) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// State of one segment taken alone: T = sum over the segment's chunks c and positions j of
+// gamma^(127 - j + 128 (last - c)) k_j v_j^T, which is what the walk in order would add to its state over these
+// chunks. The whole decay sits on the rows of K (scaled in place in shared memory, like the state update of the kernel
+// above), so the accumulator in tensor memory is touched by nothing but the MMAs: a row whose factor underflows in
+// 16 bits is a contribution that small. Grid (dv / DVC, BH, segments - 1); K and V tiles in a ring of two. Warps 0-3
+// scale the K rows, warp 4 issues the MMAs, warp 5 lane 0 is the TMA producer. Output: fp32, [state half][column][row]
+// per CTA, so that both this kernel's stores and the consumer's loads (a thread per state row) are coalesced.
+template <class Cfg>
+struct RetChunkStateLayout {
+  static constexpr int STAGE_BYTES = Cfg::QK_BYTES + Cfg::V_BYTES;
+  static constexpr int SMEM_TILES = 2 * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = 1024 + SMEM_TILES + 512;
+  static constexpr int TMEM_COLS = 256;
+  static_assert(SMEM_BYTES <= 232448, "shared memory");
+  static_assert(Cfg::NH * 128 <= TMEM_COLS, "tensor memory");
+};
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::NTHREADS, 1)
+ret_chunk_state_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                             const RetChunkParams p) {
+  using Lay = RetChunkStateLayout<Cfg>;
+  constexpr int DQK = Cfg::DQK, DVC = Cfg::DVC, NH = Cfg::NH, KB = Cfg::KB, VB = Cfg::VB, BOX = Cfg::BOX_BYTES;
+  constexpr bool BF16 = Cfg::BF16;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Lay::SMEM_TILES);
+  uint64_t* kv_full = bars + 0;    // [2] K and V of a chunk landed                    (TMA -> element-wise, MMA)
+  uint64_t* kv_empty = bars + 2;   // [2] the chunk's MMAs complete                     (MMA -> TMA)
+  uint64_t* k_scaled = bars + 4;   // [2] rows of the K tile scaled in place            (element-wise -> MMA), 128 arrivals
+  uint64_t* s_done = bars + 6;     // every MMA of the segment complete                 (MMA -> element-wise)
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 1);
+
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
+  const int lane = threadIdx.x & 31;
+  const int bh = blockIdx.y;
+  const int n_off = blockIdx.x * DVC;
+  const int c_begin = blockIdx.z * p.seg;
+  const int nchunk = p.seg;  // every segment but the last is whole
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(kv_full + s, 1);
+      mbar_init(kv_empty + s, 1);
+      mbar_init(k_scaled + s, 128);
+    }
+    mbar_init(s_done, 1);
+    ab->flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(tmem_base_slot, Lay::TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 5 && lane == 0) {
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 5) {
+    if (lane == 0) {
+      bool ok = true;
+      int nload = 0;
+      for (int c = 0; c < nchunk && ok; ++c) {
+        const int s = c & 1;
+        if (c >= 2) ok = mbar_wait(kv_empty + s, ((c >> 1) - 1) & 1, ab, kRsEmpty);
+        if (!ok) break;
+        uint8_t* sK = smem + s * Lay::STAGE_BYTES;
+        uint8_t* sV = sK + Cfg::QK_BYTES;
+        mbar_expect_tx(kv_full + s, Lay::STAGE_BYTES);
+#pragma unroll
+        for (int b = 0; b < KB; ++b) tma_load_3d(sK + b * BOX, &tmK, kv_full + s, b * 64, (c_begin + c) * 128, bh);
+#pragma unroll
+        for (int b = 0; b < VB; ++b) tma_load_3d(sV + b * BOX, &tmV, kv_full + s, n_off + b * 64, (c_begin + c) * 128, bh);
+        ++nload;
+      }
+      if (!ok) {
+        // abort path: let the copies already issued land before this CTA's shared memory is released
+        if (nload > 0) mbar_wait_drain(kv_full + ((nload - 1) & 1), ((nload - 1) >> 1) & 1, 2000000ull);
+        if (nload > 1) mbar_wait_drain(kv_full + ((nload - 2) & 1), ((nload - 2) >> 1) & 1, 2000000ull);
+      }
+    }
+  } else if (warp == 4) {
+    constexpr uint32_t idesc_u = umma_idesc(128, DVC, BF16, true, true);  // K^T V: A and B MN-major
+    bool ok = true;
+    for (int c = 0; c < nchunk && ok; ++c) {
+      const int s = c & 1;
+      const uint32_t ph = (c >> 1) & 1;
+      ok = mbar_wait_warp(kv_full + s, ph, ab, kRsFull);
+      if (ok) ok = mbar_wait_warp(k_scaled + s, ph, ab, kRsScaled);
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint32_t k_addr = smem_u32(smem + s * Lay::STAGE_BYTES), v_addr = k_addr + Cfg::QK_BYTES;
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_ss(tmem_base + h * 128, umma_smem_desc(k_addr + (2 * h) * BOX + ks * 2048, BOX, 1024),
+                    umma_smem_desc(v_addr + ks * 2048, BOX, 1024), idesc_u, (c > 0 || ks > 0) ? 1u : 0u);
+        }
+        tc_commit(kv_empty + s);
+        if (c + 1 == nchunk) tc_commit(s_done);
+      }
+      __syncwarp();
+    }
+  } else {
+    const int tid = threadIdx.x;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32);
+    const float lg = log2f(p.decay[bh % p.H]);
+    bool ok = true;
+    for (int c = 0; c < nchunk && ok; ++c) {
+      const int s = c & 1;
+      ok = mbar_wait_warp(kv_full + s, (c >> 1) & 1, ab, kRsFull);
+      if (!ok) break;
+      uint8_t* sK = smem + s * Lay::STAGE_BYTES;
+      const int later = 128 * (nchunk - 1 - c);  // positions of the segment after this chunk
+      // shared by address (lane l: line l / 8, 16-byte group l % 8), free of bank conflicts
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int krow_idx = warp * 32 + it * 4 + (lane >> 3);
+        const float kf = exp2f((127 - krow_idx + later) * lg);
+        const uint64_t kr2 = f2_pack(kf, kf);
+#pragma unroll
+        for (int b = 0; b < KB; ++b) {
+          uint4* ptr = reinterpret_cast<uint4*>(sK + b * BOX + krow_idx * 128 + (lane & 7) * 16);
+          uint4 u = *ptr;
+          uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float lo, hi;
+            f2_unpack(fmul2(chain_unpack_pair<BF16>(w[e]), kr2), lo, hi);
+            w[e] = pack2<BF16>(lo, hi);
+          }
+          *ptr = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(k_scaled + s);
+    }
+    if (ok) ok = mbar_wait_warp(s_done, 0, ab, kRsDone);
+    if (ok) {
+      tc_fence_after();
+      float* dst = p.ws + ((static_cast<size_t>(bh) * gridDim.x + blockIdx.x) * gridDim.z + blockIdx.z) * (DQK * DVC) + tid;
+#pragma unroll 1
+      for (int hh = 0; hh < NH; ++hh) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < DVC; c0 += 32) {
+          uint32_t rr[32];
+          tmem_ld32(tmem_addr(tmem_base + hh * 128, lane_base, 0) + c0, rr);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) dst[(hh * DVC + c0 + i) * 128] = __uint_as_float(rr[i]);
+        }
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Lay::TMEM_COLS);
   }
 }
 

@@ -88,7 +88,9 @@ def retnet_chunkwise(q, k, v, decay, device_type: Arch = None, scale=None):
     """Chunkwise (recurrent-state) RetNet forward: o[i] = scale * sum_{j <= i} decay_h^(i-j) (q_i . k_j) v_j, the
     unnormalised retention of the reference's recurrent kernel (csrc/kernels/retnet/recurrent/recurrent.h:427-463),
     evaluated chunk by chunk with the state in tensor memory: the cost grows with L, not L^2. Forward only.
-    q, k [B,H,L,dqk] (dqk 128 or 256), v [B,H,L,dv], fp16 or bf16 on one CUDA device; ``decay``: H per-head gammas."""
+    q, k [B,H,L,dqk] (dqk 128 or 256), v [B,H,L,dv], fp16 or bf16 on one CUDA device; ``decay``: H per-head gammas.
+    With few (batch, head) slices and a long sequence the library cuts the sequence into segments that run at once
+    (attn_b200_ret_chunk_fwd_ws); the scratch for the segment states is allocated here."""
     import ctypes
 
     from .. import _lib
@@ -107,9 +109,11 @@ def retnet_chunkwise(q, k, v, decay, device_type: Arch = None, scale=None):
     P = lambda t: ctypes.c_void_p(t.data_ptr())
     with torch.cuda.device(q.device):
         stream = ctypes.c_void_p(torch.cuda.current_stream(q.device).cuda_stream)
-        _lib.check(lib.attn_b200_ret_chunk_fwd(P(q), P(k), P(v), P(decayd), P(o), B, H, L, dqk, dv,
-                                               0 if q.dtype == torch.float16 else 1, 1.0 if scale is None else float(scale),
-                                               stream))
+        ws_bytes = int(lib.attn_b200_ret_chunk_workspace_bytes(B, H, L, dqk, dv, 0))
+        ws = torch.empty(ws_bytes, device=q.device, dtype=torch.uint8) if ws_bytes else None
+        _lib.check(lib.attn_b200_ret_chunk_fwd_ws(P(q), P(k), P(v), P(decayd), P(o), P(ws) if ws_bytes else None, ws_bytes, 0,
+                                                  B, H, L, dqk, dv, 0 if q.dtype == torch.float16 else 1,
+                                                  1.0 if scale is None else float(scale), stream))
     return o
 
 

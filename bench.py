@@ -288,6 +288,11 @@ class Runner:
         self.mask = self.decay = self.do = None
         if self.chunk:
             self.gam = (1.0 - torch.pow(2.0, -5.0 - torch.arange(H, dtype=torch.float64))).float().to(dev)
+            # few slices and a long sequence: scratch for the segment states, so that the sequence is cut into segments
+            # that run at once (one more launch: the kernel that computes the segment states)
+            self.ws_bytes = int(self.lib.attn_b200_ret_chunk_workspace_bytes(B, H, Lq, dqk, dv, 0))
+            self.ws = torch.empty(max(self.ws_bytes, 16), device=dev, dtype=torch.uint8)
+            self.launches = 2 if self.ws_bytes else 1
         elif self.ret:
             WH = WORKLOADS[name][1]
             self.gam = (1.0 - torch.pow(2.0, -5.0 - torch.arange(WH, dtype=torch.float64))).float().to(dev)
@@ -317,8 +322,8 @@ class Runner:
         B, H, Lq, Lkv, dqk, dv = self.shape
         lib, chk = self.lib, self._lib.check
         if self.chunk:
-            chk(lib.attn_b200_ret_chunk_fwd(P(self.q), P(self.k), P(self.v), P(self.gam), P(self.o), B, H, Lq, dqk, dv, self.code,
-                                            self.scale, self.sp))
+            chk(lib.attn_b200_ret_chunk_fwd_ws(P(self.q), P(self.k), P(self.v), P(self.gam), P(self.o), P(self.ws), self.ws_bytes, 0,
+                                               B, H, Lq, dqk, dv, self.code, self.scale, self.sp))
         elif self.ret:
             chk(lib.attn_b200_ret_fwd(P(self.q), P(self.k), P(self.v), P(self.mask), P(self.o), P(self.r), B, H, Lq, Lkv, dqk,
                                       dv, self.code, self.scale, P(self.decay), 1, self.sp))

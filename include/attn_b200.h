@@ -183,6 +183,23 @@ int attn_b200_ret_chunk_fwd(const void* q, const void* k, const void* v, const f
                             int dqk, int dv, int dtype, float scale, void* stream);
 
 /*
+ * The same function with scratch memory, for few (batch, head) slices and long sequences, where a walk in order leaves
+ * most SMs idle: the sequence is cut into segments; a first kernel computes the state every segment but the last leaves
+ * behind on its own (fp32, one [dqk x dv] tile per slice and segment), then all segments run at once, each starting from
+ * the decayed sum of the states before it. Same result as the walk in order up to rounding (the segment states are
+ * exact fp32 sums of the same 16-bit products; the decay over a segment sits on the rows of K).
+ *   segments = 0: the library chooses (as many as fill the SMs and the workspace holds; 1, the walk in order, when the
+ *                 slices alone fill the GPU or workspace is null);  n > 0: min(n, chunks of 128) segments, an error
+ *                 if the workspace is too small for them.
+ *   attn_b200_ret_chunk_workspace_bytes: bytes for `segments` (0: for the library's choice; may be 0).
+ * No counterpart in the reference (its recurrent kernel scans each (k, v) dimension pair over the whole sequence).
+ */
+size_t attn_b200_ret_chunk_workspace_bytes(int B, int H, int L, int dqk, int dv, int segments);
+int attn_b200_ret_chunk_fwd_ws(const void* q, const void* k, const void* v, const float* decay, void* o, void* workspace,
+                               size_t workspace_bytes, int segments, int B, int H, int L, int dqk, int dv, int dtype, float scale,
+                               void* stream);
+
+/*
  * Building-block self tests (single CTA, used by the test-suite to pin the tcgen05 / TMA descriptors):
  *   ss: d[128,N] = a[128,K] * b[N,K]^T       K in {64,128,192,256}, N multiple of 32, N*K <= 32768
  *   ts: d[128,N] = p[128,128] * v[128,N]     N in {64,128,192,256}

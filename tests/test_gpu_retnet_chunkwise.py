@@ -118,6 +118,82 @@ def test_long_sequence_full_slice(lib):
     assert oracle.report("chunkwise L=16384", oracle.error_stats(o1, ref), "fp16", scale_by_peak=True)
 
 
+def run_segments(lib, q, k, v, gam, scale, segments, poison=True):
+    """Through the entry point with scratch memory; the scratch starts as NaNs, so a tile read before it is written shows."""
+    B, H, L, dqk = q.shape
+    dv = v.shape[3]
+    code = 0 if q.dtype == torch.float16 else 1
+    qd, kd, vd, gd = q.cuda(), k.cuda(), v.cuda(), gam.float().cuda()
+    o = torch.full((B, H, L, dv), float("nan"), device="cuda", dtype=q.dtype)
+    nbytes = lib.attn_b200_ret_chunk_workspace_bytes(B, H, L, dqk, dv, segments)
+    ws = torch.full((max(nbytes, 16) // 4,), float("nan"), device="cuda")
+    _lib.check(lib.attn_b200_ret_chunk_fwd_ws(P(qd), P(kd), P(vd), P(gd), P(o), P(ws), nbytes, segments, B, H, L, dqk, dv, code,
+                                              scale, None))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    return o.cpu(), nbytes
+
+
+@pytest.mark.parametrize("dqk,dv,dt", [(128, 128, torch.float16), (256, 512, torch.float16), (256, 192, torch.bfloat16),
+                                        (128, 64, torch.float16)])
+def test_segments_run_at_once(lib, dqk, dv, dt):
+    """The sequence cut into 2, 3, 4 and 9 segments (nine chunks, the last one ragged; a segment of one chunk included)
+    against the oracle, to the tolerance of the walk in order, and close to the walk in order itself; one segment is
+    the walk in order bit for bit."""
+    H, L = 3, 1100
+    q, k, v = rand(dqk + dv + 1, 1, H, L, dqk, dv, dt)
+    gam = torch.tensor([0.9, 0.984375, 1.0], dtype=torch.float64)   # fast decay, the usual one, none
+    scale = dqk ** -0.5
+    name = "fp16" if dt == torch.float16 else "bf16"
+    ref = oracle.retnet_retention(q, k, v, gam, scale)
+    seq = run_chunk(lib, q, k, v, gam, scale)
+    one, nb = run_segments(lib, q, k, v, gam, scale, 1)
+    assert nb == 0 and torch.equal(one, seq)
+    for segments in (2, 3, 4, 9, 50):
+        o, nb = run_segments(lib, q, k, v, gam, scale, segments)
+        count = min(segments, 9)
+        count = -(-9 // -(-9 // count))
+        assert nb == (count - 1) * H * dqk * dv * 4
+        assert oracle.report(f"chunkwise {segments} segments dqk={dqk} dv={dv}", oracle.error_stats(o, ref), name, scale_by_peak=True)
+        assert oracle.report(f"chunkwise {segments} segments vs in order", oracle.error_stats(o, seq.float()), name, scale_by_peak=True)
+
+
+def test_segments_chosen_by_the_library(lib):
+    """Two slices of 4096 positions: the library asks for scratch and cuts the sequence; with no scratch, or too little
+    for two segments, it walks in order; the operator allocates the scratch itself. Reruns are bit-identical."""
+    from attention_autotuner_b200.ops.retnet_interface import retnet_chunkwise
+    B, H, L, dqk, dv = 1, 2, 4096, 256, 256
+    q, k, v = rand(31, B, H, L, dqk, dv)
+    gam = torch.tensor([0.96875, 0.998], dtype=torch.float64)
+    ref = oracle.retnet_retention(q, k, v, gam, 1 / 16)
+    o1, nb = run_segments(lib, q, k, v, gam, 1 / 16, 0)
+    assert nb == 7 * B * H * dqk * dv * 4          # 4 tiles of 128 columns, 32 chunks: 8 segments of 4 chunks
+    o2, _ = run_segments(lib, q, k, v, gam, 1 / 16, 0)
+    assert torch.equal(o1, o2)
+    assert oracle.report("chunkwise, library's segments", oracle.error_stats(o1, ref), "fp16", scale_by_peak=True)
+    seq = run_chunk(lib, q, k, v, gam, 1 / 16)
+    assert not torch.equal(o1, seq)                # another order of rounding: the segments did run
+    a = retnet_chunkwise(q.cuda(), k.cuda(), v.cuda(), gam, B200(), scale=1 / 16)
+    assert torch.equal(a.cpu(), o1)
+    # no scratch, or too little for two segments: the walk in order
+    qd, kd, vd, gd = q.cuda(), k.cuda(), v.cuda(), gam.float().cuda()
+    for ws, nbytes in ((None, 0), (torch.empty(1024, device="cuda"), 4096)):
+        o = torch.empty(B, H, L, dv, device="cuda", dtype=q.dtype)
+        _lib.check(lib.attn_b200_ret_chunk_fwd_ws(P(qd), P(kd), P(vd), P(gd), P(o), P(ws), nbytes, 0, B, H, L, dqk, dv, 0, 1 / 16, None))
+        torch.cuda.synchronize()
+        assert torch.equal(o.cpu(), seq)
+    # many slices: no scratch wanted
+    assert lib.attn_b200_ret_chunk_workspace_bytes(8, 8, 2048, 256, 512, 0) == 0
+    # segments asked for by number and scratch too small: an error, nothing launched
+    o = torch.empty(B, H, L, dv, device="cuda", dtype=q.dtype)
+    small = torch.empty(1024, device="cuda")
+    assert lib.attn_b200_ret_chunk_fwd_ws(P(qd), P(kd), P(vd), P(gd), P(o), P(small), 4096, 4, B, H, L, dqk, dv, 0, 1 / 16, None) == 1
+    assert "scratch" in lib.attn_b200_last_error().decode()
+    assert lib.attn_b200_ret_chunk_fwd_ws(P(qd), P(kd), P(vd), P(gd), P(o), None, 0, -1, B, H, L, dqk, dv, 0, 1 / 16, None) == 1
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+
+
 def test_argument_errors(lib):
     x = torch.zeros(1, 1, 128, 128, device="cuda", dtype=torch.float16)
     d = torch.ones(1, device="cuda")
