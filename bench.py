@@ -391,7 +391,8 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     B, H, Lq, Lkv, dqk, dv, dtype, causal = WORKLOADS[args.workload]
     opname = "RetNet parallel " + RETNET[args.workload] + " (decay mask)" if args.workload in RETNET else (
-        "flash-attention forward + backward" if args.workload in ATTN_BWD else "flash-attention forward")
+        "flash-attention forward + backward" if args.workload in ATTN_BWD else
+        "RetNet chunkwise forward (per-head decay)" if args.workload in CHUNKWISE else "flash-attention forward")
     config = {"workload": f"{args.workload}: {opname} B={B} H={H} Lq={Lq} Lkv={Lkv} dqk={dqk} dv={dv} "
                           f"{dtype} causal={causal} scale=1/sqrt(dqk), per GPU",
               "slices_per_gpu": B * H, "sharding": "(batch, head) slices, no collective",
