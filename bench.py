@@ -642,7 +642,7 @@ def main():
                          "frac": achieved / peak_tf, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                          "peak_source": f"{peak_src} (cuBLAS bf16 burst; the timed region is a burst of a few tens of ms; "
                                         "for the fraction of the sustained peak see workloads.*.sustained)",
-                         "flops_per_step": fl_gpu, "launches_per_step": 4 if (args.workload in ATTN_BWD or ret == "fwd+bwd") else 1,
+                         "flops_per_step": fl_gpu, "launches_per_step": run.launches,
                          "kernel": kernel_of(args.workload)},
             "clocks": clocks,
             "gpu_launches": gpu_launches,
