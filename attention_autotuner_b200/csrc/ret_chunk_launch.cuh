@@ -97,7 +97,7 @@ int ret_chunk_launch(const RetChunkArgs& a, cudaStream_t stream, int segments = 
     cudaError_t es = cudaFuncSetAttribute(state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay::SMEM_BYTES);
     if (es != cudaSuccess) return fail(kErrCuda, "ret_chunk_fwd: cudaFuncSetAttribute: %s", cudaGetErrorString(es));
     dim3 sgrid(a.dv / DVC, a.BH, nseg - 1);
-    state_kernel<<<sgrid, Cfg::NTHREADS, Lay::SMEM_BYTES, stream>>>(tk, tv, p);
+    state_kernel<<<sgrid, Lay::NTHREADS, Lay::SMEM_BYTES, stream>>>(tk, tv, p);
     if ((rc = check_launch("ret_chunk_fwd state launch"))) return rc;
   }
   auto kernel = &ret_chunk_sm100_kernel<Cfg>;

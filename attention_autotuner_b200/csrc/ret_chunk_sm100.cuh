@@ -28,9 +28,11 @@
 // release of the K and V buffers come early and the next chunk's loads run under this chunk's epilogue. So no
 // intermediate exceeds the magnitudes of Q K^T and V whatever gamma in (0, 1] is, and no scratch memory is needed.
 //
-// Roles: warps 0-3 element-wise warpgroup (thread t owns TMEM lane t: a row of Z / ACC, or a row of the state, and
-// a share of the K tile), warp 4 issues every MMA (converged warp, one elected lane; a single issuer keeps all
-// tensor-memory hazards in program order), warp 5 lane 0 is the TMA producer. Tensor memory: Z at [0,128), ACC at
+// Roles: warps 0-3 row warpgroup (thread t owns TMEM lane t: row t of Z / ACC; W, the carried term, the output),
+// warps 4-7 state warpgroup (row t of each state half and a share of the K tile; the two groups work side by side, which
+// takes the scaling of K and the copy of the state off the chain Z -> W -> W V), warp 8 issues every MMA (converged
+// warp, one elected lane; a single issuer keeps all tensor-memory hazards in program order), warp 9 lane 0 is the TMA
+// producer. Tensor memory: Z at [0,128), ACC at
 // [128,128+DVC), the state halves (dqk rows 0-127, 128-255) at [256,256+DVC) and [384,384+DVC).
 //
 // Few slices, long sequences: a walk in order leaves most SMs idle (a grid of BH * dv / DVC CTAs is all the parallelism
@@ -68,7 +70,7 @@ struct RetChunkConfig {
   static constexpr int SB_HALF_BYTES = VB * BOX_BYTES;  // 128 state rows x DVC columns, 16-bit
   static constexpr int SMEM_TILES = 2 * QK_BYTES + V_BYTES + NH * SB_HALF_BYTES;
   static constexpr int SMEM_BYTES = 1024 + SMEM_TILES + 512;
-  static constexpr int NTHREADS = 192;
+  static constexpr int NTHREADS = 320;
   static constexpr int TMEM_COLS = 512;
   static_assert(DQK == 128 || DQK == 256, "dqk");
   static_assert(DVC == 64 || DVC == 128, "dv chunk");
@@ -98,7 +100,7 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint64_t* k_full = bars + 1;     // K chunk landed
   uint64_t* v_full = bars + 2;     // V chunk landed
   uint64_t* q_free = bars + 3;     // Z and Q S of the chunk complete                   (MMA -> TMA)
-  uint64_t* kv_free = bars + 4;    // state update of the chunk complete: K and V free  (MMA -> TMA)
+  uint64_t* k_free = bars + 4;     // state update of the chunk complete: K free        (MMA -> TMA)
   uint64_t* z_full = bars + 5;     // Z complete                                        (MMA -> element-wise)
   uint64_t* w_full = bars + 6;     // W written over Z and the carried term scaled       (element-wise -> MMA), 128 arrivals
   uint64_t* acc_done = bars + 7;   // ACC of the chunk complete                         (MMA -> element-wise)
@@ -107,7 +109,8 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint64_t* s_ready = bars + 10;   // decayed state in TMEM and its 16-bit copy in smem (element-wise -> MMA), 128 arrivals
   uint64_t* y_done = bars + 11;    // Q S complete                                      (MMA -> element-wise)
   uint64_t* k_scaled = bars + 12;  // rows of the K tile scaled in place                (element-wise -> MMA), 128 arrivals
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* v_free = bars + 13;    // W V of the chunk complete: V free                 (MMA -> TMA)
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 14);
   CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 1);
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
@@ -126,7 +129,8 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     mbar_init(k_full, 1);
     mbar_init(v_full, 1);
     mbar_init(q_free, 1);
-    mbar_init(kv_free, 1);
+    mbar_init(k_free, 1);
+    mbar_init(v_free, 1);
     mbar_init(z_full, 1);
     mbar_init(w_full, 128);
     mbar_init(acc_done, 1);
@@ -138,11 +142,11 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     ab->flag = 0;
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(tmem_base_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
-  if (warp == 5 && lane == 0) {
+  if (warp == 9 && lane == 0) {
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
@@ -155,23 +159,29 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const uint32_t tACC = tmem_base + 128;
   const uint32_t tS = tmem_base + 256;  // half h at tS + 128 * h
 
-  if (warp == 5) {
+  if (warp == 9) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       bool ok = true;
-      int nq = 0, nkv = 0;  // chunks whose Q / K and V' loads have been issued
+      int nq = 0, nk = 0, nkv = 0;  // chunks whose Q / K / V loads have been issued
       for (int c = 0; c < nchunk && ok; ++c) {
         if (c > 0) ok = mbar_wait(q_free, (c - 1) & 1, ab, kRcQFree);
         if (!ok) break;
+        AB200_CTR(1, c, 4);
         mbar_expect_tx(q_full, Cfg::QK_BYTES);
 #pragma unroll
         for (int b = 0; b < KB; ++b) tma_load_3d(sQ + b * BOX, &tmQ, q_full, b * 64, (c_begin + c) * 128, bh);
         ++nq;
-        if (c > 0) ok = mbar_wait(kv_free, (c - 1) & 1, ab, kRcKVFree);
+        if (c > 0) ok = mbar_wait(k_free, (c - 1) & 1, ab, kRcKVFree);
         if (!ok) break;
+        AB200_CTR(1, c, 5);
         mbar_expect_tx(k_full, Cfg::QK_BYTES);
 #pragma unroll
         for (int b = 0; b < KB; ++b) tma_load_3d(sK + b * BOX, &tmK, k_full, b * 64, (c_begin + c) * 128, bh);
+        ++nk;
+        if (c > 0) ok = mbar_wait(v_free, (c - 1) & 1, ab, kRcKVFree);
+        if (!ok) break;
+        AB200_CTR(1, c, 6);
         mbar_expect_tx(v_full, Cfg::V_BYTES);
 #pragma unroll
         for (int b = 0; b < VB; ++b) tma_load_3d(sV + b * BOX, &tmV, v_full, n_off + b * 64, (c_begin + c) * 128, bh);
@@ -191,13 +201,11 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       if (!ok) {
         // abort path: let the copies already issued land before this CTA's shared memory is released
         if (nq > 0) mbar_wait_drain(q_full, (nq - 1) & 1, 2000000ull);
-        if (nkv > 0) {
-          mbar_wait_drain(k_full, (nkv - 1) & 1, 2000000ull);
-          mbar_wait_drain(v_full, (nkv - 1) & 1, 2000000ull);
-        }
+        if (nk > 0) mbar_wait_drain(k_full, (nk - 1) & 1, 2000000ull);
+        if (nkv > 0) mbar_wait_drain(v_full, (nkv - 1) & 1, 2000000ull);
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     // ------------------------------------------------------------------ MMA issuer (converged warp, one elected lane)
     constexpr uint32_t idesc_z = umma_idesc(128, 128, BF16, false, false);   // Q K^T: both K-major
     constexpr uint32_t idesc_y = umma_idesc(128, DVC, BF16, false, true);    // Q S, W V: B MN-major
@@ -210,6 +218,7 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       if (ok) ok = mbar_wait_warp(k_full, ph, ab, kRcK);
       if (!ok) break;
       tc_fence_after();
+      if (lane == 0) AB200_CTR(1, c, 0);
       if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < DQK / 16; ++ks) {
@@ -226,6 +235,7 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         if (ok && c > 0) ok = mbar_wait_warp(acc_free, (c - 1) & 1, ab, kRcAccFree);
         if (!ok) break;
         tc_fence_after();
+        if (lane == 0) AB200_CTR(1, c, 1);
         if (elect_one()) {
 #pragma unroll
           for (int ks = 0; ks < DQK / 16; ++ks) {
@@ -245,6 +255,7 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       if (ok) ok = mbar_wait_warp(k_scaled, ph, ab, kRcKScaled);
       if (!ok) break;
       tc_fence_after();
+      if (lane == 0) AB200_CTR(1, c, 2);
       if (elect_one()) {
 #pragma unroll
         for (int h = 0; h < NH; ++h) {
@@ -254,34 +265,31 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     umma_smem_desc(v_addr + ks * 2048, BOX, 1024), idesc_u, (carried || ks > 0) ? 1u : 0u);
         }
         tc_commit(u_done);
+        tc_commit(k_free);  // the next chunk's K tile loads under this chunk's W V
       }
       __syncwarp();
       ok = mbar_wait_warp(w_full, ph, ab, kRcW);
       if (!ok) break;
       tc_fence_after();
+      if (lane == 0) AB200_CTR(1, c, 3);
       if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           umma_ts(tACC, tZ + ks * 8, umma_smem_desc(v_addr + ks * 2048, BOX, 1024), idesc_y, (carried || ks > 0) ? 1u : 0u);
         tc_commit(acc_done);
-        tc_commit(kv_free);
+        tc_commit(v_free);
       }
       __syncwarp();
     }
-  } else {
-    // ------------------------------------------------------------------ element-wise warpgroup
-    const int tid = threadIdx.x;  // 0..127 = TMEM lane = row of the chunk
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32);
-    const int h = bh % p.H;
-    const float lg = log2f(p.decay[h]);
-    const float row_decay = exp2f(tid * lg);                 // gamma^i, row factor of W (columns bring gamma^-j)
-    const float carry = exp2f((tid + 1) * lg);               // gamma^(i+1): the carried state seen from row i
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ state warpgroup (warps 4-7): rows of the K tile
+    // and rows of the state. Thread t owns TMEM lane t = row t of each state half.
+    const int wq = warp - 4;
+    const int tid = threadIdx.x - 128;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32);
+    const float lg = log2f(p.decay[bh % p.H]);
     const float g128 = exp2f(128.0f * lg);
     const uint64_t g2 = f2_pack(g128, g128);
-    const uint64_t carry2 = f2_pack(carry, carry);
-    const uint64_t sc2 = f2_pack(p.scale, p.scale);
-    const uint32_t tz = tmem_addr(tZ, lane_base, 0);
-    const uint32_t ta = tmem_addr(tACC, lane_base, 0);
     // 32 columns of row `tid` of state half hh, fp32 in rr: 16-bit copy into shared memory (operand of the next Q S; four
     // 16-byte groups of the row's 128-byte line in box c0 / 64, 128-byte swizzle), and g * S into tensor memory, where
     // the next chunk's K^T V is added
@@ -337,44 +345,84 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     }
     for (int c = 0; c < nchunk && ok; ++c) {
       const uint32_t ph = c & 1;
-      // ---- W = Z .* gamma^(i-j), keys after the row's own position removed (the forward flavour of the chain kernels'
-      //      element-wise step: row factor gamma^i, running column factor gamma^-j, triangular predicate)
       ok = mbar_wait_warp(z_full, ph, ab, kRcZ);
       if (ok) ok = mbar_wait_warp(k_full, ph, ab, kRcK);  // long complete; makes the TMA's writes visible to this thread
       if (!ok) break;
-      tc_fence_after();
       // ---- Q K^T has read the plain K tile: scale its rows in place for the state update. A row takes one factor, so
       //      the work is shared by address, not by row: the 32 lanes of a warp cover four consecutive 128-byte lines at a
       //      time (lane l: line l / 8, 16-byte group l % 8), which is free of bank conflicts; a thread per row would put
       //      all lanes of a warp on the same banks.
-      {
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
-          const int krow_idx = warp * 32 + it * 4 + (lane >> 3);
-          const float kf = exp2f((127 - krow_idx) * lg);  // gamma^(127-j)
-          const uint64_t kr2 = f2_pack(kf, kf);
+      for (int it = 0; it < 8; ++it) {
+        const int krow_idx = wq * 32 + it * 4 + (lane >> 3);
+        const float kf = exp2f((127 - krow_idx) * lg);  // gamma^(127-j)
+        const uint32_t kr2 = pack2<BF16>(kf, kf);       // one packed 16-bit product per pair (a factor rounded to 16
+                                                        // bits costs what the rounding of the product costs)
 #pragma unroll
-          for (int b = 0; b < KB; ++b) {
-            uint4* ptr = reinterpret_cast<uint4*>(sK + b * BOX + krow_idx * 128 + (lane & 7) * 16);
-            uint4 u = *ptr;
-            uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float lo, hi;
-              f2_unpack(fmul2(chain_unpack_pair<BF16>(w[e]), kr2), lo, hi);
-              w[e] = pack2<BF16>(lo, hi);
-            }
-            *ptr = make_uint4(w[0], w[1], w[2], w[3]);
-          }
+        for (int b = 0; b < KB; ++b) {
+          uint4* ptr = reinterpret_cast<uint4*>(sK + b * BOX + krow_idx * 128 + (lane & 7) * 16);
+          uint4 u = *ptr;
+          *ptr = make_uint4(mul2_16<BF16>(u.x, kr2), mul2_16<BF16>(u.y, kr2), mul2_16<BF16>(u.z, kr2), mul2_16<BF16>(u.w, kr2));
         }
-        fence_proxy_async_smem();
-        mbar_arrive(k_scaled);
       }
+      fence_proxy_async_smem();
+      mbar_arrive(k_scaled);
+      if (tid == 0) AB200_CTR(0, c, 5);
+      // ---- carried state for the next chunk: 16-bit copy of S into shared memory, S <- g S in tensor memory. The commit
+      //      behind u_done follows the chunk's Q S in the issuing thread, so the copy that Q S read is free as well.
+      if (c + 1 < nchunk) {
+        ok = mbar_wait_warp(u_done, ph, ab, kRcU);
+        if (!ok) break;
+        tc_fence_after();
+        if (tid == 0) AB200_CTR(0, c, 6);
+        // blocks of 32 columns, two in flight: the load of the next block runs under the work on this one
+        constexpr int NBLK = NH * (DVC / 32);
+        auto blk_addr = [&](int blk) { return tmem_addr(tS + (blk / (DVC / 32)) * 128, lane_base, 0) + (blk % (DVC / 32)) * 32; };
+        uint32_t ra[32], rb[32];
+        tmem_ld32(blk_addr(0), ra);
+#pragma unroll 1
+        for (int blk = 0; blk < NBLK; blk += 2) {
+          tc_wait_ld();
+          tmem_ld32(blk_addr(blk + 1), rb);
+          put_state(blk / (DVC / 32), (blk % (DVC / 32)) * 32, ra);
+          tc_wait_ld();
+          if (blk + 2 < NBLK) tmem_ld32(blk_addr(blk + 2), ra);
+          put_state((blk + 1) / (DVC / 32), ((blk + 1) % (DVC / 32)) * 32, rb);
+        }
+        tc_wait_st();
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(s_ready);
+        if (tid == 0) AB200_CTR(0, c, 7);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ row warpgroup (warps 0-3): thread t owns TMEM
+    // lane t = row t of the chunk in Z and ACC
+    const int tid = threadIdx.x;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32);
+    const float lg = log2f(p.decay[bh % p.H]);
+    const float row_decay = exp2f(tid * lg);                 // gamma^i, row factor of W (columns bring gamma^-j)
+    const float carry = exp2f((tid + 1) * lg);               // gamma^(i+1): the carried state seen from row i
+    const uint64_t carry2 = f2_pack(carry, carry);
+    const uint64_t sc2 = f2_pack(p.scale, p.scale);
+    const uint32_t tz = tmem_addr(tZ, lane_base, 0);
+    const uint32_t ta = tmem_addr(tACC, lane_base, 0);
+    bool ok = true;
+    for (int c = 0; c < nchunk && ok; ++c) {
+      const uint32_t ph = c & 1;
+      // ---- W = Z .* gamma^(i-j), keys after the row's own position removed (the forward flavour of the chain kernels'
+      //      element-wise step: row factor gamma^i, running column factor gamma^-j, triangular predicate)
+      ok = mbar_wait_warp(z_full, ph, ab, kRcZ);
+      if (!ok) break;
+      tc_fence_after();
+      if (tid == 0) AB200_CTR(0, c, 0);
       {
         float unused_sum = 0.f;
         chain_ew_decay2<kChainFwd, BF16, 0, false>(tz, row_decay, lg, 0.f, 0.f, true, tid, unused_sum);
         chain_ew_decay2<kChainFwd, BF16, 2, false>(tz, row_decay, lg, 0.f, 0.f, true, tid, unused_sum);
       }
+      if (tid == 0) AB200_CTR(0, c, 1);
       // ---- the carried term Q S, now in ACC, seen from row i: times gamma^(i+1)
       if (c > 0 || init) {
         ok = mbar_wait_warp(y_done, (c - 1 + sb) & 1, ab, kRcY);
@@ -398,32 +446,12 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(w_full);
-
-      // ---- carried state for the next chunk: 16-bit copy of S into shared memory, S <- g S in tensor memory
-      if (c + 1 < nchunk) {
-        ok = mbar_wait_warp(u_done, ph, ab, kRcU);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int hh = 0; hh < NH; ++hh) {
-          const uint32_t ts = tmem_addr(tS + hh * 128, lane_base, 0);
-#pragma unroll
-          for (int c0 = 0; c0 < DVC; c0 += 32) {
-            uint32_t rr[32];
-            tmem_ld32(ts + c0, rr);
-            tc_wait_ld();
-            put_state(hh, c0, rr);
-          }
-        }
-        tc_wait_st();
-        fence_proxy_async_smem();
-        tc_fence_before();
-        mbar_arrive(s_ready);
-      }
+      if (tid == 0) AB200_CTR(0, c, 2);
       // ---- O_c = scale * ACC
       ok = mbar_wait_warp(acc_done, ph, ab, kRcAcc);
       if (!ok) break;
       tc_fence_after();
+      if (tid == 0) AB200_CTR(0, c, 3);
       {
         const int row = (c_begin + c) * 128 + tid;
         uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (static_cast<size_t>(bh) * p.L + row) * p.dv + n_off;
@@ -451,14 +479,14 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           }
         }
       }
-
+      if (tid == 0) AB200_CTR(0, c, 4);
     }
   }
 
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
@@ -477,12 +505,13 @@ struct RetChunkStateLayout {
   static constexpr int SMEM_TILES = 2 * STAGE_BYTES;
   static constexpr int SMEM_BYTES = 1024 + SMEM_TILES + 512;
   static constexpr int TMEM_COLS = 256;
+  static constexpr int NTHREADS = 192;
   static_assert(SMEM_BYTES <= 232448, "shared memory");
   static_assert(Cfg::NH * 128 <= TMEM_COLS, "tensor memory");
 };
 
 template <class Cfg>
-__global__ void __launch_bounds__(Cfg::NTHREADS, 1)
+__global__ void __launch_bounds__(RetChunkStateLayout<Cfg>::NTHREADS, 1)
 ret_chunk_state_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                              const RetChunkParams p) {
   using Lay = RetChunkStateLayout<Cfg>;
@@ -592,19 +621,12 @@ ret_chunk_state_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       for (int it = 0; it < 8; ++it) {
         const int krow_idx = warp * 32 + it * 4 + (lane >> 3);
         const float kf = exp2f((127 - krow_idx + later) * lg);
-        const uint64_t kr2 = f2_pack(kf, kf);
+        const uint32_t kr2 = pack2<BF16>(kf, kf);
 #pragma unroll
         for (int b = 0; b < KB; ++b) {
           uint4* ptr = reinterpret_cast<uint4*>(sK + b * BOX + krow_idx * 128 + (lane & 7) * 16);
           uint4 u = *ptr;
-          uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float lo, hi;
-            f2_unpack(fmul2(chain_unpack_pair<BF16>(w[e]), kr2), lo, hi);
-            w[e] = pack2<BF16>(lo, hi);
-          }
-          *ptr = make_uint4(w[0], w[1], w[2], w[3]);
+          *ptr = make_uint4(mul2_16<BF16>(u.x, kr2), mul2_16<BF16>(u.y, kr2), mul2_16<BF16>(u.z, kr2), mul2_16<BF16>(u.w, kr2));
         }
       }
       fence_proxy_async_smem();

@@ -465,6 +465,7 @@ def main():
     ms_total = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
     check_status("the headline region")
+    launches_per_step = run.launches
     gpu_launches = run.launches * args.steps
 
     # ------------------------------------------------------------------ end to end through the public operator
@@ -642,7 +643,7 @@ def main():
                          "frac": achieved / peak_tf, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                          "peak_source": f"{peak_src} (cuBLAS bf16 burst; the timed region is a burst of a few tens of ms; "
                                         "for the fraction of the sustained peak see workloads.*.sustained)",
-                         "flops_per_step": fl_gpu, "launches_per_step": run.launches,
+                         "flops_per_step": fl_gpu, "launches_per_step": launches_per_step,
                          "kernel": kernel_of(args.workload)},
             "clocks": clocks,
             "gpu_launches": gpu_launches,
