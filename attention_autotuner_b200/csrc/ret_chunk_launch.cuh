@@ -75,10 +75,11 @@ int ret_chunk_launch(const RetChunkArgs& a, cudaStream_t stream, int segments = 
     return fail(kErrUnsupported, "ret_chunk_fwd: dqk=%d dv=%d do not match tile %d/%d", a.dqk, a.dv, DQK, DVC);
   if ((rc = check_prior_status("ret_chunk_fwd"))) return rc;
   if ((rc = bind_device_of(a.q, "ret_chunk_fwd"))) return rc;
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, to;
   if ((rc = make_tmap_3d(&tq, a.q, BF16, DQK, a.L, a.BH, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tk, a.k, BF16, DQK, a.L, a.BH, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tv, a.v, BF16, a.dv, a.L, a.BH, 64, 128))) return rc;
+  if ((rc = make_tmap_3d(&to, a.o, BF16, a.dv, a.L, a.BH, 64, 32))) return rc;  // a warp stores its 32 rows
   RetChunkParams p;
   p.o = a.o;
   p.decay = a.decay;
@@ -104,7 +105,7 @@ int ret_chunk_launch(const RetChunkArgs& a, cudaStream_t stream, int segments = 
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
   if (e != cudaSuccess) return fail(kErrCuda, "ret_chunk_fwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   dim3 grid(a.dv / DVC, a.BH, nseg);
-  kernel<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  kernel<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, to, p);
   return check_launch("ret_chunk_fwd launch");
 }
 

@@ -85,7 +85,8 @@ enum RetChunkTag : int {
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
 ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                       const __grid_constant__ CUtensorMap tmV, const RetChunkParams p) {
+                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                       const RetChunkParams p) {
   constexpr int DQK = Cfg::DQK, DVC = Cfg::DVC, NH = Cfg::NH, KB = Cfg::KB, VB = Cfg::VB, BOX = Cfg::BOX_BYTES;
   constexpr bool BF16 = Cfg::BF16;
 
@@ -109,7 +110,7 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint64_t* s_ready = bars + 10;   // decayed state in TMEM and its 16-bit copy in smem (element-wise -> MMA), 128 arrivals
   uint64_t* y_done = bars + 11;    // Q S complete                                      (MMA -> element-wise)
   uint64_t* k_scaled = bars + 12;  // rows of the K tile scaled in place                (element-wise -> MMA), 128 arrivals
-  uint64_t* v_free = bars + 13;    // W V of the chunk complete: V free                 (MMA -> TMA)
+  uint64_t* v_free = bars + 13;    // the chunk's output, staged in the V tile, has left it (row warps -> TMA), 4 arrivals
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 14);
   CtaAbort* ab = reinterpret_cast<CtaAbort*>(tmem_base_slot + 1);
 
@@ -130,7 +131,7 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     mbar_init(v_full, 1);
     mbar_init(q_free, 1);
     mbar_init(k_free, 1);
-    mbar_init(v_free, 1);
+    mbar_init(v_free, 4);
     mbar_init(z_full, 1);
     mbar_init(w_full, 128);
     mbar_init(acc_done, 1);
@@ -150,6 +151,7 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmO);
   }
   tc_fence_before();
   __syncthreads();
@@ -277,7 +279,6 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         for (int ks = 0; ks < 8; ++ks)
           umma_ts(tACC, tZ + ks * 8, umma_smem_desc(v_addr + ks * 2048, BOX, 1024), idesc_y, (carried || ks > 0) ? 1u : 0u);
         tc_commit(acc_done);
-        tc_commit(v_free);
       }
       __syncwarp();
     }
@@ -453,8 +454,10 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tc_fence_after();
       if (tid == 0) AB200_CTR(0, c, 3);
       {
-        const int row = (c_begin + c) * 128 + tid;
-        uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (static_cast<size_t>(bh) * p.L + row) * p.dv + n_off;
+        // W V was the last reader of the V tile, which has the size and the layout of this CTA's piece of the output: the
+        // rows go there (16-bit, 128-byte swizzle) and leave through TMA stores, one per warp and 64-column box (32 rows
+        // each, so no warp waits for another); rows past the end of the sequence are clipped by the store
+        uint8_t* stage = sV + tid * 128;
 #pragma unroll
         for (int c0 = 0; c0 < DVC; c0 += 32) {
           uint32_t rr[32];
@@ -464,23 +467,35 @@ ret_chunk_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             tc_fence_before();
             mbar_arrive(acc_free);
           }
-          if (row < p.L) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 16) {
-              uint32_t v[8];
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint32_t v[4];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                float x0, x1;
-                f2_unpack(fmul2(f2_pack(__uint_as_float(rr[i + 2 * e]), __uint_as_float(rr[i + 2 * e + 1])), sc2), x0, x1);
-                v[e] = pack2<BF16>(x0, x1);
-              }
-              st_global_v8(orow + c0 + i, v);
+            for (int e = 0; e < 4; ++e) {
+              float x0, x1;
+              f2_unpack(fmul2(f2_pack(__uint_as_float(rr[q4 * 8 + 2 * e]), __uint_as_float(rr[q4 * 8 + 2 * e + 1])), sc2), x0, x1);
+              v[e] = pack2<BF16>(x0, x1);
             }
+            const int chunk16 = ((c0 & 63) >> 3) + q4;
+            *reinterpret_cast<uint4*>(stage + (c0 >> 6) * BOX + ((chunk16 ^ (tid & 7)) << 4)) = make_uint4(v[0], v[1], v[2], v[3]);
           }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int row0 = (c_begin + c) * 128 + warp * 32;
+          if (row0 < p.L) {
+#pragma unroll
+            for (int b = 0; b < VB; ++b) tma_store_3d(&tmO, sV + b * BOX + warp * 32 * 128, n_off + b * 64, row0, bh);
+            tma_store_commit();
+            tma_store_wait_read0();
+          }
+          mbar_arrive(v_free);
         }
       }
       if (tid == 0) AB200_CTR(0, c, 4);
     }
+    if (lane == 0) tma_store_wait0();  // all output written before the CTA exits
   }
 
   __syncwarp();
