@@ -517,6 +517,11 @@ def main():
 
         def short_leg(r: Runner, reps=20):
             """Reference timing method: flush, one event pair per launch, median and p20/p80; C ABI and operator."""
+            # every leg is a burst timed alone, like the peak it is compared with: the SM clock follows the power drawn over
+            # the last tens of milliseconds, so a light kernel timed right after a heavy leg would run at that leg's clock
+            # (measured: 0.160 ms against 0.136 ms for the same launch); a short idle gap lets the clock come back
+            torch.cuda.synchronize()
+            time.sleep(0.15)
             smp = ClockSampler(local_rank)
             if rank == 0:
                 smp.start()
@@ -529,7 +534,8 @@ def main():
                     "reps": st["reps"], "tflops_per_gpu": tf, "tflops": tf * world, "frac": tf / peak_tf,
                     "op_ms": op_ms, "op_tflops_per_gpu": r.flops / (op_ms * 1e-3) / 1e12,
                     "launches_per_step": r.launches, "kernel": kernel_of(r.name), "scaling": "weak", "clocks": ck,
-                    "timing": "256 MB L2 flush before every launch, one CUDA event pair per launch, median"}, \
+                    "timing": "0.15 s idle, 3 warm-up launches, then 256 MB L2 flush before every launch, one CUDA event pair per "
+                              "launch, median"}, \
                 r.launches * (st["reps"] + op["reps"] + 6)
 
         def sustained_leg(r: Runner, seconds: float):
