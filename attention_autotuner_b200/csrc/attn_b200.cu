@@ -56,7 +56,15 @@ template <bool BF16>
 int fa_fwd_dispatch(const FaFwdArgs& a, int dqk, cudaStream_t st, bool profile, float* ms) {
   auto run = [&](auto cfg_tag) -> int {
     using Cfg = decltype(cfg_tag);
-    auto launch = [&]() -> int { return fa_fwd_launch_auto<Cfg>(a, st); };
+    auto launch = [&]() -> int {
+      // the persistent form with a K / V ring of three entries leaves room to stage the finished tiles in shared memory
+      // and store them by TMA (the tuner's choice at d = 128 as well); the grid form keeps its ring of four
+      if constexpr (Cfg::DQK == 128 && Cfg::NQ == 2 && Cfg::NSTAGE == 4) {
+        using P = FaFwdConfig<128, Cfg::DV, 2, 3, Cfg::BF16>;
+        if (fa_fwd_picks_persistent<P>(a)) return fa_fwd_persist_launch<P>(a, st);
+      }
+      return fa_fwd_launch_auto<Cfg>(a, st);
+    };
     if (!profile) return launch();
     *ms = profile_loop(launch, st);
     return *ms < 0.f ? kErrCuda : kOk;

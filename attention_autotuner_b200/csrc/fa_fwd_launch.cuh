@@ -89,6 +89,9 @@ int fa_fwd_persist_launch(const FaFwdArgs& a, cudaStream_t stream) {
   if ((rc = make_tmap_3d(&tq, a.q, Cfg::BF16, Cfg::DQK, a.Lq, a.BH, 64, Cfg::BM))) return rc;
   if ((rc = make_tmap_3d(&tk, a.k, Cfg::BF16, Cfg::DQK, a.Lkv, a.BH, 64, Cfg::BN))) return rc;
   if ((rc = make_tmap_3d(&tv, a.v, Cfg::BF16, a.dv, a.Lkv, a.BH, 64, Cfg::BN))) return rc;
+  CUtensorMap to = tv;  // stands in where the output is not staged
+  using Lay = FaFwdPersistLayout<Cfg>;
+  if (Lay::STAGE_O && (rc = make_tmap_3d(&to, a.o, Cfg::BF16, a.dv, a.Lq, a.BH, 64, 32))) return rc;  // a warp stores its 32 rows
 
   FaFwdPersistParams pp;
   pp.f.o = a.o;
@@ -106,13 +109,13 @@ int fa_fwd_persist_launch(const FaFwdArgs& a, cudaStream_t stream) {
   pp.n_super = static_cast<int>(n_super);
 
   auto kernel = &fa_fwd_persist_sm100_kernel<Cfg>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay::SMEM_BYTES);
   if (e != cudaSuccess) return fail(kErrCuda, "fa_fwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
     sms = 148;
   const int grid = pp.n_super < sms ? pp.n_super : sms;
-  kernel<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, pp);
+  kernel<<<grid, Cfg::NTHREADS, Lay::SMEM_BYTES, stream>>>(tq, tk, tv, to, pp);
   return check_launch("fa_fwd launch");
 }
 
@@ -123,12 +126,20 @@ int fa_fwd_persist_launch(const FaFwdArgs& a, cudaStream_t stream) {
 // -3 % (with long items a static work list loses more to the slowest SM than the boundaries cost). The rule: persistent
 // up to 40 KV blocks per item on average (half of the blocks count under a causal mask).
 template <class Cfg>
-int fa_fwd_launch_auto(const FaFwdArgs& a, cudaStream_t stream) {
+bool fa_fwd_picks_persistent(const FaFwdArgs& a) {
   if constexpr (Cfg::NQ == 2 && Cfg::SPLIT == 1 && Cfg::NMMA == 1 && Cfg::EXP_EMU == 0 && Cfg::EXP_H2 == 0 && Cfg::DV <= 128) {
     const int form = fa_fwd_form_requested();
     const int nblk = (a.Lkv + Cfg::BN - 1) / Cfg::BN;
     const int avg_blocks = a.causal ? (nblk + 1) / 2 : nblk;
-    if (form == 2 || (form == 0 && avg_blocks <= 40)) return fa_fwd_persist_launch<Cfg>(a, stream);
+    return form == 2 || (form == 0 && avg_blocks <= 40);
+  }
+  return false;
+}
+
+template <class Cfg>
+int fa_fwd_launch_auto(const FaFwdArgs& a, cudaStream_t stream) {
+  if constexpr (Cfg::NQ == 2 && Cfg::SPLIT == 1 && Cfg::NMMA == 1 && Cfg::EXP_EMU == 0 && Cfg::EXP_H2 == 0 && Cfg::DV <= 128) {
+    if (fa_fwd_picks_persistent<Cfg>(a)) return fa_fwd_persist_launch<Cfg>(a, stream);
   }
   return fa_fwd_launch<Cfg>(a, stream);
 }

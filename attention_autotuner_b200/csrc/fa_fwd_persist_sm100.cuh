@@ -35,10 +35,27 @@ struct FaFwdItem {
   int nmax;
 };
 
+// Output staging: where shared memory has room for both finished tiles (a K / V ring of up to three entries at
+// d = 128), a tile's rows are written there (16-bit, 128-byte swizzle) and leave through TMA stores, one per warp and
+// 64-column box (32 rows each, so no warp waits for another). A thread storing its own row writes 32-byte pieces of 32
+// different rows per instruction, which keeps the softmax warps from the next item's first block for as long as a
+// couple of KV blocks take.
+template <class Cfg>
+struct FaFwdPersistLayout {
+  static constexpr int O_TILE_BYTES = Cfg::BM * Cfg::DV * 2;
+#ifdef AB200_FA_FWD_NO_STAGE_O  // build option for comparisons: every thread stores its own row
+  static constexpr bool STAGE_O = false;
+#else
+  static constexpr bool STAGE_O = Cfg::DV % 64 == 0 && Cfg::SMEM_BYTES + 2 * O_TILE_BYTES <= 232448;
+#endif
+  static constexpr int SMEM_BYTES = Cfg::SMEM_BYTES + (STAGE_O ? 2 * O_TILE_BYTES : 0);
+};
+
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
 fa_fwd_persist_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                            const __grid_constant__ CUtensorMap tmV, const FaFwdPersistParams pp) {
+                            const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                            const FaFwdPersistParams pp) {
   static_assert(Cfg::NQ == 2 && Cfg::SPLIT == 1 && Cfg::NMMA == 1 && Cfg::EXP_EMU == 0 && Cfg::EXP_H2 == 0,
                 "the persistent kernel is built for the default tile only");
   static_assert(Cfg::DV <= 128, "the epilogue holds a whole output row in registers");
@@ -51,7 +68,10 @@ fa_fwd_persist_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sKV = smem + NQ * Cfg::Q_TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::SMEM_TILES);
+  using Lay = FaFwdPersistLayout<Cfg>;
+  constexpr bool STAGE_O = Lay::STAGE_O;
+  uint8_t* sO = smem + Cfg::SMEM_TILES;  // [2] finished tiles on their way out (STAGE_O only)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::SMEM_TILES + (STAGE_O ? 2 * Lay::O_TILE_BYTES : 0));
   uint64_t* q_full = bars;                   // [2] Q tile landed
   uint64_t* q_free = q_full + NQ;            // [2] the item's last S MMA of the tile is complete
   uint64_t* kv_full = q_free + NQ;           // [NSTAGE]
@@ -441,7 +461,37 @@ fa_fwd_persist_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         tc_wait_ld();
         tc_fence_before();
         mbar_arrive(&o_free[s]);
-        if (row < p.Lq) {
+        if constexpr (STAGE_O) {
+          (void)orow;
+          // this warp's stores of the previous item must have read the staging rows before they are written again
+          if (lane == 0) tma_store_wait_read0();
+          __syncwarp();
+          uint8_t* stage = sO + s * Lay::O_TILE_BYTES + row_in_tile * 128;
+#pragma unroll
+          for (int i = 0; i < DV; i += 8) {
+            uint4 v;
+            v.x = pack2<BF16>(__uint_as_float(r[i + 0]) * inv_l, __uint_as_float(r[i + 1]) * inv_l);
+            v.y = pack2<BF16>(__uint_as_float(r[i + 2]) * inv_l, __uint_as_float(r[i + 3]) * inv_l);
+            v.z = pack2<BF16>(__uint_as_float(r[i + 4]) * inv_l, __uint_as_float(r[i + 5]) * inv_l);
+            v.w = pack2<BF16>(__uint_as_float(r[i + 6]) * inv_l, __uint_as_float(r[i + 7]) * inv_l);
+            const int chunk16 = (i & 63) >> 3;
+            *reinterpret_cast<uint4*>(stage + (i >> 6) * (BM * 128) + ((chunk16 ^ (row_in_tile & 7)) << 4)) = v;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            FaFwdItem io;
+            get_item(u, io);
+            const int row0 = m_tile + (warp & 3) * 32;
+            if (row0 < p.Lq) {  // rows past the end of Q are clipped by the store
+#pragma unroll
+              for (int b = 0; b < DV / 64; ++b)
+                tma_store_3d(&tmO, sO + s * Lay::O_TILE_BYTES + b * (BM * 128) + (warp & 3) * (32 * 128), io.dv_off + b * 64, row0,
+                             io.bh);
+              tma_store_commit();
+            }
+          }
+        } else if (row < p.Lq) {
 #pragma unroll
           for (int i = 0; i < DV; i += 16) {
             uint32_t v[8];
@@ -456,6 +506,7 @@ fa_fwd_persist_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         if (float* l = lse_row()) *l = (l_sum > 0.f) ? (m_ref * p.scale + __logf(l_sum)) : -INFINITY;
       cs += n_my;
     }
+    if (STAGE_O && lane == 0) tma_store_wait0();  // all output written before the CTA's shared memory is released
   }
 
   // common tail: every role gets here, also after an aborted wait

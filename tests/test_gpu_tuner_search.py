@@ -1,5 +1,5 @@
 """The tile search on a GPU, pruned to the cost model's three best candidates so that it stays short: compile ->
-time (every candidate twice, the near-best three times, ranked by the median) -> log in the reference's text format
+time (every candidate twice; those within 4 % of the best, if any, three times, ranked by the median) -> log in the reference's text format
 plus its JSON twin -> cache entry, which the next tune() returns without searching
 (reference flow: python/autotuner/base_tunner.py:129-195)."""
 import json
@@ -32,9 +32,15 @@ def test_pruned_search_writes_log_and_cache_and_the_choice_computes_correctly(tm
     log = json.load(open(str(stem) + ".json"))
     assert len(log["results"]) == 3 and log["cost_model"]["pruned_to_top_k"] == 3 and log["cost_model"]["candidates"] == len(cands)
     confirmed = [r for r in log["results"] if r["confirm_ms"]]
-    assert len(confirmed) >= 2 and all(len(r["confirm_ms"]) == 3 for r in confirmed)
     best = next(r for r in log["results"] if r["config"] == repr(cfg))
-    assert best["confirm_ms"] and abs(sorted(best["confirm_ms"])[1] - log["best_ms"]) < 1e-9
+    if confirmed:
+        # the candidates within 4 % of the best were timed three times and ranked by the median
+        assert len(confirmed) >= 2 and all(len(r["confirm_ms"]) == 3 for r in confirmed)
+        assert best["confirm_ms"] and abs(sorted(best["confirm_ms"])[1] - log["best_ms"]) < 1e-9
+    else:
+        # one candidate is more than 4 % ahead of every other: nothing to confirm
+        assert abs(best["ms"] - log["best_ms"]) < 1e-9
+        assert all(r["ms"] > 1.04 * best["ms"] for r in log["results"] if r is not best)
     assert all(0 < r["ms"] < 50 and r["tflops"] > 50 for r in log["results"])
     # the cache entry: no path inside, and the next tune() returns it without a search
     cache_file = tmp_path / "cache" / "best_config_attention_128_128_sm100a_fp16_causal.json"
