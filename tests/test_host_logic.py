@@ -134,6 +134,32 @@ def test_argument_validation_without_gpu(lib):
     assert lib.attn_b200_fa_bwd(p, p, p, p, p, p, p, p, p, 1, 0, 128, 128, 128, 0, 0.1, 0, None) == 1   # H
 
 
+def test_chunkwise_segments_and_their_scratch_without_gpu(lib):
+    """Host arithmetic of the segmented chunkwise RetNet: how many segments the library prefers (as many as fill 148 SMs
+    with CTAs of 128 columns, each at least four chunks long; none when the slices alone fill the GPU or dv is not a
+    multiple of 128), how a forced count maps onto whole chunks, and the scratch (one fp32 [dqk x dv] tile per slice
+    and segment but the last). Argument errors are rejected before any CUDA call."""
+    ws = lib.attn_b200_ret_chunk_workspace_bytes
+    tile = 256 * 512 * 4
+    assert ws(1, 8, 16384, 256, 512, 0) == 3 * 8 * tile          # 32 tiles of 128 columns -> 4 segments of 32 chunks
+    assert ws(8, 8, 2048, 256, 512, 0) == 0                      # 256 tiles: the slices fill the GPU
+    assert ws(1, 2, 4096, 256, 256, 0) == 7 * 2 * 256 * 256 * 4  # 4 tiles, 32 chunks: 8 segments of 4 chunks
+    assert ws(1, 1, 512, 256, 512, 0) == 0                       # four chunks: nothing to cut
+    assert ws(1, 8, 16384, 256, 192, 0) == 0                     # dv not a multiple of 128: no preference
+    assert ws(1, 3, 1100, 128, 128, 1) == 0
+    for asked, count in ((2, 2), (3, 3), (4, 3), (5, 5), (9, 9), (50, 9)):   # nine chunks: ceil(9 / asked) chunks per segment
+        assert ws(1, 3, 1100, 128, 128, asked) == (count - 1) * 3 * 128 * 128 * 4, asked
+    assert ws(0, 1, 128, 128, 128, 0) == 0 and ws(1, 1, 128, 128, 128, -1) == 0
+    buf = ctypes.create_string_buffer(256)
+    p = ctypes.c_void_p((ctypes.addressof(buf) + 63) & ~63)      # the checks want 16- and 32-byte aligned tensors
+    call = lambda **kw: lib.attn_b200_ret_chunk_fwd_ws(p, p, p, p, p, kw.get("w"), kw.get("nbytes", 0), kw.get("segments", 0),
+                                                     1, 1, kw.get("L", 1100), kw.get("dqk", 128), 128, 0, 1.0, None)
+    assert call(dqk=64) == 2
+    assert call(segments=-1) == 1
+    assert call(segments=3) == 1 and b"scratch" in lib.attn_b200_last_error()          # no scratch at all
+    assert call(segments=3, w=p, nbytes=64) == 1 and b"scratch" in lib.attn_b200_last_error()
+
+
 def test_per_config_library_builds_and_exports_reference_symbols(tmp_path):
     cfg = AttnConfig(128, 128, 64, 64, q_tiles=1, kv_stages=2)
     rt = Runtime(B200(), cfg, tmp_dir=str(tmp_path))
